@@ -1,0 +1,102 @@
+"""CPU tests of the planner oracle and the emulated data movement (no GPU)."""
+import numpy as np
+import pytest
+import torch
+from hypothesis import given, settings, strategies as st
+
+from moonep_b200 import routing
+from moonep_b200.sim import plan_cluster, check_invariants, ops
+
+
+def _topk_all(R, S, K, E, gen):
+    return np.stack([gen(r)[0].numpy() for r in range(R)])
+
+
+@pytest.mark.parametrize("scale_target", [0.0, 0.5, 2.0])
+def test_baseline_cpu_config(scale_target):
+    """R=8, S=512, K=8, E=64, token_padding=16, softmax top-k with skew bias."""
+    R, S, K, E, pad = 8, 512, 8, 64, 16
+    scale, realised = routing.solve_scale_for_maxvio(scale_target, S, K, E, R, seed=0) if scale_target else (0.0, 0.0)
+    outs = [routing.softmax_topk(S, K, E, scale, 0, r) for r in range(R)]
+    topk = np.stack([o[0].numpy() for o in outs])
+    cp = plan_cluster(topk, E, pad)
+    check_invariants(cp)
+    H = 32
+    g = torch.Generator().manual_seed(1)
+    hidden = [torch.randn(S, H, generator=g) for _ in range(R)]
+    weights = [o[1] for o in outs]
+    hn, wn = ops.dispatch(cp, hidden, weights)
+    # every rank received exactly S*K real rows
+    for d in range(R):
+        real = ops.expert_of_slot(cp, d) >= 0
+        assert int(real.sum()) == S * K
+        assert not torch.isnan(hn[d][torch.from_numpy(real)]).any()
+    # the "FFN" scales each row by its route weight; combine must give sum_k p_k * x
+    y = [torch.nan_to_num(hn[d]) * torch.nan_to_num(wn[d])[:, None] for d in range(R)]
+    out, wsk = ops.combine(cp, y, wn)
+    for r in range(R):
+        assert torch.equal(wsk[r], weights[r])
+        expect = hidden[r] * weights[r].sum(dim=1, keepdim=True)
+        assert torch.allclose(out[r], expect, rtol=1e-5, atol=1e-5)
+    # weight grads: redundancy must not change the reduced result
+    epn = E // R
+    Hp = 4
+    slot_e = [ops.expert_of_slot(cp, d) for d in range(R)]
+    ref = [torch.zeros(epn, H, Hp) for _ in range(R)]
+    local = [torch.zeros(epn, H, Hp) for _ in range(R)]
+    red = [torch.zeros(epn, H, Hp) for _ in range(R)]
+    dy = [torch.randn(cp.NvS, Hp, generator=g) for _ in range(R)]
+    for d in range(R):
+        for g_ in range(2 * epn):
+            e = d * epn + g_ if g_ < epn else int(cp.experts_to_copy[d, g_ - epn])
+            if e < 0:
+                continue
+            rows = torch.from_numpy(slot_e[d] == e)
+            contrib = hn[d][rows].T @ dy[d][rows]
+            ref[e // epn][e % epn] += contrib
+            (local[d] if g_ < epn else red[d])[g_ % epn] += contrib
+    ops.reduce_grad(cp, local, red)
+    for r in range(R):
+        assert torch.allclose(local[r], ref[r], rtol=1e-4, atol=1e-4)
+        assert not red[r].any()
+
+
+@pytest.mark.parametrize("pattern", ["all_local", "all_remote", "single_expert", "duplicate_topk"])
+@pytest.mark.parametrize("R", [1, 2, 4])
+def test_patterns(pattern, R):
+    S, K, epn, pad = 33, 4, 3, 8
+    E = R * epn
+    topk = np.stack([routing.pattern_topk(pattern, S, K, E, R, r)[0].numpy() for r in range(R)])
+    cp = plan_cluster(topk, E, pad)
+    check_invariants(cp)
+
+
+@pytest.mark.parametrize("sigma", [0.0, 0.5, 1.0, 5.0])
+def test_lognormal(sigma):
+    R, S, K, E = 8, 256, 8, 64
+    topk = np.stack([routing.lognormal_topk(S, K, E, R, sigma, 42, r)[0].numpy() for r in range(R)])
+    cp = plan_cluster(topk, E, 128)
+    check_invariants(cp)
+    if sigma == 0.0:
+        assert (cp.experts_to_copy < 0).all()
+
+
+@settings(max_examples=60, deadline=None)
+@given(R=st.sampled_from([1, 2, 3, 4, 8]), epn=st.integers(1, 5), S=st.integers(1, 40),
+       K=st.integers(1, 6), pad=st.sampled_from([1, 4, 16]), seed=st.integers(0, 10_000),
+       hot=st.floats(0.0, 1.0))
+def test_planner_properties(R, epn, S, K, pad, seed, hot):
+    E = R * epn
+    rng = np.random.default_rng(seed)
+    p = rng.random(E) ** (1 + 8 * hot)
+    p /= p.sum()
+    topk = rng.choice(E, size=(R, S, K), p=p)
+    cp = plan_cluster(topk, E, pad)
+    check_invariants(cp)
+    # duplicate encoding: exactly one non-negative entry per (token, destination rank)
+    dest = cp.dst_raw // cp.NvS
+    for r in range(R):
+        for s in range(S):
+            row = slice(s * K, (s + 1) * K)
+            prim = dest[r, row][cp.dst[r, row] >= 0]
+            assert len(set(prim.tolist())) == len(prim) == len(set(dest[r, row].tolist()))
