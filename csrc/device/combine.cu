@@ -1,0 +1,165 @@
+// Combine: local duplicate pre-reduction, fused unpermute + K-sum over peers, and the
+// stand-alone rank sync.
+//
+// Counterpart of the reference's CombinePrologueKernel (moonep/combine_prologue.py:41-484),
+// CombineKernel (moonep/combine.py:40-511) and InterRankSyncKernel
+// (moonep/inter_rank_sync.py:22-83). Semantics kept: combine is an UNWEIGHTED sum of a
+// token's rows; duplicates of one destination rank are summed in fp32 and rounded to bf16
+// once into the primary row, the per-rank partial sums are then added in fp32 (ascending k)
+// and rounded once; the optional [S,K] channel gathers the per-slot fp32 route weights back
+// bit-exactly. Peer rows are pulled with plain 16-byte loads by whole warps (8 loads in
+// flight per lane), never with bulk copies from peer memory.
+#include "prims.cuh"
+#include "../host/launch.h"
+
+namespace mep {
+
+__device__ __forceinline__ void acc_bf16x8(float* acc, const int4& x) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+}
+__device__ __forceinline__ int4 pack_bf16x8(const float* acc) {
+  int4 o; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  return o;
+}
+
+// ------------------------------------------------------------------ dup_reduce
+struct DupArgs { __nv_bfloat16* buf; const int32_t* dup_groups; const int32_t* dup_loffs; const int32_t* dup_counts; };
+struct DupArgsPack { DupArgs a[MEP_MAX_VRANKS]; };
+
+__global__ void __launch_bounds__(256) dup_reduce_kernel(MepCtxPack P, DupArgsPack A) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const DupArgs& a = A.a[blockIdx.y];
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
+  const int ng = a.dup_counts[0];
+  const size_t row_bytes = (size_t)c.H * 2;
+  const int nvec = (int)(row_bytes >> 4);
+  char* base = (char*)a.buf;
+  for (int g = gw; g < ng; g += nw) {
+    const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
+    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
+    char* prow = base + (size_t)p * row_bytes;
+    for (int v = lane; v < nvec; v += 32) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      acc_bf16x8(acc, ld_nc_v4(prow + (size_t)v * 16));
+      for (int j = 0; j < n; ++j) {
+        const int q = a.dup_loffs[st + j];
+        if ((unsigned)q < (unsigned)c.NvS) acc_bf16x8(acc, ld_nc_v4(base + (size_t)q * row_bytes + (size_t)v * 16));
+      }
+      st_v4(prow + (size_t)v * 16, pack_bf16x8(acc));
+    }
+  }
+}
+
+// ------------------------------------------------------------------ combine
+struct CombineArgs {
+  const int32_t* dst;       // [N] plan
+  __nv_bfloat16* out;       // [S, H]
+  float* out_weights;       // [S, K] or null
+  int32_t entry_barrier;    // cross-rank barrier before the first peer read (normally 1)
+};
+struct CombineArgsPack { CombineArgs a[MEP_MAX_VRANKS]; };
+
+constexpr int kCombThreads = 512;
+constexpr int kCombBatch = 4;      // primaries loaded per batch (x2 column chunks per lane)
+
+__global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, CombineArgsPack A) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const CombineArgs& a = A.a[blockIdx.y];
+  const int nb = gridDim.x, lane = threadIdx.x & 31, wpb = blockDim.x >> 5, warp = threadIdx.x >> 5;
+  const int K = c.K, S = c.S, NvS = c.NvS;
+  const size_t row_bytes = (size_t)c.H * 2;
+  const int nvec = (int)(row_bytes >> 4);
+
+  if (a.entry_barrier) { if (!cross_rank_barrier(c, nb, 2, MEP_K_COMBINE, 10)) return; }
+
+  for (int s = blockIdx.x * wpb + warp; s < S; s += nb * wpb) {
+    int dval = -1;
+    if (lane < K) dval = a.dst[(size_t)s * K + lane];
+    const char* myrow = nullptr;
+    if (lane < K) {
+      const int raw = dval >= 0 ? dval : -dval - 1;
+      const int d = raw / NvS, loff = raw - d * NvS;
+      if (a.out_weights)
+        a.out_weights[(size_t)s * K + lane] = __ldcg((const float*)peer_ptr(c, d, c.off_weights) + loff);
+      if (dval >= 0) myrow = peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes;
+    }
+    const unsigned prim = __ballot_sync(0xffffffffu, myrow != nullptr);
+    const int np = __popc(prim);
+    char* orow = (char*)a.out + (size_t)s * row_bytes;
+    for (int v0 = 0; v0 < nvec; v0 += 64) {
+      const int va = v0 + lane, vb = v0 + 32 + lane;
+      float acc0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, acc1[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      unsigned rest = prim;
+      for (int j0 = 0; j0 < np; j0 += kCombBatch) {
+        int4 x0[kCombBatch], x1[kCombBatch];
+#pragma unroll
+        for (int j = 0; j < kCombBatch; ++j) {
+          const bool on = j0 + j < np;
+          const int src = on ? __ffs(rest) - 1 : 0;
+          if (on) rest &= rest - 1;
+          const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)myrow, src);
+          x0[j] = make_int4(0, 0, 0, 0); x1[j] = make_int4(0, 0, 0, 0);
+          if (on && va < nvec) x0[j] = ld_peer_v4(rp + (size_t)va * 16);
+          if (on && vb < nvec) x1[j] = ld_peer_v4(rp + (size_t)vb * 16);
+        }
+#pragma unroll
+        for (int j = 0; j < kCombBatch; ++j) { acc_bf16x8(acc0, x0[j]); acc_bf16x8(acc1, x1[j]); }
+      }
+      if (va < nvec) st_na_v4(orow + (size_t)va * 16, pack_bf16x8(acc0));
+      if (vb < nvec) st_na_v4(orow + (size_t)vb * 16, pack_bf16x8(acc1));
+    }
+  }
+}
+
+// ------------------------------------------------------------------ stand-alone rank sync
+__global__ void rank_sync_kernel(MepCtxPack P) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  if (c.R > 1) cross_rank_arrive_wait(c, 3, MEP_K_SYNC, 1);
+}
+
+// ------------------------------------------------------------------ bounded-wait self test
+// Waits on a flag that only the host could set; with nobody setting it the wait must give
+// up after the Buffer's budget, record MEP_ERR_FLAG_TIMEOUT and return normally.
+__global__ void wait_probe_kernel(MepCtxPack P, const uint32_t* flag, uint32_t expected) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  if (threadIdx.x == 0) {
+    uint32_t seen = 0;
+    const bool ok = bounded_wait(c, [&] { seen = ld_acquire_sys(flag); return seen == expected; });
+    if (!ok) report(c, MEP_ERR_FLAG_TIMEOUT, MEP_K_WAIT_PROBE, 1, -1, seen, expected);
+  }
+}
+
+}  // namespace mep
+
+extern "C" int mep_launch_dup_reduce(int nv, const MepRankCtx* const* ctxs, const mep::DupArgs* args,
+                                     int num_blocks, cudaStream_t stream) {
+  MepCtxPack P = {}; mep::DupArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  return mep::launch_plain(mep::dup_reduce_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A);
+}
+
+extern "C" int mep_launch_combine(int nv, const MepRankCtx* const* ctxs, const mep::CombineArgs* args,
+                                  int num_sms, cudaStream_t stream) {
+  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "combine: nv=%d out of range", nv);
+  MepCtxPack P = {}; mep::CombineArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  return mep::launch_cooperative(mep::combine_kernel, dim3(num_sms, nv), dim3(mep::kCombThreads), 0,
+                                 stream, false, P, A);
+}
+
+extern "C" int mep_launch_rank_sync(int nv, const MepRankCtx* const* ctxs, cudaStream_t stream) {
+  MepCtxPack P = {};
+  for (int i = 0; i < nv; ++i) P.ctx[i] = ctxs[i];
+  return mep::launch_cooperative(mep::rank_sync_kernel, dim3(1, nv), dim3(128), 0, stream, false, P);
+}
+
+extern "C" int mep_launch_wait_probe(const MepRankCtx* ctx, const uint32_t* flag, uint32_t expected,
+                                     cudaStream_t stream) {
+  MepCtxPack P = {}; P.ctx[0] = ctx;
+  return mep::launch_plain(mep::wait_probe_kernel, dim3(1, 1), dim3(32), 0, stream, P, flag, expected);
+}

@@ -1,0 +1,225 @@
+// Dispatch: fused permute + expert all-to-all, and the local duplicate expansion.
+//
+// Counterpart of the reference's DispatchKernel (moonep/dispatch.py:50-692) and
+// DispatchEpilogueKernel (moonep/dispatch_epilogue.py:44-304), redesigned:
+//  * every warp of every CTA is an independent sender: it stages one token row in its own
+//    shared-memory ring slot with a local bulk copy and fans it out with one bulk store per
+//    distinct destination rank (entries with dst >= 0) while its lanes scatter the K route
+//    weights -- instead of one producer lane and one consumer lane per CTA;
+//  * duplicate groups were already emitted by the planner from the sender side, so there is
+//    no builder pass here: `dup_finalize` only compacts the per-source staging regions into
+//    the plan-owned tables after the exit barrier;
+//  * a spare warp per CTA clears the padding rows of the local shard meanwhile.
+// Exit: one cross-rank barrier publishes all remote writes.
+#include "prims.cuh"
+#include "../host/launch.h"
+
+namespace mep {
+
+struct DispatchArgs {
+  const __nv_bfloat16* hidden;   // [S, H] local tokens
+  const float* weights;          // [S, K] or null
+  const int32_t* dst;            // [N] plan
+  const int32_t* zero_fill;      // [2epn, 2] plan
+  int32_t fresh;                 // 1: publish duplicate-table counts to the peers
+  int32_t entry_barrier;         // 1: cross-rank barrier before the first remote write
+};
+struct DispatchArgsPack { DispatchArgs a[MEP_MAX_VRANKS]; };
+
+constexpr int kSendWarps = 6;                 // sender warps per CTA
+constexpr int kDispThreads = (kSendWarps + 1) * 32;   // + one zero-fill warp
+constexpr int kMaxStages = 8;
+
+template <int N> __device__ __forceinline__ void wait_read_le() { bulk_wait_read<N>(); }
+__device__ __forceinline__ void wait_read_dyn(int n) {
+  switch (n) {
+    case 0: bulk_wait_read<0>(); break; case 1: bulk_wait_read<1>(); break;
+    case 2: bulk_wait_read<2>(); break; case 3: bulk_wait_read<3>(); break;
+    case 4: bulk_wait_read<4>(); break; case 5: bulk_wait_read<5>(); break;
+    case 6: bulk_wait_read<6>(); break; default: bulk_wait_read<7>(); break;
+  }
+}
+
+__global__ void __launch_bounds__(kDispThreads, 1)
+dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const DispatchArgs& a = A.a[blockIdx.y];
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t s_bar[kSendWarps * kMaxStages];
+  __shared__ int s_err;
+  const int nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int K = c.K, S = c.S, NvS = c.NvS;
+  const uint32_t row_bytes = (uint32_t)c.H * 2u;
+
+  if (tid == 0) s_err = 0;
+  if (tid < kSendWarps * kMaxStages) mbar_init(&s_bar[tid], 1);
+  fence_mbar_init();
+  __syncthreads();
+
+  if (a.entry_barrier) { if (!cross_rank_barrier(c, nb, 1, MEP_K_DISPATCH, 10)) return; }
+
+  if (a.fresh && blockIdx.x == 0) {
+    // tell every destination how many groups / duplicate offsets this rank appended
+    for (int d = tid; d < c.R; d += blockDim.x) {
+      const unsigned long long v = c.send_cnt[d];
+      int* cnt = (int*)peer_ptr(c, d, c.off_dupcnt) + 2 * c.rank;
+      cnt[0] = (int)(v >> 32); cnt[1] = (int)(v & 0xffffffffu);
+    }
+  }
+
+  if (warp < kSendWarps) {
+    unsigned char* ring = smem + (size_t)warp * stages * row_bytes;
+    uint64_t* bars = s_bar + warp * kMaxStages;
+    char* my_hidden = nullptr; (void)my_hidden;
+    int it = 0;
+    for (int s = blockIdx.x * kSendWarps + warp; s < S; s += nb * kSendWarps, ++it) {
+      const int st = it % stages;
+      const uint32_t parity = (uint32_t)(it / stages) & 1u;
+      int dval = 0; float w = 0.f;
+      if (lane < K) { dval = a.dst[(size_t)s * K + lane]; if (a.weights) w = a.weights[(size_t)s * K + lane]; }
+      bool ok = true;
+      if (lane == 0) {
+        // ring slot `st` was last read by the stores issued `stages` iterations ago
+        wait_read_dyn(stages - 1);
+        mbar_expect_tx(&bars[st], row_bytes);
+        bulk_g2s(ring + (size_t)st * row_bytes, a.hidden + (size_t)s * c.H, row_bytes, &bars[st]);
+        ok = mbar_wait_bounded(&bars[st], parity, c.wait_budget_ns);
+        if (!ok) { report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_DISPATCH, 20, s, 0, 0); s_err = 1; }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      // route weights: every entry (primary or duplicate) owns a slot on its destination
+      if (lane < K && a.weights) {
+        const int raw = dval >= 0 ? dval : -dval - 1;
+        const int d = raw / NvS, loff = raw - d * NvS;
+        ((float*)peer_ptr(c, d, c.off_weights))[loff] = w;
+      }
+      for (int k = 0; k < K; ++k) {
+        const int dv = __shfl_sync(0xffffffffu, dval, k);
+        if (dv >= 0 && lane == 0) {
+          const int d = dv / NvS, loff = dv - d * NvS;
+          bulk_s2g(peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes, ring + (size_t)st * row_bytes, row_bytes);
+        }
+      }
+      if (lane == 0) bulk_commit();
+    }
+    if (lane == 0) { bulk_wait_all<0>(); fence_proxy_async(); }
+  } else {
+    // zero-fill warp: padding rows (and their weight slots) of the local shard
+    const int ngroups = 2 * c.epn;
+    char* hid = peer_ptr(c, c.rank, c.off_hidden);
+    float* wts = (float*)peer_ptr(c, c.rank, c.off_weights);
+    const int vec_per_row = (int)(row_bytes >> 4);
+    const int4 z = make_int4(0, 0, 0, 0);
+    int rr = 0;   // running row counter to spread rows over CTAs
+    for (int g = 0; g < ngroups; ++g) {
+      const int p0 = a.zero_fill[2 * g], n = a.zero_fill[2 * g + 1];
+      for (int j = 0; j < n; ++j, ++rr) {
+        if (rr % nb != (int)blockIdx.x) continue;
+        char* row = hid + (size_t)(p0 + j) * row_bytes;
+        for (int v = lane; v < vec_per_row; v += 32) st_v4(row + (size_t)v * 16, z);
+        if (lane == 0 && a.weights) wts[p0 + j] = 0.f;
+      }
+    }
+  }
+  cross_rank_barrier(c, nb, 1, MEP_K_DISPATCH, 30);
+}
+
+// ---------------------------------------------------------------------------------------
+// dup_finalize: compact the per-source staging regions [R][cap] of this rank into the
+// plan-owned dup_groups[NvS,3] / dup_loffs[NvS] / dup_counts[2] (order = source-rank major,
+// then arrival order inside a source: a set, as in the reference).
+struct DupFinalizeArgs { int32_t* dup_groups; int32_t* dup_loffs; int32_t* dup_counts; };
+struct DupFinalizeArgsPack { DupFinalizeArgs a[MEP_MAX_VRANKS]; };
+
+__global__ void dup_finalize_kernel(MepCtxPack P, DupFinalizeArgsPack A) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const DupFinalizeArgs& a = A.a[blockIdx.y];
+  __shared__ int s_goff[MEP_MAX_RANKS + 1], s_loff[MEP_MAX_RANKS + 1];
+  const int* cnt = (const int*)peer_ptr(c, c.rank, c.off_dupcnt);
+  if (threadIdx.x == 0) {
+    int g = 0, l = 0;
+    for (int r = 0; r < c.R; ++r) { s_goff[r] = g; s_loff[r] = l; g += __ldcg(cnt + 2 * r); l += __ldcg(cnt + 2 * r + 1); }
+    s_goff[c.R] = g; s_loff[c.R] = l;
+    if (blockIdx.x == 0) { a.dup_counts[0] = g; a.dup_counts[1] = l; }
+  }
+  __syncthreads();
+  const int* sg = (const int*)peer_ptr(c, c.rank, c.off_dupgroups);
+  const int* sl = (const int*)peer_ptr(c, c.rank, c.off_duploffs);
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gnt = gridDim.x * blockDim.x;
+  for (int r = 0; r < c.R; ++r) {
+    const int ng = s_goff[r + 1] - s_goff[r], nl = s_loff[r + 1] - s_loff[r];
+    for (int j = gtid; j < ng; j += gnt) {
+      const int* src = sg + ((size_t)r * c.dup_group_cap + j) * 3;
+      int* dstp = a.dup_groups + (size_t)(s_goff[r] + j) * 3;
+      dstp[0] = __ldcg(src); dstp[1] = __ldcg(src + 1) + s_loff[r]; dstp[2] = __ldcg(src + 2);
+    }
+    for (int j = gtid; j < nl; j += gnt)
+      a.dup_loffs[s_loff[r] + j] = __ldcg(sl + (size_t)r * c.dup_loff_cap + j);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// dup_expand: copy each primary row of `buf` onto its duplicate rows (one warp per group).
+struct DupArgs { __nv_bfloat16* buf; const int32_t* dup_groups; const int32_t* dup_loffs; const int32_t* dup_counts; };
+struct DupArgsPack { DupArgs a[MEP_MAX_VRANKS]; };
+
+__global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPack A) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const DupArgs& a = A.a[blockIdx.y];
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
+  const int ng = a.dup_counts[0];
+  const size_t row_bytes = (size_t)c.H * 2;
+  const int nvec = (int)(row_bytes >> 4);
+  char* base = (char*)a.buf;
+  for (int g = gw; g < ng; g += nw) {
+    const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
+    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
+    const char* src = base + (size_t)p * row_bytes;
+    for (int v = lane; v < nvec; v += 32) {
+      const int4 x = ld_nc_v4(src + (size_t)v * 16);
+      for (int j = 0; j < n; ++j) {
+        const int q = a.dup_loffs[st + j];
+        if ((unsigned)q < (unsigned)c.NvS) st_na_v4(base + (size_t)q * row_bytes + (size_t)v * 16, x);
+      }
+    }
+  }
+}
+
+}  // namespace mep
+
+extern "C" int mep_dispatch_smem_stages(int H, int* stages_out, size_t* smem_out) {
+  const size_t row = (size_t)H * 2;
+  const size_t budget = 200 * 1024;
+  int stages = (int)(budget / (row * mep::kSendWarps));
+  if (stages > mep::kMaxStages) stages = mep::kMaxStages;
+  MEP_REQUIRE(stages >= 1, "dispatch: H=%d rows (%zu B) do not fit the shared-memory ring", H, row);
+  *stages_out = stages; *smem_out = row * mep::kSendWarps * stages;
+  return 0;
+}
+
+extern "C" int mep_launch_dispatch(int nv, const MepRankCtx* const* ctxs, const mep::DispatchArgs* args,
+                                   int num_sms, int H, cudaStream_t stream) {
+  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "dispatch: nv=%d out of range", nv);
+  MepCtxPack P = {}; mep::DispatchArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  int stages; size_t smem;
+  if (mep_dispatch_smem_stages(H, &stages, &smem)) return -1;
+  return mep::launch_cooperative(mep::dispatch_kernel, dim3(num_sms, nv), dim3(mep::kDispThreads), smem,
+                                 stream, false, P, A, stages);
+}
+
+extern "C" int mep_launch_dup_finalize(int nv, const MepRankCtx* const* ctxs, const mep::DupFinalizeArgs* args,
+                                       cudaStream_t stream) {
+  MepCtxPack P = {}; mep::DupFinalizeArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  return mep::launch_plain(mep::dup_finalize_kernel, dim3(8, nv), dim3(256), 0, stream, P, A);
+}
+
+extern "C" int mep_launch_dup_expand(int nv, const MepRankCtx* const* ctxs, const mep::DupArgs* args,
+                                     int num_blocks, cudaStream_t stream) {
+  MepCtxPack P = {}; mep::DupArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  return mep::launch_plain(mep::dup_expand_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A);
+}

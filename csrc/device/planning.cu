@@ -1,0 +1,337 @@
+// Online redundant-expert planner, replicated on every rank.
+//
+// Produces, with no host synchronisation, the same tables as the reference's
+// rank-0-centralised PlanningKernel (moonep/planning.py:328-1101; executable spec
+// tests/planning_reference.py:25-311): dst[N], cu_seqlens[2epn], experts_to_copy[R,epn],
+// zero_fill_ranges[2epn,2], remote_stats[2] -- plus the duplicate-row groups, which this
+// kernel emits from the sender side straight into the destination rank's staging tables.
+//
+// Structure (one cooperative launch, grid = num_sms CTAs x 1024 threads per rank):
+//   P0  CTA 0 stores this rank's expert histogram into row `rank` of every peer's table;
+//       all CTAs histogram their 1024-entry blocks of the local top-k table;
+//       ONE cross-rank barrier (the reference needs three).
+//   P1  CTA 0 solves the plan from the all-gathered histograms -- every rank computes the
+//       identical result, so nothing is broadcast; the other CTAs turn the block
+//       histograms into exclusive offsets.
+//   P2  every entry gets its index among the same-expert entries (stable order), its
+//       destination rank by binary search in the per-expert prefix over ranks, and its
+//       slot; per token, later entries to an already used rank are marked duplicates and
+//       (primary, duplicates) groups are appended to the destination's staging tables.
+#include "prims.cuh"
+#include "../host/launch.h"
+#include <limits.h>
+
+namespace mep {
+
+struct PlanArgs {
+  const int32_t* topk;        // [N]
+  const int32_t* tpe;         // [E]
+  int32_t* dst;               // [N]
+  int32_t* cu_seqlens;        // [2epn]
+  int32_t* experts_to_copy;   // [R, epn]
+  int32_t* zero_fill;         // [2epn, 2]
+  int32_t* remote_stats;      // [2]
+};
+struct PlanArgsPack { PlanArgs a[MEP_MAX_VRANKS]; };
+
+constexpr int kPlanThreads = 1024;
+constexpr int kSmemECap = 8192;   // per-expert scratch lives in shared memory up to this E
+
+__device__ __forceinline__ int vload(const int* p) { return *(const volatile int*)p; }
+__device__ __forceinline__ void vstore(int* p, int v) { *(volatile int*)p = v; }
+
+// ---- P1 on CTA 0: receiver selection, expert split, layout (see file header).
+__device__ void solve(const MepRankCtx& c, const PlanArgs& a, int* s_e, bool e_in_smem) {
+  __shared__ int s_bal[MEP_MAX_RANKS];
+  __shared__ int s_recv_from[MEP_MAX_RANKS];
+  __shared__ int s_quota[MEP_MAX_RANKS];
+  __shared__ int s_send[MEP_MAX_RANKS];
+  __shared__ int s_recvn[MEP_MAX_RANKS];
+  const int R = c.R, E = c.E, epn = c.epn, cap = c.N, pad = c.token_padding;
+  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+  const int* tpeall = (const int*)peer_ptr(c, c.rank, c.off_tpe);
+  int* remaining = e_in_smem ? s_e : c.remaining;
+
+  // S1: totals per expert, my exclusive prefix over source ranks
+  for (int e = tid; e < E; e += nt) {
+    int run = 0;
+    for (int r = 0; r < R; ++r) {
+      if (r == c.rank) c.tpe_prefix[e] = run;
+      run += __ldcg(tpeall + (size_t)r * E + e);
+    }
+    c.count[e] = run;
+    remaining[e] = run;
+  }
+  for (int r = tid; r < R; r += nt) { s_recv_from[r] = -1; s_quota[r] = 0; s_send[r] = 0; s_recvn[r] = 0; }
+  __syncthreads();
+  for (int h = warp; h < R; h += nwarps) {
+    int sum = 0;
+    for (int j = lane; j < epn; j += 32) sum += vload(remaining + h * epn + j);
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) s_bal[h] = sum - cap;
+  }
+  __syncthreads();
+
+  // S2: receivers. Most loaded group feeds the emptiest rank until it holds exactly S*K.
+  if (warp == 0) {
+    for (int it = 0; it < R; ++it) {
+      long long kmax = LLONG_MIN, kmin = LLONG_MIN;
+      for (int r = lane; r < R; r += 32) {
+        const int b = s_bal[r];
+        const long long k1 = argmax_key(b, r), k2 = argmax_key(-b, r);
+        kmax = k1 > kmax ? k1 : kmax; kmin = k2 > kmin ? k2 : kmin;
+      }
+      kmax = warp_max64(kmax); kmin = warp_max64(kmin);
+      const int h = key_index(kmax), bh = key_value(kmax);
+      const int u = key_index(kmin), bu = -key_value(kmin);
+      if (bh <= 0 || bu >= 0) break;
+      if (lane == 0) { s_recv_from[u] = h; s_quota[u] = -bu; s_bal[h] = bh + bu; s_bal[u] = 0; }
+      __syncwarp();
+    }
+  }
+  // S3a: dense allocation table starts with every expert at home
+  for (int i = tid; i < E * R; i += nt) {
+    const int e = i / R, d = i - e * R;
+    c.alloc[i] = (d == e / epn) ? c.count[e] : 0;
+  }
+  __syncthreads();
+
+  // S3b: split each donor group's tokens over its receivers (one warp per home group)
+  for (int h = warp; h < R; h += nwarps) {
+    for (int guard = 0; guard < R + epn + 2; ++guard) {
+      long long kq = LLONG_MIN;
+      for (int u = lane; u < R; u += 32)
+        if (s_recv_from[u] == h) { const long long k = argmax_key(s_quota[u], u); kq = k > kq ? k : kq; }
+      kq = warp_max64(kq);
+      if (kq == LLONG_MIN || key_value(kq) <= 0) break;
+      long long kr = LLONG_MIN;
+      for (int j = lane; j < epn; j += 32) { const long long k = argmax_key(vload(remaining + h * epn + j), j); kr = k > kr ? k : kr; }
+      kr = warp_max64(kr);
+      const int d = key_index(kq), quota = key_value(kq), le = key_index(kr), rem = key_value(kr);
+      const int take = rem < quota ? rem : quota;
+      if (take <= 0) break;
+      if (lane == 0) {
+        const int e = h * epn + le;
+        c.alloc[(size_t)e * R + d] += take;
+        c.alloc[(size_t)e * R + h] -= take;
+        vstore(remaining + e, rem - take);
+        s_quota[d] = quota - take;
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+
+  // S5: prefix over destination ranks per expert (binary-searched in P2)
+  for (int e = tid; e < E; e += nt) {
+    int run = 0;
+    for (int d = 0; d < R; ++d) { run += c.alloc[(size_t)e * R + d]; c.alloc_cumsum[(size_t)e * R + d] = run; }
+  }
+  // S4: layout of every destination rank (one warp each)
+  for (int d = warp; d < R; d += nwarps) {
+    const int h = s_recv_from[d];
+    int* etc = c.etc_all + (size_t)d * epn;
+    for (int b = lane; b < epn; b += 32) { vstore(etc + b, -1); a.experts_to_copy[(size_t)d * epn + b] = -1; }
+    __syncwarp();
+    int nrem = 0;
+    if (h >= 0) {
+      for (int j0 = 0; j0 < epn; j0 += 32) {
+        const int j = j0 + lane;
+        const bool has = j < epn && c.alloc[(size_t)(h * epn + j) * R + d] > 0;
+        const unsigned bal = __ballot_sync(0xffffffffu, has);
+        if (has) {
+          const int pos = nrem + __popc(bal & lanemask_lt());
+          vstore(etc + pos, h * epn + j);
+          a.experts_to_copy[(size_t)d * epn + pos] = h * epn + j;
+        }
+        nrem += __popc(bal);
+      }
+    }
+    if (lane == 0) { s_recvn[d] = nrem; if (h >= 0 && nrem) atomicAdd(&s_send[h], nrem); }
+    __syncwarp();
+    int start = 0;
+    for (int g0 = 0; g0 < 2 * epn; g0 += 32) {
+      const int g = g0 + lane;
+      int e = -1, cnt = 0;
+      if (g < epn) e = d * epn + g; else if (g < 2 * epn) e = vload(etc + g - epn);
+      if (e >= 0) cnt = c.alloc[(size_t)e * R + d];
+      const int padded = cnt > 0 ? (cnt + pad - 1) / pad * pad : 0;
+      const int incl = warp_incl_scan(padded);
+      const int beg = start + incl - padded, end = start + incl;
+      if (g < 2 * epn) {
+        if (cnt > 0) c.expert_off[(size_t)d * E + e] = beg;
+        if (d == c.rank) {
+          a.cu_seqlens[g] = end;
+          const bool haspad = cnt > 0 && padded > cnt;
+          a.zero_fill[2 * g] = haspad ? beg + cnt : 0;
+          a.zero_fill[2 * g + 1] = haspad ? padded - cnt : 0;
+        }
+      }
+      start += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) { a.remote_stats[0] = s_recvn[c.rank]; a.remote_stats[1] = s_send[c.rank]; }
+  for (int r = tid; r < R; r += nt) { c.stats_all[2 * r] = s_recvn[r]; c.stats_all[2 * r + 1] = s_send[r]; }
+}
+
+__global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P, PlanArgsPack A) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const PlanArgs& a = A.a[blockIdx.y];
+  extern __shared__ int s_e[];
+  __shared__ int s_raw[kPlanThreads];
+  __shared__ unsigned char s_dest[kPlanThreads];
+  __shared__ int s_pos[kPlanThreads];                 // CTA-local (group<<16 | loff) position of a primary's group
+  __shared__ unsigned long long s_cnt[MEP_MAX_RANKS]; // groups<<32 | loffs reserved by this CTA per destination
+  __shared__ unsigned long long s_base[MEP_MAX_RANKS];
+  const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
+  const int R = c.R, E = c.E, N = c.N, K = c.K, NvS = c.NvS, VB = c.vblock_entries;
+  const bool e_in_smem = E <= kSmemECap;
+
+  // ---------------- P0
+  if (blockIdx.x == 0) {
+    for (int i = tid; i < R * E; i += nt) {
+      const int p = i / E, e = i - p * E;
+      ((int*)peer_ptr(c, p, c.off_tpe))[(size_t)c.rank * E + e] = a.tpe[e];
+    }
+    for (int d = tid; d < R; d += nt) c.send_cnt[d] = 0ull;
+  }
+  for (int v = blockIdx.x; v < c.num_vblocks; v += nb) {
+    int* row = c.hist + (size_t)v * E;
+    int* h = e_in_smem ? s_e : row;
+    for (int e = tid; e < E; e += nt) h[e] = 0;
+    __syncthreads();
+    const int i = v * VB + tid;
+    if (tid < VB && i < N) {
+      const int e = a.topk[i];
+      if ((unsigned)e < (unsigned)E) atomicAdd(&h[e], 1);
+      else report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 1, i, (uint32_t)e, (uint32_t)E);
+    }
+    __syncthreads();
+    if (e_in_smem) for (int e = tid; e < E; e += nt) row[e] = s_e[e];
+    __syncthreads();
+  }
+  if (!cross_rank_barrier(c, nb, 0, MEP_K_PLANNING, 10)) return;
+
+  // ---------------- P1
+  if (blockIdx.x == 0) { solve(c, a, s_e, e_in_smem); __syncthreads(); }
+  if (nb == 1 || blockIdx.x != 0) {
+    const int workers = nb == 1 ? 1 : nb - 1, me = nb == 1 ? 0 : blockIdx.x - 1;
+    for (int e = me * nt + tid; e < E; e += workers * nt) {
+      int run = 0;
+      for (int v = 0; v < c.num_vblocks; ++v) {
+        int* p = c.hist + (size_t)v * E + e;
+        const int t = __ldcg(p);
+        *p = run; run += t;
+      }
+    }
+  }
+  if (!grid_sync(c, nb, MEP_K_PLANNING, 20)) return;
+  if (aborted(c)) return;
+
+  // ---------------- P2
+  const int tok_per_vb = VB / K;
+  for (int v = blockIdx.x; v < c.num_vblocks; v += nb) {
+    int* row = c.hist + (size_t)v * E;
+    int* cnt = e_in_smem ? s_e : row;
+    if (e_in_smem) for (int e = tid; e < E; e += nt) s_e[e] = __ldcg(row + e);
+    for (int d = tid; d < R; d += nt) s_cnt[d] = 0ull;
+    __syncthreads();
+    const int i = v * VB + tid;
+    const bool active = tid < VB && i < N;
+    int e = active ? a.topk[i] : 0;
+    if ((unsigned)e >= (unsigned)E) e = 0;
+    const int n_here = min(VB, N - v * VB);
+    const int nw = (n_here + 31) >> 5;
+    int local_cnt = 0;
+    for (int w = 0; w < nw; ++w) {       // warps in index order => stable ranking
+      if (warp == w) {
+        const unsigned act = __ballot_sync(0xffffffffu, active);
+        if (active) {
+          const unsigned m = __match_any_sync(act, e);
+          const int leader = __ffs(m) - 1;
+          int old = 0;
+          if (lane == leader) { old = vload(cnt + e); vstore(cnt + e, old + __popc(m)); }
+          old = __shfl_sync(m, old, leader);
+          local_cnt = old + __popc(m & lanemask_lt());
+        }
+      }
+      __syncthreads();
+    }
+    int raw = 0, dr = 0;
+    if (active) {
+      const int g = __ldcg(c.tpe_prefix + e) + local_cnt;
+      const int* ac = c.alloc_cumsum + (size_t)e * R;
+      int lo = 0, hi = R - 1;
+      while (lo < hi) { const int mid = (lo + hi) >> 1; if (__ldcg(ac + mid) > g) hi = mid; else lo = mid + 1; }
+      dr = lo;
+      const int prev = dr ? __ldcg(ac + dr - 1) : 0;
+      const int loff = __ldcg(c.expert_off + (size_t)dr * E + e) + (g - prev);
+      if ((unsigned)loff >= (unsigned)NvS || g >= __ldcg(ac + dr))
+        report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 2, i, (uint32_t)loff, (uint32_t)NvS);
+      raw = dr * NvS + loff;
+    }
+    s_raw[tid] = raw; s_dest[tid] = (unsigned char)dr; s_pos[tid] = -1;
+    __syncthreads();
+
+    // token phase A: duplicate marking + CTA-local reservation of group slots
+    const int s_tok = v * tok_per_vb + tid;
+    const bool tok_active = tid < tok_per_vb && s_tok < c.S;
+    if (tok_active) {
+      const int base = tid * K;
+      for (int k = 0; k < K; ++k) {
+        const int d = s_dest[base + k];
+        bool first = true;
+        for (int k2 = 0; k2 < k; ++k2) first = first && (s_dest[base + k2] != d);
+        const int r = s_raw[base + k];
+        a.dst[(size_t)s_tok * K + k] = first ? r : -r - 1;
+        if (first) {
+          int n = 0;
+          for (int k2 = k + 1; k2 < K; ++k2) n += (s_dest[base + k2] == d);
+          if (n > 0) {
+            const unsigned long long old = atomicAdd(&s_cnt[d], (1ull << 32) | (unsigned)n);
+            s_pos[base + k] = (int)(((old >> 32) << 16) | (old & 0xffffu));
+          }
+        }
+      }
+    }
+    __syncthreads();
+    for (int d = tid; d < R; d += nt) {
+      const unsigned long long add = s_cnt[d];
+      s_base[d] = add ? atomicAdd(&c.send_cnt[d], add) : 0ull;
+    }
+    __syncthreads();
+    // token phase B: append (primary, start, n) and the duplicate offsets to the
+    // destination rank's staging tables (region reserved for this source rank)
+    if (tok_active) {
+      const int base = tid * K;
+      for (int k = 0; k < K; ++k) {
+        const int p = s_pos[base + k];
+        if (p < 0) continue;
+        const int d = s_dest[base + k];
+        const unsigned long long b = s_base[d];
+        const int gi = (int)(b >> 32) + (p >> 16);
+        const int li = (int)(b & 0xffffffffu) + (p & 0xffff);
+        int* grp = (int*)peer_ptr(c, d, c.off_dupgroups) + ((size_t)c.rank * c.dup_group_cap + gi) * 3;
+        int* lof = (int*)peer_ptr(c, d, c.off_duploffs) + (size_t)c.rank * c.dup_loff_cap + li;
+        int n = 0;
+        for (int k2 = k + 1; k2 < K; ++k2)
+          if (s_dest[base + k2] == d) lof[n++] = s_raw[base + k2] - d * NvS;
+        grp[0] = s_raw[base + k] - d * NvS; grp[1] = li; grp[2] = n;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace mep
+
+extern "C" int mep_launch_planning(int nv, const MepRankCtx* const* ctxs, const mep::PlanArgs* args,
+                                   int num_sms, int E, cudaStream_t stream) {
+  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "planning: nv=%d out of range", nv);
+  MepCtxPack P = {}; mep::PlanArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  const size_t smem = (E <= mep::kSmemECap ? (size_t)E : 1) * sizeof(int);
+  return mep::launch_cooperative(mep::planning_kernel, dim3(num_sms, nv), dim3(mep::kPlanThreads), smem,
+                                 stream, false, P, A);
+}

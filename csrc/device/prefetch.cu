@@ -1,0 +1,87 @@
+// prefetch_weight: owner-push of redundant experts' weights into the peers' prefetch slots.
+//
+// Counterpart of the reference's PrefetchKernel (moonep/prefetch.py:45-470): one launch
+// copies up to six tensors (gate/up/down and optionally their block scales) of every local
+// expert that the plan placed in some rank's slot (experts_to_copy[d, b] in this rank's id
+// range) to pool[d, b]. Expert payloads are contiguous, so the copy is 1-D: 32 KB chunks are
+// dealt round-robin to the CTAs and moved with 16-byte local loads and 16-byte peer stores
+// (four per thread in flight) -- no TMA touches peer memory. Dtype-agnostic (bytes).
+// Ends with a cross-rank barrier: on return every rank's slots are complete.
+#include "prims.cuh"
+#include "../host/launch.h"
+
+namespace mep {
+
+struct CopyTensor {
+  const char* local;          // [epn, expert_bytes]
+  char* pool;                 // rank 0's slot 0; slot (d, b) = pool + d*rank_stride + b*expert_bytes
+  int64_t expert_bytes;
+  int64_t rank_stride;
+};
+struct PrefetchArgs {
+  const int32_t* etc;         // plan.experts_to_copy [R, epn]
+  int32_t ntensors;
+  int32_t pad;
+  CopyTensor t[6];
+};
+struct PrefetchArgsPack { PrefetchArgs a[MEP_MAX_VRANKS]; };
+
+constexpr int kCopyThreads = 512;
+constexpr int64_t kChunk = 32768;
+
+__global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P, PrefetchArgsPack A) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const PrefetchArgs& a = A.a[blockIdx.y];
+  extern __shared__ int s_list[];
+  __shared__ int s_n;
+  const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x;
+  const int R = c.R, epn = c.epn, lo = c.rank * epn;
+
+  if (tid == 0) s_n = 0;
+  __syncthreads();
+  for (int i = tid; i < R * epn; i += nt) {
+    const int e = a.etc[i];
+    if (e >= lo && e < lo + epn && i / epn != c.rank) s_list[atomicAdd(&s_n, 1)] = i;
+  }
+  __syncthreads();
+  const int nslots = s_n;
+
+  int64_t chunks_per_slot = 0;
+  for (int t = 0; t < a.ntensors; ++t) chunks_per_slot += (a.t[t].expert_bytes + kChunk - 1) / kChunk;
+  const int64_t total = (int64_t)nslots * chunks_per_slot;
+  for (int64_t u = blockIdx.x; u < total; u += nb) {
+    const int si = (int)(u / chunks_per_slot);
+    int64_t ck = u - (int64_t)si * chunks_per_slot;
+    int t = 0;
+    for (;; ++t) { const int64_t n = (a.t[t].expert_bytes + kChunk - 1) / kChunk; if (ck < n) break; ck -= n; }
+    const CopyTensor& T = a.t[t];
+    const int idx = s_list[si], d = idx / epn, b = idx - d * epn, le = a.etc[idx] - lo;
+    const int64_t beg = ck * kChunk;
+    const int64_t len = (T.expert_bytes - beg) < kChunk ? (T.expert_bytes - beg) : kChunk;
+    const char* src = T.local + (int64_t)le * T.expert_bytes + beg;
+    char* dstp = T.pool + (int64_t)d * T.rank_stride + (int64_t)b * T.expert_bytes + beg;
+    const int nvec = (int)(len >> 4);
+    for (int v0 = 0; v0 < nvec; v0 += 4 * nt) {
+      int4 x[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) x[j] = ld_nc_v4(src + (size_t)v * 16); }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) st_na_v4(dstp + (size_t)v * 16, x[j]); }
+    }
+    for (int64_t i = ((int64_t)nvec << 4) + tid; i < len; i += nt) dstp[i] = src[i];   // ragged tail
+  }
+  cross_rank_barrier(c, nb, 1, MEP_K_PREFETCH, 10);
+}
+
+}  // namespace mep
+
+extern "C" int mep_launch_prefetch(int nv, const MepRankCtx* const* ctxs, const mep::PrefetchArgs* args,
+                                   int num_sms, int R, int epn, cudaStream_t stream) {
+  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "prefetch: nv=%d out of range", nv);
+  MepCtxPack P = {}; mep::PrefetchArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  const size_t smem = (size_t)R * epn * sizeof(int);
+  MEP_REQUIRE(smem <= 160 * 1024, "prefetch: R*epn=%d exceeds the slot-list capacity", R * epn);
+  return mep::launch_cooperative(mep::prefetch_kernel, dim3(num_sms, nv), dim3(mep::kCopyThreads), smem,
+                                 stream, false, P, A);
+}

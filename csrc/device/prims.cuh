@@ -1,0 +1,217 @@
+// Device primitives: bounded waits, software grid barrier, cross-rank barrier,
+// peer-memory addressing, bulk-copy and mbarrier wrappers.
+//
+// Behavioural counterpart of the reference's moonep/_common.py (grid_sync :249-271,
+// cross_rank_barrier :274-346, bulk copies :414-459) with two deliberate differences:
+//  * every wait is bounded by a wall-clock budget (%globaltimer); on expiry the waiter
+//    records the site in MepStatus and the kernel returns -- it never traps;
+//  * cross-rank flags are monotone epochs (one slot per peer) instead of +/-1 counters,
+//    so a barrier needs no reset and a late or repeated arrival cannot corrupt it.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../mep_types.h"
+
+namespace mep {
+
+// ---------------------------------------------------------------- memory-model wrappers
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v; asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t atom_add_release_gpu(uint32_t* p, uint32_t v) {
+  uint32_t old; asm volatile("atom.add.release.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory"); return old;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
+}
+__device__ __forceinline__ uint32_t lanemask_lt() {
+  uint32_t m; asm volatile("mov.u32 %0, %%lanemask_lt;" : "=r"(m)); return m;
+}
+// 16-byte accesses that bypass L1 allocation (streaming payloads, peer memory)
+__device__ __forceinline__ int4 ld_nc_v4(const void* p) {
+  int4 v; asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)); return v;
+}
+// peer data that other GPUs may have just written: weak load through L2, no L1 allocation
+__device__ __forceinline__ int4 ld_peer_v4(const void* p) {
+  int4 v; asm volatile("ld.global.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ void st_v4(void* p, int4 v) {
+  asm volatile("st.global.v4.s32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_na_v4(void* p, int4 v) {
+  asm volatile("st.global.L1::no_allocate.v4.s32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// ---------------------------------------------------------------- peer addressing
+__device__ __forceinline__ char* peer_ptr(const MepRankCtx& c, int r, int64_t off) {
+  return c.heap_base + (int64_t)r * c.chunk_stride + off;
+}
+
+// ---------------------------------------------------------------- status
+__device__ __forceinline__ void report(const MepRankCtx& c, int code, int kernel, int site,
+                                       int peer, uint32_t observed, uint32_t expected) {
+  MepStatus* s = c.status;
+  if (atomicCAS(&s->code, 0, code) == 0) {
+    s->kernel = kernel; s->site = site; s->rank = c.rank; s->peer = peer;
+    s->observed = observed; s->expected = expected;
+    __threadfence();
+  }
+}
+__device__ __forceinline__ bool aborted(const MepRankCtx& c) {
+  return *(volatile int32_t*)&c.status->code != 0;
+}
+
+// Spin helper: `cond()` is polled; every 64 polls the clock and the abort word are
+// checked. Returns false when the budget ran out or another waiter already failed.
+template <class Cond>
+__device__ __forceinline__ bool bounded_wait(const MepRankCtx& c, Cond cond) {
+  if (cond()) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) { if (cond()) return true; }
+    if (aborted(c)) return false;
+    if (globaltimer_ns() - t0 > c.wait_budget_ns) return false;
+    __nanosleep(32);
+  }
+}
+
+// ---------------------------------------------------------------- grid barrier
+// All `nblocks` CTAs of one rank (blockIdx.x in [0, nblocks)) must call it; CTAs must be
+// co-resident (cooperative launch). Self-resetting: CTA 0 adds 0x80000000-(n-1), the
+// others add 1, so the top bit flips exactly when everyone has arrived.
+// `sys` makes this CTA's earlier writes to peer memory visible system-wide first.
+__device__ __forceinline__ bool grid_sync(const MepRankCtx& c, int nblocks, int kernel, int site, bool sys = false) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (sys) __threadfence_system(); else __threadfence();
+    bool ok = true;
+    if (nblocks > 1) {
+      const uint32_t inc = (blockIdx.x == 0) ? (0x80000000u - (uint32_t)(nblocks - 1)) : 1u;
+      const uint32_t old = atom_add_release_gpu(c.grid_bar, inc);
+      uint32_t now = 0;
+      ok = bounded_wait(c, [&] { now = ld_acquire_gpu(c.grid_bar); return ((now ^ old) & 0x80000000u) != 0; });
+      if (!ok) report(c, MEP_ERR_GRID_SYNC_TIMEOUT, kernel, site, blockIdx.x, now, old);
+    }
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+// ---------------------------------------------------------------- cross-rank barrier
+// Executed by ONE CTA of the rank (all its threads). Flag row `row` of every rank holds
+// one epoch word per peer; arrival = release-store of the new epoch into slot [my rank]
+// of every peer; completion = every slot of my row has reached the epoch.
+__device__ __forceinline__ bool cross_rank_arrive_wait(const MepRankCtx& c, int row, int kernel, int site) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) { s_epoch = c.epoch[row] + 1; c.epoch[row] = s_epoch; s_fail = 0; }
+  __syncthreads();
+  const uint32_t ep = s_epoch;
+  for (int p = threadIdx.x; p < c.R; p += blockDim.x) {
+    uint32_t* slot = (uint32_t*)peer_ptr(c, p, c.off_bar) + row * MEP_MAX_RANKS + c.rank;
+    st_release_sys(slot, ep);
+  }
+  for (int p = threadIdx.x; p < c.R; p += blockDim.x) {
+    const uint32_t* slot = (const uint32_t*)peer_ptr(c, c.rank, c.off_bar) + row * MEP_MAX_RANKS + p;
+    uint32_t seen = 0;
+    bool ok = bounded_wait(c, [&] { seen = ld_acquire_sys(slot); return (int32_t)(seen - ep) >= 0; });
+    if (!ok) { report(c, MEP_ERR_PEER_TIMEOUT, kernel, site, p, seen, ep); s_fail = 1; }
+  }
+  __syncthreads();
+  return s_fail == 0;
+}
+
+// Full barrier for every CTA of the rank: local grid barrier (publishing peer writes),
+// CTA 0 exchanges epochs with the peers, second grid barrier releases the rest.
+__device__ __forceinline__ bool cross_rank_barrier(const MepRankCtx& c, int nblocks, int row, int kernel, int site) {
+  if (!grid_sync(c, nblocks, kernel, site, true)) return false;
+  if (blockIdx.x == 0) {
+    if (c.R > 1) cross_rank_arrive_wait(c, row, kernel, site + 1);
+  }
+  if (!grid_sync(c, nblocks, kernel, site + 2, false)) return false;
+  return !aborted(c);
+}
+
+// ---------------------------------------------------------------- mbarrier + bulk copies (local TMA engine)
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded mbarrier wait without a rank context (budget in polls; ~a few seconds).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t budget_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) { if (mbar_try_wait(bar, parity)) return true; }
+    if (globaltimer_ns() - t0 > budget_ns) return false;
+  }
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// 1-D bulk copy global -> this CTA's shared memory, completion counted on `bar`.
+// Source must be LOCAL device memory. Size and both addresses multiples of 16 bytes.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :: "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// 1-D bulk copy shared -> global (local or peer memory), tracked by bulk groups.
+__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               :: "l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" :: "n"(N) : "memory"); }
+
+// ---------------------------------------------------------------- warp helpers
+__device__ __forceinline__ int warp_incl_scan(int v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += t; }
+  return v;
+}
+__device__ __forceinline__ long long warp_max64(long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { long long t = __shfl_xor_sync(0xffffffffu, v, o); v = t > v ? t : v; }
+  return v;
+}
+// key for "largest value, lowest index wins ties"
+__device__ __forceinline__ long long argmax_key(int value, int index) {
+  return ((long long)value << 32) | (uint32_t)(0x7fffffff - index);
+}
+__device__ __forceinline__ int key_index(long long key) { return 0x7fffffff - (int)(uint32_t)(key & 0xffffffffu); }
+__device__ __forceinline__ int key_value(long long key) { return (int)(key >> 32); }
+
+}  // namespace mep

@@ -1,0 +1,68 @@
+// Plain-C structs shared by the host launchers, the device kernels and the
+// Python ctypes layer (moonep_b200/_native.py mirrors them field by field).
+#pragma once
+#include <stdint.h>
+
+#define MEP_MAX_RANKS 128   // rank ids fit 7 bits (reference: moonep/constants.py:7)
+#define MEP_MAX_VRANKS 8    // ranks one launch may host on a single GPU (emulation)
+#define MEP_MAX_TOPK 32
+#define MEP_BAR_ROWS 4      // independent cross-rank flag rows per Buffer
+
+// Error codes written to MepStatus.code by device code; 0 means "no error".
+enum MepError {
+  MEP_OK = 0,
+  MEP_ERR_GRID_SYNC_TIMEOUT = 1,   // a CTA of this rank never arrived
+  MEP_ERR_PEER_TIMEOUT = 2,        // a peer rank never arrived at a cross-rank barrier
+  MEP_ERR_BOUNDS = 3,              // checked build: computed index out of range
+  MEP_ERR_FLAG_TIMEOUT = 4,        // a ready flag never reached its expected value
+  MEP_ERR_MBAR_TIMEOUT = 5,        // an mbarrier phase never completed
+};
+
+enum MepKernelId {
+  MEP_K_SYNC = 1, MEP_K_PLANNING = 2, MEP_K_DISPATCH = 3, MEP_K_EXPAND = 4,
+  MEP_K_DUP_REDUCE = 5, MEP_K_COMBINE = 6, MEP_K_PREFETCH = 7, MEP_K_GRAD_REDUCE = 8,
+  MEP_K_GEMM = 9, MEP_K_WAIT_PROBE = 10,
+};
+
+// First failure recorded by any kernel of a Buffer. Lives in device memory; the host
+// copies it back lazily. All-zero == healthy.
+typedef struct MepStatus {
+  int32_t code;       // MepError
+  int32_t kernel;     // MepKernelId
+  int32_t site;       // which wait inside the kernel
+  int32_t rank;
+  int32_t peer;       // peer rank (cross-rank barrier) or CTA index (grid sync)
+  uint32_t observed;
+  uint32_t expected;
+  int32_t reserved;
+} MepStatus;
+
+// Per-rank constant context. One instance per rank in device memory, written once
+// when the Buffer is created.
+typedef struct MepRankCtx {
+  int32_t rank, R, S, H, K, E, epn, N, NvS, token_padding;
+  int32_t vblock_entries, num_vblocks, num_sms, checked;
+  // symmetric heap: rank r's chunk is heap_base + r * chunk_stride (all ranks mapped)
+  char* heap_base;
+  int64_t chunk_stride;
+  int64_t off_hidden, off_weights, off_tpe, off_bar, off_dupcnt, off_dupgroups,
+      off_duploffs, off_ready;
+  int64_t dup_group_cap, dup_loff_cap;   // per-source capacity of the staging tables
+  // local scratch (ordinary device memory)
+  uint32_t* grid_bar;      // [1] software grid barrier word
+  uint32_t* epoch;         // [MEP_BAR_ROWS] cross-rank barrier epochs
+  int32_t* hist;           // [num_vblocks, E]
+  int32_t* count;          // [E]   tokens per expert over the whole group
+  int32_t* tpe_prefix;     // [E]   tokens of expert e on ranks < rank
+  int32_t* remaining;      // [E]
+  int32_t* alloc;          // [E, R]
+  int32_t* alloc_cumsum;   // [E, R]
+  int32_t* expert_off;     // [R, E]
+  int32_t* etc_all;        // [R, epn] experts_to_copy of every rank
+  int32_t* stats_all;      // [R, 2]
+  unsigned long long* send_cnt;  // [R] (groups<<32 | loffs) emitted to each destination
+  MepStatus* status;
+  uint64_t wait_budget_ns;
+} MepRankCtx;
+
+typedef struct MepCtxPack { const MepRankCtx* ctx[MEP_MAX_VRANKS]; } MepCtxPack;

@@ -1,0 +1,125 @@
+"""ctypes binding of ``libmoonep_b200.so`` (plain ``extern "C"`` ABI).
+
+The structs mirror ``csrc/mep_types.h`` and the per-kernel argument structs field by
+field.  Every native function returns 0 on success; on failure ``check`` raises
+``MoonEPNativeError`` with the library's thread-local message.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch  # noqa: F401  (loads the CUDA runtime the library links against)
+
+MAX_RANKS = 128
+MAX_VRANKS = 8
+BAR_ROWS = 4
+
+_LIB = None
+
+
+class MoonEPNativeError(RuntimeError):
+    pass
+
+
+class MepStatus(C.Structure):
+    _fields_ = [("code", C.c_int32), ("kernel", C.c_int32), ("site", C.c_int32), ("rank", C.c_int32),
+                ("peer", C.c_int32), ("observed", C.c_uint32), ("expected", C.c_uint32), ("reserved", C.c_int32)]
+
+
+class MepRankCtx(C.Structure):
+    _fields_ = (
+        [(n, C.c_int32) for n in ("rank", "R", "S", "H", "K", "E", "epn", "N", "NvS", "token_padding",
+                                  "vblock_entries", "num_vblocks", "num_sms", "checked")]
+        + [("heap_base", C.c_void_p), ("chunk_stride", C.c_int64)]
+        + [(n, C.c_int64) for n in ("off_hidden", "off_weights", "off_tpe", "off_bar", "off_dupcnt",
+                                    "off_dupgroups", "off_duploffs", "off_ready",
+                                    "dup_group_cap", "dup_loff_cap")]
+        + [(n, C.c_void_p) for n in ("grid_bar", "epoch", "hist", "count", "tpe_prefix", "remaining", "alloc",
+                                     "alloc_cumsum", "expert_off", "etc_all", "stats_all", "send_cnt", "status")]
+        + [("wait_budget_ns", C.c_uint64)]
+    )
+
+
+class PlanArgs(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("topk", "tpe", "dst", "cu_seqlens", "experts_to_copy",
+                                          "zero_fill", "remote_stats")]
+
+
+class DispatchArgs(C.Structure):
+    _fields_ = [("hidden", C.c_void_p), ("weights", C.c_void_p), ("dst", C.c_void_p), ("zero_fill", C.c_void_p),
+                ("fresh", C.c_int32), ("entry_barrier", C.c_int32)]
+
+
+class DupFinalizeArgs(C.Structure):
+    _fields_ = [("dup_groups", C.c_void_p), ("dup_loffs", C.c_void_p), ("dup_counts", C.c_void_p)]
+
+
+class DupArgs(C.Structure):
+    _fields_ = [("buf", C.c_void_p), ("dup_groups", C.c_void_p), ("dup_loffs", C.c_void_p), ("dup_counts", C.c_void_p)]
+
+
+class CombineArgs(C.Structure):
+    _fields_ = [("dst", C.c_void_p), ("out", C.c_void_p), ("out_weights", C.c_void_p), ("entry_barrier", C.c_int32)]
+
+
+class CopyTensor(C.Structure):
+    _fields_ = [("local", C.c_void_p), ("pool", C.c_void_p), ("expert_bytes", C.c_int64), ("rank_stride", C.c_int64)]
+
+
+class PrefetchArgs(C.Structure):
+    _fields_ = [("etc", C.c_void_p), ("ntensors", C.c_int32), ("pad", C.c_int32), ("t", CopyTensor * 6)]
+
+
+class ReduceTensor(C.Structure):
+    _fields_ = [("local", C.c_void_p), ("pool", C.c_void_p), ("expert_elems", C.c_int64), ("rank_stride", C.c_int64)]
+
+
+class GradReduceArgs(C.Structure):
+    _fields_ = [("etc", C.c_void_p), ("ntensors", C.c_int32), ("pad", C.c_int32), ("t", ReduceTensor * 3)]
+
+
+def lib_path() -> Path:
+    return Path(__file__).resolve().parent / "_lib" / "libmoonep_b200.so"
+
+
+def load(build_if_missing: bool = True):
+    """Load (building first if the library is missing or older than its sources and nvcc exists)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    from . import _build
+    p = lib_path()
+    if build_if_missing and _build.nvcc_path() is not None and os.environ.get("MOONEP_NO_AUTOBUILD") != "1":
+        if _build.is_stale():
+            _build.build()
+    if not p.exists():
+        raise MoonEPNativeError(
+            f"{p} is missing: build it with `python -m moonep_b200._build` (needs nvcc); "
+            "the CUDA kernels are the only implementation of the device ops")
+    lib = C.CDLL(str(p), mode=C.RTLD_GLOBAL)
+    lib.mep_last_error.restype = C.c_char_p
+    _LIB = lib
+    return lib
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc != 0:
+        msg = load().mep_last_error().decode(errors="replace")
+        raise MoonEPNativeError(f"{what}: {msg}" if what else msg)
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a tensor (None stays None)."""
+    return None if t is None else t.data_ptr()
+
+
+def ctx_array(ctx_ptrs):
+    arr = (C.c_void_p * len(ctx_ptrs))(*ctx_ptrs)
+    return arr
+
+
+def cur_stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)

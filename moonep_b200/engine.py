@@ -1,0 +1,253 @@
+"""Per-rank device state and thin launch wrappers around the native kernels.
+
+Every wrapper takes LISTS (one entry per rank hosted by this process): a normal
+``Buffer`` passes lists of length one; the single-GPU ``LocalCluster`` passes all R ranks
+so that one cooperative launch runs every rank's CTAs side by side (blockIdx.y = rank)
+and the cross-rank barriers work on one device.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+
+import torch
+
+from . import _native
+from ._native import (MepRankCtx, PlanArgs, DispatchArgs, DupFinalizeArgs, DupArgs, CombineArgs,
+                      PrefetchArgs, GradReduceArgs, ptr)
+from .geometry import Geometry
+from .plan import MoonEPCommPlan
+
+ERROR_NAMES = {1: "grid barrier timed out (a CTA never arrived)",
+               2: "cross-rank barrier timed out (a peer never arrived)",
+               3: "index out of range",
+               4: "ready flag never reached its expected value",
+               5: "mbarrier phase never completed"}
+KERNEL_NAMES = {1: "rank_sync", 2: "planning", 3: "dispatch", 4: "dup_expand", 5: "dup_reduce", 6: "combine",
+                7: "prefetch", 8: "grad_reduce", 9: "grouped_gemm", 10: "wait_probe"}
+
+
+class MoonEPTimeout(RuntimeError):
+    """A bounded device-side wait expired (or a checked index was out of range)."""
+
+    def __init__(self, status: dict):
+        self.status = status
+        super().__init__(
+            f"rank {status['rank']}: {KERNEL_NAMES.get(status['kernel'], status['kernel'])} kernel, site "
+            f"{status['site']}: {ERROR_NAMES.get(status['code'], status['code'])} "
+            f"(peer/cta {status['peer']}, observed {status['observed']}, expected {status['expected']})")
+
+
+def wait_budget_ns() -> int:
+    ms = float(os.environ.get("MOONEP_WAIT_BUDGET_MS", "2000"))
+    return max(1, int(ms * 1e6))
+
+
+@dataclass
+class RankState:
+    geo: Geometry
+    rank: int
+    heap: object
+    device: torch.device
+    ctx_host: MepRankCtx = None
+    ctx_dev: torch.Tensor = None
+    scratch: dict = field(default_factory=dict)
+    hidden_local: torch.Tensor = None     # [NvS, H] bf16 view of this rank's shard
+    weights_local: torch.Tensor = None    # [NvS] fp32 view
+    status: torch.Tensor = None           # int32[8] device
+
+    @property
+    def ctx_ptr(self) -> int:
+        return self.ctx_dev.data_ptr()
+
+
+def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | None = None) -> RankState:
+    dev = torch.device(device)
+    st = RankState(geo, rank, heap, dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    R, E, epn = geo.R, geo.E, geo.epn
+    s = st.scratch
+    s["grid_bar"] = torch.zeros(4, **i32)
+    s["epoch"] = torch.zeros(_native.BAR_ROWS, **i32)
+    s["hist"] = torch.zeros(geo.num_vblocks * E, **i32)
+    s["count"] = torch.zeros(E, **i32)
+    s["tpe_prefix"] = torch.zeros(E, **i32)
+    s["remaining"] = torch.zeros(E, **i32)
+    s["alloc"] = torch.zeros(E * R, **i32)
+    s["alloc_cumsum"] = torch.zeros(E * R, **i32)
+    s["expert_off"] = torch.zeros(R * E, **i32)
+    s["etc_all"] = torch.zeros(R * epn, **i32)
+    s["stats_all"] = torch.zeros(R * 2, **i32)
+    s["send_cnt"] = torch.zeros(R, dtype=torch.int64, device=dev)
+    st.status = torch.zeros(8, **i32)
+
+    c = MepRankCtx()
+    c.rank, c.R, c.S, c.H, c.K, c.E, c.epn, c.N, c.NvS = rank, R, geo.S, geo.H, geo.K, E, epn, geo.N, geo.NvS
+    c.token_padding, c.vblock_entries, c.num_vblocks = geo.token_padding, geo.vblock_entries, geo.num_vblocks
+    c.num_sms = geo.num_sms
+    c.checked = 1 if os.environ.get("MOONEP_CHECKED") == "1" else 0
+    c.heap_base, c.chunk_stride = heap.base, heap.chunk_bytes
+    for name in ("off_hidden", "off_weights", "off_tpe", "off_bar", "off_dupcnt", "off_dupgroups",
+                 "off_duploffs", "off_ready"):
+        setattr(c, name, getattr(geo, name))
+    c.dup_group_cap, c.dup_loff_cap = geo.dup_group_cap, geo.dup_loff_cap
+    for name in ("grid_bar", "epoch", "hist", "count", "tpe_prefix", "remaining", "alloc", "alloc_cumsum",
+                 "expert_off", "etc_all", "stats_all", "send_cnt"):
+        setattr(c, name, s[name].data_ptr())
+    c.status = st.status.data_ptr()
+    c.wait_budget_ns = wait_budget_ns() if budget_ns is None else budget_ns
+    st.ctx_host = c
+    raw = bytes(c)
+    st.ctx_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
+    st.hidden_local = heap.view(rank, geo.off_hidden, (geo.NvS, geo.H), torch.bfloat16)
+    st.weights_local = heap.view(rank, geo.off_weights, (geo.NvS,), torch.float32)
+    return st
+
+
+def read_status(st: RankState) -> dict | None:
+    v = st.status.cpu().tolist()
+    if v[0] == 0:
+        return None
+    return dict(code=v[0], kernel=v[1], site=v[2], rank=v[3], peer=v[4],
+                observed=v[5] & 0xFFFFFFFF, expected=v[6] & 0xFFFFFFFF)
+
+
+def _pack(states):
+    return _native.ctx_array([s.ctx_ptr for s in states])
+
+
+def allocate_plan(st: RankState):
+    """Plan-owned tensors plus cu_seqlens for one rank (reference: planning.py:1168-1215)."""
+    g = st.geo
+    i32 = dict(dtype=torch.int32, device=st.device)
+    plan = MoonEPCommPlan(
+        dst=torch.empty(g.N, **i32),
+        experts_to_copy=torch.empty(g.R, g.epn, **i32),
+        zero_fill_ranges=torch.empty(2 * g.epn, 2, **i32),
+        remote_stats=torch.empty(2, **i32),
+        N=g.N, R=g.R, E=g.E, NvS=g.NvS, K=g.K,
+        dup_groups=torch.empty(g.NvS, 3, **i32),
+        dup_loffs=torch.empty(g.NvS, **i32),
+        dup_counts=torch.zeros(2, **i32),
+    )
+    cu = torch.empty(2 * g.epn, **i32)
+    return plan, cu
+
+
+def launch_planning(states, topk_list, tpe_list, plans, cu_list):
+    lib = _native.load()
+    n = len(states)
+    args = (PlanArgs * n)()
+    for i in range(n):
+        p = plans[i]
+        args[i] = PlanArgs(ptr(topk_list[i]), ptr(tpe_list[i]), ptr(p.dst), ptr(cu_list[i]),
+                           ptr(p.experts_to_copy), ptr(p.zero_fill_ranges), ptr(p.remote_stats))
+    g = states[0].geo
+    _native.check(lib.mep_launch_planning(n, _pack(states), args, g.num_sms, g.E, _native.cur_stream()), "planning")
+
+
+def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry_barrier: bool):
+    lib = _native.load()
+    n = len(states)
+    args = (DispatchArgs * n)()
+    for i in range(n):
+        w = weights_list[i] if weights_list is not None else None
+        args[i] = DispatchArgs(ptr(hidden_list[i]), ptr(w), ptr(plans[i].dst), ptr(plans[i].zero_fill_ranges),
+                               1 if fresh else 0, 1 if entry_barrier else 0)
+    g = states[0].geo
+    _native.check(lib.mep_launch_dispatch(n, _pack(states), args, g.num_sms, g.H, _native.cur_stream()), "dispatch")
+
+
+def launch_dup_finalize(states, plans):
+    lib = _native.load()
+    n = len(states)
+    args = (DupFinalizeArgs * n)()
+    for i in range(n):
+        args[i] = DupFinalizeArgs(ptr(plans[i].dup_groups), ptr(plans[i].dup_loffs), ptr(plans[i].dup_counts))
+    _native.check(lib.mep_launch_dup_finalize(n, _pack(states), args, _native.cur_stream()), "dup_finalize")
+
+
+def _dup_args(states, bufs, plans):
+    n = len(states)
+    args = (DupArgs * n)()
+    for i in range(n):
+        args[i] = DupArgs(ptr(bufs[i]), ptr(plans[i].dup_groups), ptr(plans[i].dup_loffs), ptr(plans[i].dup_counts))
+    return args
+
+
+def launch_dup_expand(states, bufs, plans, num_blocks: int):
+    lib = _native.load()
+    _native.check(lib.mep_launch_dup_expand(len(states), _pack(states), _dup_args(states, bufs, plans),
+                                            num_blocks, _native.cur_stream()), "dup_expand")
+
+
+def launch_dup_reduce(states, bufs, plans, num_blocks: int):
+    lib = _native.load()
+    _native.check(lib.mep_launch_dup_reduce(len(states), _pack(states), _dup_args(states, bufs, plans),
+                                            num_blocks, _native.cur_stream()), "dup_reduce")
+
+
+def launch_combine(states, plans, outs, out_weights, entry_barrier: bool = True):
+    lib = _native.load()
+    n = len(states)
+    args = (CombineArgs * n)()
+    for i in range(n):
+        ow = out_weights[i] if out_weights is not None else None
+        args[i] = CombineArgs(ptr(plans[i].dst), ptr(outs[i]), ptr(ow), 1 if entry_barrier else 0)
+    _native.check(lib.mep_launch_combine(n, _pack(states), args, states[0].geo.num_sms, _native.cur_stream()), "combine")
+
+
+def launch_rank_sync(states):
+    lib = _native.load()
+    _native.check(lib.mep_launch_rank_sync(len(states), _pack(states), _native.cur_stream()), "rank_sync")
+
+
+def _rank_stride_bytes(pool: torch.Tensor) -> int:
+    return int(pool.stride(0)) * pool.element_size()
+
+
+def launch_prefetch(states, etc_list, tensor_pairs_list):
+    """``tensor_pairs_list[i]`` = sequence of up to six ``(local[epn,...], pool[R,epn,...])``."""
+    lib = _native.load()
+    n = len(states)
+    args = (PrefetchArgs * n)()
+    for i in range(n):
+        a = PrefetchArgs()
+        a.etc = ptr(etc_list[i])
+        pairs = tensor_pairs_list[i]
+        a.ntensors = len(pairs)
+        for j, (local, pool) in enumerate(pairs):
+            a.t[j].local = local.data_ptr()
+            a.t[j].pool = pool.data_ptr()
+            a.t[j].expert_bytes = local[0].numel() * local.element_size()
+            a.t[j].rank_stride = _rank_stride_bytes(pool)
+        args[i] = a
+    g = states[0].geo
+    _native.check(lib.mep_launch_prefetch(n, _pack(states), args, g.num_sms, g.R, g.epn, _native.cur_stream()), "prefetch")
+
+
+def launch_grad_reduce(states, etc_list, tensor_pairs_list):
+    lib = _native.load()
+    n = len(states)
+    args = (GradReduceArgs * n)()
+    for i in range(n):
+        a = GradReduceArgs()
+        a.etc = ptr(etc_list[i])
+        pairs = tensor_pairs_list[i]
+        a.ntensors = len(pairs)
+        for j, (local, pool) in enumerate(pairs):
+            a.t[j].local = local.data_ptr()
+            a.t[j].pool = pool.data_ptr()
+            a.t[j].expert_elems = local[0].numel()
+            a.t[j].rank_stride = _rank_stride_bytes(pool)
+        args[i] = a
+    g = states[0].geo
+    _native.check(lib.mep_launch_grad_reduce(n, _pack(states), args, g.num_sms, g.R, g.epn, _native.cur_stream()), "grad_reduce")
+
+
+def launch_wait_probe(st: RankState, flag: torch.Tensor, expected: int):
+    lib = _native.load()
+    _native.check(lib.mep_launch_wait_probe(C.c_void_p(st.ctx_ptr), C.c_void_p(flag.data_ptr()),
+                                            C.c_uint32(expected), _native.cur_stream()), "wait_probe")

@@ -49,6 +49,8 @@ class Geometry:
     off_dupgroups: int = 0
     off_duploffs: int = 0
     off_ready: int = 0
+    dup_group_cap: int = 0    # staging capacity per source rank (groups)
+    dup_loff_cap: int = 0     # staging capacity per source rank (duplicate offsets)
     chunk_bytes: int = 0      # before granularity padding
 
     @staticmethod
@@ -84,11 +86,14 @@ class Geometry:
         o_weights = take(NvS * 4)
         o_tpe = take(R * E * 4)
         o_bar = take(4 * MAX_RANKS * 4)       # 4 independent flag rows
-        o_dupcnt = take(64)
-        o_dupgroups = take(NvS * 3 * 4)
-        o_duploffs = take(NvS * 4)
+        # duplicate-group staging: one region per SOURCE rank, so senders never contend.
+        # A source can emit at most N/2 groups and N duplicate offsets to one destination.
+        gcap, lcap = N // 2 + 1, N
+        o_dupcnt = take(R * 2 * 4)
+        o_dupgroups = take(R * gcap * 3 * 4)
+        o_duploffs = take(R * lcap * 4)
         o_ready = take(4 * (2 * epn + 8))
         chunk = align_up(off, 1024)
         return Geometry(S, H, K, E, R, token_padding, num_sms, epn, N, NvS, vb, nvb,
                         o_hidden, o_weights, o_tpe, o_bar, o_dupcnt, o_dupgroups,
-                        o_duploffs, o_ready, chunk)
+                        o_duploffs, o_ready, gcap, lcap, chunk)

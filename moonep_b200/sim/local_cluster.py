@@ -1,0 +1,64 @@
+"""All R ranks of an EP group hosted by ONE process on ONE GPU.
+
+Every native kernel takes a list of rank contexts and runs them as the y-dimension of a
+single cooperative launch, so cross-rank barriers, peer stores and peer loads behave as on R
+GPUs (peer memory is simply another region of the same device).  This is how the multi-rank
+logic is tested when only one GPU is available; it is not a performance path.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import engine
+from ..api import OpsMixin
+from ..geometry import Geometry, MAX_VRANKS
+from ..parallel.symm import SymmetricHeap
+
+
+class LocalCluster(OpsMixin):
+    def __init__(self, S, H, K, E, R, num_sms=4, token_padding=128, device="cuda:0", num_sms_dedup=8,
+                 budget_ms: float | None = None):
+        assert 1 <= R <= MAX_VRANKS, f"LocalCluster hosts at most {MAX_VRANKS} ranks"
+        self.geo = Geometry.make(S, H, K, E, R, token_padding, num_sms)
+        self.device = torch.device(device)
+        self.heap = SymmetricHeap.local(R, self.geo.chunk_bytes, self.device)
+        bn = None if budget_ms is None else int(budget_ms * 1e6)
+        self._states = [engine.make_rank_state(self.geo, r, self.heap, self.device, bn) for r in range(R)]
+        self._num_sms_dedup = num_sms_dedup
+        self.R = R
+
+    def dispatch(self, hidden, weights=None, topk=None, tpe=None, plans=None, *, inter_rank_sync=True,
+                 zero_copy=False, router_weights_zero_copy=False):
+        return self._dispatch_lists(hidden, weights, topk, tpe, plans, inter_rank_sync=inter_rank_sync,
+                                    zero_copy=zero_copy, w_zero_copy=router_weights_zero_copy)
+
+    def combine(self, plans, hidden_nvsh, weights_nvs=None, *, inter_rank_sync=True, zero_copy=False,
+                router_weights_zero_copy=False):
+        return self._combine_lists(plans, hidden_nvsh, weights_nvs, inter_rank_sync=inter_rank_sync,
+                                   zero_copy=zero_copy, w_zero_copy=router_weights_zero_copy)
+
+    def prefetch(self, plans, pairs_list):
+        self._prefetch_lists(plans, pairs_list)
+
+    def reduce_grad(self, plans, pairs_list):
+        self._reduce_lists(plans, pairs_list)
+
+    def check(self):
+        for s in self._states:
+            st = engine.read_status(s)
+            if st is not None:
+                raise engine.MoonEPTimeout(st)
+
+    def make_pool(self, shape_per_rank, dtype, pad_elems=0):
+        """``[R, *shape]`` pool on this device with an optional gap between ranks."""
+        n = 1
+        for s in shape_per_rank:
+            n *= int(s)
+        stride = n + pad_elems
+        flat = torch.zeros(self.R * stride, dtype=dtype, device=self.device)
+        strides, acc = [], 1
+        for s in reversed(shape_per_rank):
+            strides.append(acc)
+            acc *= int(s)
+        return flat.as_strided((self.R, *shape_per_rank), [stride] + list(reversed(strides))), flat

@@ -1,0 +1,68 @@
+"""Host-only checks of argument validation (no GPU): num_sms is validated before any CUDA
+or process-group access, like the reference (tests/test_api_validation.py:8-86)."""
+import pytest
+
+from moonep_b200.api import validate_num_sms, num_sms_dedup_from_env
+from moonep_b200.geometry import Geometry
+
+
+def _boom():
+    raise AssertionError("device must not be queried for an invalid num_sms")
+
+
+@pytest.mark.parametrize("bad", [True, 1.5, "8", [4]])
+def test_num_sms_type(bad):
+    with pytest.raises(TypeError, match="num_sms must be a positive int"):
+        validate_num_sms(bad, _boom)
+
+
+@pytest.mark.parametrize("bad", [0, -3])
+def test_num_sms_range(bad):
+    with pytest.raises(ValueError, match="num_sms must be a positive int"):
+        validate_num_sms(bad, _boom)
+
+
+def test_num_sms_vs_device():
+    assert validate_num_sms(None, lambda: 148) == (32, 148)
+    assert validate_num_sms(None, lambda: 16) == (16, 16)
+    assert validate_num_sms(20, lambda: 148) == (20, 148)
+    with pytest.raises(ValueError, match="must not exceed the device SM count"):
+        validate_num_sms(200, lambda: 148)
+
+
+def test_buffer_rejects_bad_num_sms_before_cuda(monkeypatch):
+    import torch
+    from moonep_b200.api import Buffer
+    monkeypatch.setattr(torch.cuda, "current_device", _boom)
+    with pytest.raises(TypeError):
+        Buffer(8, 64, 2, 4, 1, num_sms="x")
+    with pytest.raises(ValueError):
+        Buffer(8, 64, 2, 4, 1, num_sms=0)
+
+
+def test_dedup_env(monkeypatch):
+    monkeypatch.delenv("MOONEP_NUM_SMS_DEDUP", raising=False)
+    assert num_sms_dedup_from_env(148) == 148
+    monkeypatch.setenv("MOONEP_NUM_SMS_DEDUP", "12")
+    assert num_sms_dedup_from_env(148) == 12
+    monkeypatch.setenv("MOONEP_NUM_SMS_DEDUP", "abc")
+    with pytest.raises(ValueError):
+        num_sms_dedup_from_env(148)
+    monkeypatch.setenv("MOONEP_NUM_SMS_DEDUP", "0")
+    with pytest.raises(ValueError):
+        num_sms_dedup_from_env(148)
+
+
+def test_geometry_limits():
+    g = Geometry.make(4096, 7168, 8, 256, 8, 128, 32)
+    assert g.NvS == 40960 and g.epn == 32 and g.N == 32768
+    with pytest.raises(AssertionError, match="divisible"):
+        Geometry.make(8, 64, 2, 5, 2)
+    with pytest.raises(AssertionError, match="K <= 32"):
+        Geometry.make(8, 64, 33, 64, 2)
+    with pytest.raises(AssertionError, match="R <= 128"):
+        Geometry.make(8, 64, 2, 256, 256)
+    with pytest.raises(AssertionError, match="multiple of 8"):
+        Geometry.make(8, 60, 2, 4, 2)
+    with pytest.raises(AssertionError, match="token_padding"):
+        Geometry.make(8, 64, 2, 4, 2, token_padding=0)

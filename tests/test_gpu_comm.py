@@ -1,0 +1,200 @@
+"""GPU tests of planning / dispatch / combine / prefetch / reduce_grad against the CPU oracle.
+All R ranks run on one GPU through LocalCluster (one cooperative launch hosts every rank)."""
+import numpy as np
+import pytest
+import torch
+
+from moonep_b200.sim import ops as simops
+
+pytestmark = pytest.mark.gpu
+
+from gpu_helpers import run_case, defined_rows  # noqa: E402
+
+CASES = [
+    # name, S, K, epn, H, R, num_sms, pad, routing
+    ("tiny_r1", 1, 1, 1, 64, 1, 1, 1, "random"),
+    ("r1_balanced", 128, 4, 4, 256, 1, 4, 16, "balanced"),
+    ("r2_random", 96, 4, 3, 128, 2, 3, 8, "random"),
+    ("r2_all_remote", 64, 2, 2, 128, 2, 2, 16, "all_remote"),
+    ("r4_single_expert", 40, 3, 2, 64, 4, 2, 8, "single_expert"),
+    ("r4_duplicate_topk", 33, 4, 3, 64, 4, 2, 4, "duplicate_topk"),
+    ("r4_all_local", 50, 4, 4, 64, 4, 3, 128, "all_local"),
+    ("r8_balanced", 256, 8, 8, 256, 8, 4, 128, "balanced"),
+    ("r8_biased", 256, 8, 8, 512, 8, 4, 128, "biased"),
+    ("r8_heavy", 300, 6, 5, 128, 8, 3, 32, "biased"),
+    ("r8_k32", 64, 32, 8, 64, 8, 2, 16, "random"),
+    ("r3_odd", 77, 5, 7, 72, 3, 5, 5, "random"),
+    ("r2_multi_vblock", 700, 8, 16, 64, 2, 2, 64, "biased"),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_dispatch_combine(case, cuda_device):
+    _, S, K, epn, H, R, num_sms, pad, kind = case
+    sigma = 5.0 if case[0] == "r8_heavy" else 1.0
+    cl, cp, plans, cus, hidden, weights, topk, tpe, oh, ow = run_case(S, K, epn, H, R, num_sms, pad, kind, sigma=sigma)
+    dev = cuda_device
+    # combine of small-integer payloads is exact: use value = (slot index mod 7) + 1 per row
+    ys = []
+    for d in range(R):
+        y = torch.zeros(cp.NvS, H, dtype=torch.bfloat16)
+        y[:] = ((torch.arange(cp.NvS) % 7) + 1)[:, None].to(torch.bfloat16)
+        ys.append(y)
+    outs, outw = cl.combine(plans, [y.to(dev) for y in ys], [w.to(dev) for w in ow])
+    torch.cuda.synchronize()
+    cl.check()
+    eo, ewk = simops.combine(cp, [y.float() for y in ys], [w.cpu().view(torch.int32).float() for w in ow])
+    for r in range(R):
+        assert torch.equal(outs[r].cpu().float(), eo[r].to(torch.bfloat16).float()), f"rank {r}: combine mismatch"
+        assert torch.equal(outw[r].cpu().view(torch.int32).float(), ewk[r]), f"rank {r}: gathered weights mismatch"
+        assert torch.equal(outw[r].cpu().view(torch.int32), weights[r].view(torch.int32)), "weights must round-trip bit-exactly"
+
+
+def test_combine_rounding(cuda_device):
+    """randn payloads: duplicates rounded once locally, then one final rounding (<= 1 bf16 ulp)."""
+    S, K, epn, H, R = 128, 8, 4, 256, 4
+    cl, cp, plans, cus, hidden, weights, topk, tpe, oh, ow = run_case(S, K, epn, H, R, 4, 32, "biased")
+    g = torch.Generator().manual_seed(3)
+    ys = [torch.randn(cp.NvS, H, generator=g).to(torch.bfloat16) for _ in range(R)]
+    outs, _ = cl.combine(plans, [y.to(cuda_device) for y in ys])
+    torch.cuda.synchronize()
+    eo, _ = simops.combine(cp, ys)
+    for r in range(R):
+        assert torch.equal(outs[r].cpu(), eo[r]), f"rank {r}: combine differs from the emulated rounding order"
+
+
+def test_plan_reuse_and_repeat(cuda_device):
+    """Backward path: dispatch with a saved plan (no planning, plan untouched), many times."""
+    S, K, epn, H, R = 96, 4, 4, 128, 4
+    cl, cp, plans, cus, hidden, weights, topk, tpe, oh, ow = run_case(S, K, epn, H, R, 3, 16, "biased")
+    snap = [p.clone() for p in plans]
+    ref = [h.clone() for h in oh]
+    dev = cuda_device
+    for it in range(5):
+        for s in cl._states:
+            s.hidden_local.view(torch.int16).fill_(0x3333)
+        oh2, ow2, cu2, plans2 = cl.dispatch([h.to(dev) for h in hidden], None, plans=snap)
+        torch.cuda.synchronize()
+        cl.check()
+        assert all(c is None for c in cu2) and all(w is None for w in ow2)
+        assert all(a is b for a, b in zip(plans2, snap))
+        for d in range(R):
+            m = defined_rows(cp, d)
+            assert torch.equal(oh2[d].cpu().view(torch.int16)[m], ref[d].cpu().view(torch.int16)[m])
+            for name in ("dst", "dup_groups", "dup_loffs", "dup_counts", "experts_to_copy"):
+                assert torch.equal(getattr(snap[d], name), getattr(plans[d], name))
+    # fresh dispatches back to back (barrier epochs keep advancing)
+    for it in range(3):
+        cl.dispatch([h.to(dev) for h in hidden], None, [t.to(dev) for t in topk], [t.to(dev) for t in tpe])
+    torch.cuda.synchronize()
+    cl.check()
+
+
+@pytest.mark.parametrize("R,epn,pad_elems", [(4, 4, 0), (8, 3, 24), (2, 5, 8)])
+def test_prefetch_and_reduce(R, epn, pad_elems, cuda_device):
+    S, K, H = 200, 6, 64
+    cl, cp, plans, *_ = run_case(S, K, epn, H, R, 3, 16, "biased", sigma=2.0, with_weights=False)
+    assert (cp.experts_to_copy >= 0).any(), "case must produce redundant experts"
+    dev = cuda_device
+    rows, cols = 40, 24          # expert payload 40*24*2 B = 1920 B (multiple of 16, not of the chunk)
+    g = torch.Generator().manual_seed(5)
+    names = ("gate", "up", "down")
+    local = {n: [torch.randn(epn, rows, cols, generator=g).to(torch.bfloat16) for _ in range(R)] for n in names}
+    pools, flats = {}, {}
+    for n in names:
+        pools[n], flats[n] = cl.make_pool((epn, rows, cols), torch.bfloat16, pad_elems)
+        flats[n].fill_(-123.0)
+    pairs = [[(local[n][r].to(dev), pools[n]) for n in names] for r in range(R)]
+    cl.prefetch(plans, pairs)
+    torch.cuda.synchronize()
+    cl.check()
+    for n in names:
+        exp = [torch.full((epn, rows, cols), -123.0, dtype=torch.bfloat16) for _ in range(R)]
+        simops.prefetch(cp, local[n], exp)
+        for r in range(R):
+            assert torch.equal(pools[n][r].cpu(), exp[r]), f"{n}: prefetch slots of rank {r} differ"
+        if pad_elems:
+            per = epn * rows * cols
+            gaps = flats[n].cpu().view(R, per + pad_elems)[:, per:]
+            assert (gaps == -123.0).all(), "padding between ranks was overwritten"
+
+    # --- reduce_grad (fp32, bitwise: fixed summation order)
+    lg = {n: [torch.randn(epn, rows, cols, generator=g) for _ in range(R)] for n in names}
+    rb = {n: [torch.randn(epn, rows, cols, generator=g) for _ in range(R)] for n in names}
+    rpools, rflats, lgd = {}, {}, {}
+    for n in names:
+        rpools[n], rflats[n] = cl.make_pool((epn, rows, cols), torch.float32, pad_elems)
+        rflats[n].fill_(-7.0)
+        for r in range(R):
+            rpools[n][r].copy_(rb[n][r])
+        lgd[n] = [x.to(dev) for x in lg[n]]
+    pairs = [[(lgd[n][r], rpools[n]) for n in names] for r in range(R)]
+    cl.reduce_grad(plans, pairs)
+    torch.cuda.synchronize()
+    cl.check()
+    for n in names:
+        el = [x.clone() for x in lg[n]]
+        er = [x.clone() for x in rb[n]]
+        simops.reduce_grad(cp, el, er)
+        for r in range(R):
+            assert torch.equal(lgd[n][r].cpu(), el[r]), f"{n}: reduced grad of rank {r} differs (must be bitwise)"
+            assert torch.equal(rpools[n][r].cpu(), er[r]), f"{n}: reduce slots of rank {r} differ"
+    # second launch on the same cluster: barrier state must have reset itself
+    cl.reduce_grad(plans, pairs)
+    torch.cuda.synchronize()
+    cl.check()
+
+
+def test_bounded_wait_reports_timeout(cuda_device):
+    """A wait on a flag nobody sets must give up after the budget and leave the context usable."""
+    from moonep_b200 import engine
+    from moonep_b200.sim.local_cluster import LocalCluster
+    cl = LocalCluster(8, 64, 2, 4, 1, num_sms=1, token_padding=4, budget_ms=20.0)
+    flag = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    engine.launch_wait_probe(cl._states[0], flag, 1)
+    torch.cuda.synchronize()
+    with pytest.raises(engine.MoonEPTimeout) as ei:
+        cl.check()
+    assert ei.value.status["code"] == 4 and ei.value.status["expected"] == 1
+    # the context is still healthy
+    assert float((torch.ones(4, device=cuda_device) * 2).sum()) == 8.0
+
+
+def test_public_buffer_r1(cuda_device):
+    """Public API on one rank: sync vs async, zero-copy aliasing, plan reuse."""
+    from moonep_b200 import Buffer, MoonEPCommPlan
+    S, H, K, E = 64, 128, 4, 8
+    buf = Buffer(S, H, K, E, 1, num_sms=4, token_padding=16)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    hidden = torch.randn(S, H, dtype=torch.bfloat16, device="cuda", generator=g)
+    w = torch.rand(S, K, device="cuda", generator=g)
+    topk = torch.randint(0, E, (S, K), dtype=torch.int32, device="cuda", generator=g)
+    tpe = torch.bincount(topk.flatten(), minlength=E).to(torch.int32)
+    h1, w1, cu1, plan1 = buf.dispatch(hidden, w, topk, tpe)
+    assert isinstance(plan1, MoonEPCommPlan) and tuple(h1.shape) == (buf.NvS, H)
+    h2, w2, cu2, plan2, ev = buf.dispatch(hidden, w, topk, tpe, async_finish=True)
+    ev.wait(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    n = int(cu1[-1])
+    assert torch.equal(h1[:n], h2[:n]) and torch.equal(w1[:n], w2[:n]) and torch.equal(cu1, cu2)
+    assert torch.equal(plan1.dst, plan2.dst)
+    out, wsk, _ = buf.combine(plan=plan1, hidden_nvsh=h1, route_weights_nvs=w1)
+    torch.cuda.synchronize()
+    assert torch.equal(wsk, w)
+    ref = (hidden.float() * K)       # each of the K copies comes back unweighted
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+    hz, wz, _, planz = buf.dispatch(hidden, w, topk, tpe, zero_copy=True, router_weights_zero_copy=True)
+    assert hz.data_ptr() == buf.hidden_nvsh_buffer_view.data_ptr()
+    outz, wz2, _ = buf.combine(plan=planz, hidden_nvsh=hz, route_weights_nvs=wz, zero_copy=True, router_weights_zero_copy=True)
+    torch.cuda.synchronize()
+    assert torch.equal(outz, out)
+    with pytest.raises(AssertionError, match="alias"):
+        buf.combine(plan=planz, hidden_nvsh=h1, zero_copy=True)
+    hr, wr, cur, pr = buf.dispatch(hidden, plan=plan1)
+    assert wr is None and cur is None and pr is plan1
+    torch.cuda.synchronize()
+    assert torch.equal(hr[:n], h1[:n])
+    buf.check()
+    buf.destroy()
+    assert buf.destroyed
+    buf.destroy()
