@@ -38,7 +38,7 @@ int launch_cooperative(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   if (pdl) { attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
              attr[n].val.programmaticStreamSerializationAllowed = 1; ++n; }
   cfg.attrs = attr; cfg.numAttrs = n;
-  if (smem > 48 * 1024)
+  if (smem > 16 * 1024)
     MEP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   MEP_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
   return 0;
@@ -50,7 +50,7 @@ int launch_plain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cfg.attrs = nullptr; cfg.numAttrs = 0;
-  if (smem > 48 * 1024)
+  if (smem > 16 * 1024)
     MEP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   MEP_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
   return 0;
