@@ -1,0 +1,118 @@
+"""Expert weight / gradient pools in symmetric memory.
+
+The communication API takes, per projection (gate, up, down), a local tensor
+``[epn, rows, cols]`` and an all-rank view ``[R, epn, rows, cols]`` of every rank's spare
+slots; the expert GEMM wants ``[2*epn, rows, cols]`` = local experts followed by this
+rank's slots (contract: README.md:45-68 of the reference, which leaves building these
+views to the integrating framework; its tests assemble them by hand,
+tests/test_e2e.py:50-57).  ``ExpertPools`` allocates ``[local | slots]`` per projection in
+one symmetric chunk and hands out all three views, for weights (payload dtype) and, for
+training, for gradients (fp32: local grad | reduce slots).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .geometry import align_up
+from .parallel.symm import SymmetricHeap
+
+NAMES = ("gate", "up", "down")
+
+
+class ExpertPools:
+    def __init__(self, epn: int, gate_shape, up_shape, down_shape, dtype=torch.bfloat16, group=None,
+                 with_grads: bool = False, world: int | None = None, rank: int | None = None,
+                 heap: SymmetricHeap | None = None, device=None):
+        """``*_shape`` = (rows, cols) of one expert's matrix.  With ``world``/``rank``/``heap``
+        given explicitly the pools live in an existing (e.g. single-process) heap."""
+        self.epn = epn
+        self.dtype = dtype
+        self.with_grads = with_grads
+        self._shapes = dict(zip(NAMES, (tuple(gate_shape), tuple(up_shape), tuple(down_shape))))
+        if world is None:
+            if dist.is_initialized():
+                world, rank = dist.get_world_size(group), dist.get_rank(group)
+            else:
+                world, rank = 1, 0
+        self.world, self.rank, self._group = world, rank, group
+        es = torch.tensor([], dtype=dtype).element_size()
+        off = 0
+        self._woff, self._goff = {}, {}
+        for n in NAMES:
+            r, c = self._shapes[n]
+            self._woff[n] = off
+            off = align_up(off + 2 * epn * r * c * es, 1024)
+        if with_grads:
+            for n in NAMES:
+                r, c = self._shapes[n]
+                self._goff[n] = off
+                off = align_up(off + 2 * epn * r * c * 4, 1024)
+        self._own_heap = heap is None
+        if heap is None:
+            if world > 1:
+                heap = SymmetricHeap.create(off, group=group)
+            else:
+                heap = SymmetricHeap.local(1, off, device or torch.device("cuda", torch.cuda.current_device()))
+        else:
+            assert heap.chunk_bytes >= off, "heap chunk too small for the pools"
+        self.heap = heap
+        self.bytes_per_rank = off
+
+    def shape(self, name):
+        return self._shapes[name]
+
+    def _view(self, off, name, dtype, first, count, rank=None):
+        r, c = self._shapes[name]
+        es = torch.tensor([], dtype=dtype).element_size()
+        rank = self.rank if rank is None else rank
+        return self.heap.view(rank, off + first * r * c * es, (count, r, c), dtype)
+
+    # ---- weights
+    def local_weight(self, name, rank=None) -> torch.Tensor:
+        return self._view(self._woff[name], name, self.dtype, 0, self.epn, rank)
+
+    def compute_weight(self, name, rank=None) -> torch.Tensor:
+        """``[2*epn, rows, cols]``: local experts then this rank's prefetch slots."""
+        return self._view(self._woff[name], name, self.dtype, 0, 2 * self.epn, rank)
+
+    def prefetch_view(self, name) -> torch.Tensor:
+        """``[R, epn, rows, cols]`` view of every rank's prefetch slots."""
+        r, c = self._shapes[name]
+        es = torch.tensor([], dtype=self.dtype).element_size()
+        return self.heap.strided_view(self._woff[name] + self.epn * r * c * es, (self.epn, r, c), self.dtype)
+
+    # ---- grads
+    def local_grad(self, name, rank=None) -> torch.Tensor:
+        return self._view(self._goff[name], name, torch.float32, 0, self.epn, rank)
+
+    def compute_grad(self, name, rank=None) -> torch.Tensor:
+        return self._view(self._goff[name], name, torch.float32, 0, 2 * self.epn, rank)
+
+    def reduce_view(self, name) -> torch.Tensor:
+        r, c = self._shapes[name]
+        return self.heap.strided_view(self._goff[name] + self.epn * r * c * 4, (self.epn, r, c), torch.float32)
+
+    # ---- keyword bundles for Buffer.prefetch_weight / Buffer.reduce_grad
+    def prefetch_kwargs(self, rank=None) -> dict:
+        kw = {}
+        for n in NAMES:
+            kw[f"local_{n}_weight"] = self.local_weight(n, rank)
+            kw[f"{n}_prefetch_buffer"] = self.prefetch_view(n)
+        return kw
+
+    def reduce_kwargs(self, rank=None) -> dict:
+        kw = {}
+        for n in NAMES:
+            kw[f"local_{n}_grad"] = self.local_grad(n, rank)
+            kw[f"{n}_reduce_buffer"] = self.reduce_view(n)
+        return kw
+
+    def destroy(self) -> None:
+        if self.heap is not None and self._own_heap:
+            torch.cuda.synchronize()
+            if self.world > 1 and dist.is_initialized():
+                dist.barrier(group=self._group)
+            self.heap.close()
+        self.heap = None

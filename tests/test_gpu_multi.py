@@ -1,0 +1,27 @@
+"""Multi-GPU tests: spawn one process per GPU (skipped with fewer than two devices)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_dist_e2e(n):
+    if _ngpu() < n:
+        pytest.skip(f"needs {n} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29500 + n), os.path.join(ROOT, "tests", "dist_e2e.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, f"dist_e2e failed on {n} ranks:\n{r.stdout[-3000:]}\n{r.stderr[-3000:]}"
+    assert "[dist_e2e] PASS" in r.stdout
