@@ -1,0 +1,347 @@
+// Grouped expert GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), bf16 -> fp32.
+//
+// The reference ships no GEMM: it hands `cu_seqlens[2*epn]` and the `[2*epn, in, out]`
+// compute views to the integrating framework's "VM group GEMM" (README.md:45,54 of the
+// reference). This file is that consumer, written for sm_100a:
+//   * persistent CTAs (one per SM), warp-specialised: warp 0 = TMA producer, warp 1 = MMA
+//     issuer (one elected thread issues tcgen05.mma), warps 2-5 = epilogue;
+//   * operands staged by 2-D tiled TMA (128-byte swizzle) from LOCAL memory into a 4-stage
+//     shared-memory ring; accumulators live in TMEM, double-buffered (2 x 256 columns) so the
+//     epilogue of tile i overlaps the main loop of tile i+1;
+//   * the tile scheduler walks `cu_seqlens` on the device (no host sync); every group is padded
+//     to a multiple of 128 rows by the planner, so a 128-row tile never straddles two experts.
+// Tile: 128 x 256 x 64. Modes (weights stored [group, in, out], i.e. "N-contiguous"):
+//   GATE_UP   act = silu(x Wg) * (x Wu)       A K-major, B MN-major from two tensors (128+128)
+//   DOWN      y = (act Wd) * row_scale         A K-major, B MN-major
+//   DGRAD     dA = dY W^T                      A K-major, B K-major
+//   DGRAD_GU  dx = dG Wg^T + dU Wu^T           A = [dG | dU] K-major, B K-major from two tensors
+//   WGRAD     dW[g] (+)= X_g^T dY_g  (fp32)    A and B MN-major, K = rows of the group
+#include "tcgen05.cuh"
+#include "../host/driver_api.h"
+#include "../host/launch.h"
+
+namespace mep {
+
+enum GemmMode { GEMM_GATE_UP = 0, GEMM_DOWN = 1, GEMM_DGRAD = 2, GEMM_DGRAD_GU = 3, GEMM_WGRAD = 4 };
+
+struct GemmArgs {
+  const int32_t* cu_seqlens;   // [G] padded end row of each group
+  int32_t G;
+  int32_t N;                   // output columns (GATE_UP: width of act = out dim of each weight)
+  int32_t K;                   // reduction length (DGRAD_GU: 2 * inner); unused for WGRAD
+  int32_t M_w;                 // WGRAD: rows of one weight matrix
+  int32_t b_group_rows;        // rows one group occupies in the flattened 2-D weight tensor(s)
+  int32_t accumulate;          // WGRAD: 1 -> out += acc, 0 -> out = acc
+  int32_t g_begin, g_end;      // only groups in [g_begin, g_end) are computed
+  void* out;                   // bf16 [rows, ldo]; WGRAD: fp32 [G, M_w, N]
+  void* out2;                  // GATE_UP: optional bf16 [rows, 2N] pre-activations (gate | up)
+  const float* row_scale;      // GATE_UP / DOWN: optional per-row factor [rows]
+  int64_t ldo;
+  int32_t* status;             // [4] error word: code, site, block, tile
+  uint64_t budget_ns;
+};
+
+constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;            // 16 KB
+constexpr int kBBytes = kBN * kBK * 2;            // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kAtomBytes = 64 * kBK * 2;          // one 64-wide MN-major atom: 64 k-rows x 128 B
+constexpr int kGemmThreads = 192;
+constexpr int kMaxGroups = 1024;
+constexpr int kTmemCols = 512;
+
+struct TileInfo { int g, row0, m0, n0, kblocks; };
+
+template <int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b0,
+                    const __grid_constant__ CUtensorMap tma_b1, GemmArgs args) {
+  constexpr bool A_MN = MODE == GEMM_WGRAD;
+  constexpr bool B_MN = MODE == GEMM_GATE_UP || MODE == GEMM_DOWN || MODE == GEMM_WGRAD;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], tfull_bar[2], tempty_bar[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+  __shared__ int s_ntiles, s_nact;
+  __shared__ int s_start[kMaxGroups + 1];   // non-WGRAD: first tile of group; WGRAD: active group ids
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = args.G;
+
+  // ---------------- setup
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 4); }
+    fence_mbar_init();
+    if (MODE == GEMM_WGRAD) {
+      int n = 0, prev = 0;
+      for (int g = 0; g < G; ++g) { const int e = args.cu_seqlens[g]; if (e > prev && g >= args.g_begin && g < args.g_end) s_start[n++] = g; prev = e; }
+      s_nact = n;
+      s_ntiles = n * (args.M_w / kBM) * (args.N / kBN);
+    } else {
+      const int nblk = MODE == GEMM_GATE_UP ? args.N / 128 : args.N / kBN;
+      int run = 0, prev = 0;
+      for (int g = 0; g < G; ++g) { const int e = args.cu_seqlens[g]; s_start[g] = run; if (g >= args.g_begin && g < args.g_end) run += ((e - prev) / kBM) * nblk; prev = e; }
+      s_start[G] = run;
+      s_ntiles = run;
+    }
+    tc::prefetch_tmap(&tma_a); tc::prefetch_tmap(&tma_b0); tc::prefetch_tmap(&tma_b1);
+  }
+  if (warp == 1) { tc::tmem_alloc(&s_tmem_base, kTmemCols); tc::tmem_relinquish(); }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = s_tmem_base;
+  const int ntiles = s_ntiles;
+
+  auto fail = [&](int site, int tile) {
+    if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = site; args.status[2] = blockIdx.x; args.status[3] = tile; }
+    s_abort = 1;
+  };
+
+  // tile index -> coordinates; `gcur` is a monotone cursor over groups (non-WGRAD)
+  auto get_tile = [&](int t, int& gcur, TileInfo& ti) {
+    if (MODE == GEMM_WGRAD) {
+      const int mblk = args.M_w / kBM, per = mblk * (args.N / kBN);
+      const int ai = t / per, local = t - ai * per;
+      const int g = s_start[ai];
+      const int beg = g ? args.cu_seqlens[g - 1] : 0;
+      ti.g = g; ti.row0 = beg; ti.kblocks = (args.cu_seqlens[g] - beg) / kBK;
+      ti.m0 = (local % mblk) * kBM; ti.n0 = (local / mblk) * kBN;
+    } else {
+      while (gcur + 1 <= G && s_start[gcur + 1] <= t) ++gcur;
+      const int g = gcur;
+      const int beg = g ? args.cu_seqlens[g - 1] : 0;
+      const int mblk = (args.cu_seqlens[g] - beg) / kBM;
+      const int local = t - s_start[g];
+      ti.g = g; ti.row0 = beg + (local % mblk) * kBM; ti.m0 = 0;
+      ti.n0 = (local / mblk) * (MODE == GEMM_GATE_UP ? 128 : kBN);
+      ti.kblocks = args.K / kBK;
+    }
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one thread)
+    if (lane == 0) {
+      int it = 0, gcur = 0; TileInfo ti;
+      for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x) {
+        get_tile(t, gcur, ti);
+        for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
+          const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, args.budget_ns)) { fail(1, t); break; }
+          unsigned char* sa = smem + (size_t)s * kStageBytes;
+          unsigned char* sb = sa + kABytes;
+          mbar_expect_tx(&full_bar[s], kStageBytes);
+          const int k0 = kb * kBK;
+          if (A_MN) {   // x[rows, in]: two 64-wide atoms along M, 64 token rows of K
+            tc::tma_load_2d(sa, &tma_a, ti.m0, ti.row0 + k0, &full_bar[s]);
+            tc::tma_load_2d(sa + kAtomBytes, &tma_a, ti.m0 + 64, ti.row0 + k0, &full_bar[s]);
+          } else {
+            tc::tma_load_2d(sa, &tma_a, k0, ti.row0, &full_bar[s]);
+          }
+          if (MODE == GEMM_GATE_UP) {
+            const int r = ti.g * args.b_group_rows + k0;
+            tc::tma_load_2d(sb, &tma_b0, ti.n0, r, &full_bar[s]);
+            tc::tma_load_2d(sb + kAtomBytes, &tma_b0, ti.n0 + 64, r, &full_bar[s]);
+            tc::tma_load_2d(sb + 2 * kAtomBytes, &tma_b1, ti.n0, r, &full_bar[s]);
+            tc::tma_load_2d(sb + 3 * kAtomBytes, &tma_b1, ti.n0 + 64, r, &full_bar[s]);
+          } else if (MODE == GEMM_DOWN) {
+            const int r = ti.g * args.b_group_rows + k0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tc::tma_load_2d(sb + i * kAtomBytes, &tma_b0, ti.n0 + 64 * i, r, &full_bar[s]);
+          } else if (MODE == GEMM_WGRAD) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tc::tma_load_2d(sb + i * kAtomBytes, &tma_b0, ti.n0 + 64 * i, ti.row0 + k0, &full_bar[s]);
+          } else if (MODE == GEMM_DGRAD) {
+            tc::tma_load_2d(sb, &tma_b0, k0, ti.g * args.b_group_rows + ti.n0, &full_bar[s]);
+          } else {  // DGRAD_GU: first half of K from Wg, second half from Wu
+            const int half = args.K / 2;
+            if (k0 < half) tc::tma_load_2d(sb, &tma_b0, k0, ti.g * args.b_group_rows + ti.n0, &full_bar[s]);
+            else tc::tma_load_2d(sb, &tma_b1, k0 - half, ti.g * args.b_group_rows + ti.n0, &full_bar[s]);
+          }
+        }
+      }
+      // drain: do not leave the CTA while copies into its shared memory may still be in flight
+      if (it > 0) {
+        const int last = it - 1;
+        const int s = last % kStages; const uint32_t ph = (uint32_t)(last / kStages) & 1u;
+        mbar_wait_bounded(&full_bar[s], ph, args.budget_ns);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::instr_desc_bf16(kBM, kBN, A_MN, B_MN);
+      int it = 0, tcnt = 0, gcur = 0; TileInfo ti;
+      for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x, ++tcnt) {
+        get_tile(t, gcur, ti);
+        const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
+        if (!mbar_wait_bounded(&tempty_bar[acc], aph ^ 1u, args.budget_ns)) { fail(2, t); break; }
+        tc::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * kBN;
+        bool ok = true;
+        for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
+          const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+          if (!mbar_wait_bounded(&full_bar[s], ph, args.budget_ns)) { fail(3, t); ok = false; break; }
+          tc::fence_after_sync();
+          const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t ad = A_MN ? tc::smem_desc(sa + k * 2048, kAtomBytes, 1024) : tc::smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? tc::smem_desc(sb + k * 2048, kAtomBytes, 1024) : tc::smem_desc(sb + k * 32, 16, 1024);
+            tc::mma_bf16(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          tc::mma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
+        }
+        if (!ok) break;
+        tc::mma_commit(&tfull_bar[acc]);      // accumulator complete
+      }
+    }
+  } else {
+    // ---------------- epilogue warps (TMEM lane quarter = warp % 4)
+    const int q = warp & 3;
+    const int r_in_tile = q * 32 + lane;
+    int tcnt = 0, gcur = 0; TileInfo ti;
+    for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x, ++tcnt) {
+      get_tile(t, gcur, ti);
+      const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait_bounded(&tfull_bar[acc], aph, args.budget_ns) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) fail(4, t); break; }
+      tc::fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * kBN;
+      if (MODE == GEMM_GATE_UP) {
+        const size_t row = (size_t)ti.row0 + r_in_tile;
+        __nv_bfloat16* orow = (__nv_bfloat16*)args.out + row * args.ldo + ti.n0;
+        __nv_bfloat16* grow = args.out2 ? (__nv_bfloat16*)args.out2 + row * (size_t)(2 * args.N) + ti.n0 : nullptr;
+        const float sc = args.row_scale ? args.row_scale[row] : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t gr[32], ur[32];
+          tc::tmem_ld32(taddr + c * 32, gr);
+          tc::tmem_ld32(taddr + 128 + c * 32, ur);
+          tc::tmem_ld_wait();
+          uint32_t o[16], og[16], ou[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g0 = __uint_as_float(gr[2 * j]), g1 = __uint_as_float(gr[2 * j + 1]);
+            const float u0 = __uint_as_float(ur[2 * j]), u1 = __uint_as_float(ur[2 * j + 1]);
+            const float a0 = g0 / (1.f + __expf(-g0)) * u0 * sc, a1 = g1 / (1.f + __expf(-g1)) * u1 * sc;
+            __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1); o[j] = *reinterpret_cast<uint32_t*>(&h);
+            __nv_bfloat162 hg = __floats2bfloat162_rn(g0, g1); og[j] = *reinterpret_cast<uint32_t*>(&hg);
+            __nv_bfloat162 hu = __floats2bfloat162_rn(u0, u1); ou[j] = *reinterpret_cast<uint32_t*>(&hu);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            st_v4(orow + c * 32 + j * 8, make_int4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+            if (grow) {
+              st_v4(grow + c * 32 + j * 8, make_int4(og[4 * j], og[4 * j + 1], og[4 * j + 2], og[4 * j + 3]));
+              st_v4(grow + args.N + c * 32 + j * 8, make_int4(ou[4 * j], ou[4 * j + 1], ou[4 * j + 2], ou[4 * j + 3]));
+            }
+          }
+        }
+      } else if (MODE == GEMM_WGRAD) {
+        float* orow = (float*)args.out + ((size_t)ti.g * args.M_w + ti.m0 + r_in_tile) * args.N + ti.n0;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[32];
+          tc::tmem_ld32(taddr + c * 32, r);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            float4* p = reinterpret_cast<float4*>(orow + c * 32 + j * 4);
+            if (args.accumulate) { const float4 old = *p; v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w; }
+            *p = v;
+          }
+        }
+      } else {
+        const size_t row = (size_t)ti.row0 + r_in_tile;
+        __nv_bfloat16* orow = (__nv_bfloat16*)args.out + row * args.ldo + ti.n0;
+        const float sc = (MODE == GEMM_DOWN && args.row_scale) ? args.row_scale[row] : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[32];
+          tc::tmem_ld32(taddr + c * 32, r);
+          tc::tmem_ld_wait();
+          uint32_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * sc, __uint_as_float(r[2 * j + 1]) * sc);
+            o[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) st_v4(orow + c * 32 + j * 8, make_int4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  // ---------------- teardown: everyone joins, then the allocating warp frees TMEM
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  if (warp == 1) tc::tmem_dealloc(tmem_base, kTmemCols);
+}
+
+static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
+  const DriverApi* d = driver(); if (!d) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t es[2] = {1, 1};
+  MEP_REQUIRE(((uintptr_t)base & 15) == 0 && (ld * 2) % 16 == 0 && ld >= cols,
+              "gemm: tensor base/stride must be 16-byte aligned");
+  MEP_CU_CHECK(d->TensorMapEncodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return 0;
+}
+
+}  // namespace mep
+
+// One grouped GEMM launch. `a` is a row-major bf16 matrix [a_rows, a_cols]; `b0`/`b1` are the
+// weight tensors flattened to 2-D [b_rows, b_cols] (WGRAD: b0 = dY [rows, N]); `a_ld` / `b_ld` are
+// the row pitches in elements (>= the column count). See the file
+// header for what each mode computes.
+extern "C" int mep_grouped_gemm(int mode, const void* a, int64_t a_rows, int64_t a_cols, int64_t a_ld,
+                                const void* b0, const void* b1, int64_t b_rows, int64_t b_cols, int64_t b_ld,
+                                const mep::GemmArgs* args_in, int num_ctas, cudaStream_t stream) {
+  using namespace mep;
+  GemmArgs args = *args_in;
+  MEP_REQUIRE(args.G >= 1 && args.G <= kMaxGroups, "gemm: G=%d out of range [1,%d]", args.G, kMaxGroups);
+  CUtensorMap ma, mb0, mb1;
+  const bool b_mn = mode == GEMM_GATE_UP || mode == GEMM_DOWN || mode == GEMM_WGRAD;
+  if (mode == GEMM_WGRAD) {
+    MEP_REQUIRE(args.M_w % kBM == 0 && args.N % kBN == 0, "wgrad: weight shape [%d,%d] must be multiples of [128,256]", args.M_w, args.N);
+    if (make_map(&ma, a, a_rows, a_cols, a_ld, 64, 64)) return -1;
+  } else {
+    MEP_REQUIRE(args.K % kBK == 0, "gemm: K=%d must be a multiple of 64", args.K);
+    MEP_REQUIRE(args.N % (mode == GEMM_GATE_UP ? 128 : kBN) == 0, "gemm: N=%d not tileable", args.N);
+    if (make_map(&ma, a, a_rows, a_cols, a_ld, 64, kBM)) return -1;
+  }
+  if (b_mn) { if (make_map(&mb0, b0, b_rows, b_cols, b_ld, 64, 64)) return -1; }
+  else      { if (make_map(&mb0, b0, b_rows, b_cols, b_ld, 64, kBN)) return -1; }
+  if (b1) { if (make_map(&mb1, b1, b_rows, b_cols, b_ld, 64, b_mn ? 64 : kBN)) return -1; }
+  else mb1 = mb0;
+  const size_t smem = (size_t)kStages * kStageBytes + 1024;
+  dim3 grid(num_ctas), block(kGemmThreads);
+#define MEP_GEMM_CASE(M)                                                                             \
+  case M:                                                                                            \
+    MEP_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    grouped_gemm_kernel<M><<<grid, block, smem, stream>>>(ma, mb0, mb1, args);                       \
+    break;
+  switch (mode) {
+    MEP_GEMM_CASE(GEMM_GATE_UP) MEP_GEMM_CASE(GEMM_DOWN) MEP_GEMM_CASE(GEMM_DGRAD)
+    MEP_GEMM_CASE(GEMM_DGRAD_GU) MEP_GEMM_CASE(GEMM_WGRAD)
+    default: return set_error("gemm: unknown mode %d", mode);
+  }
+#undef MEP_GEMM_CASE
+  MEP_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}

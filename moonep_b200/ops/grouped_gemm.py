@@ -1,0 +1,148 @@
+"""Python front end of the tcgen05 grouped expert GEMM (csrc/device/grouped_gemm.cu) and its
+element-wise companions (csrc/device/swiglu.cu).
+
+Conventions: ``x`` is the dispatched token matrix ``[NvS, in]`` in VM-group order;
+``cu_seqlens[G]`` holds each group's padded end row (multiples of 128); weights are
+``[G, in, out]`` bf16 (G = 2*epn: local experts then prefetch slots).  All functions launch
+on the current stream and fail loudly if the native library is missing.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _native
+
+GATE_UP, DOWN, DGRAD, DGRAD_GU, WGRAD = range(5)
+_status_cache: dict = {}
+_sm_cache: dict = {}
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [("cu_seqlens", C.c_void_p), ("G", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+                ("M_w", C.c_int32), ("b_group_rows", C.c_int32), ("accumulate", C.c_int32),
+                ("g_begin", C.c_int32), ("g_end", C.c_int32),
+                ("out", C.c_void_p), ("out2", C.c_void_p), ("row_scale", C.c_void_p), ("ldo", C.c_int64),
+                ("status", C.c_void_p), ("budget_ns", C.c_uint64)]
+
+
+def _status(device) -> torch.Tensor:
+    key = torch.device(device).index
+    if key not in _status_cache:
+        _status_cache[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status_cache[key]
+
+
+def _num_sms(device) -> int:
+    key = torch.device(device).index
+    if key not in _sm_cache:
+        _sm_cache[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_cache[key]
+
+
+def check_status(device="cuda") -> None:
+    """Synchronise and raise if a GEMM pipeline wait expired."""
+    v = _status(torch.device(device) if not isinstance(device, torch.device) else device).cpu().tolist()
+    if v[0] != 0:
+        raise RuntimeError(f"grouped GEMM aborted: code {v[0]} at site {v[1]}, CTA {v[2]}, tile {v[3]}")
+
+
+def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=None, row_scale=None, ldo=0,
+            accumulate=False, a_cols=None, b_rows=None, b_cols=None, b_ld=None, groups=None, num_ctas=None):
+    lib = _native.load()
+    assert a.dtype == torch.bfloat16 and b0.dtype == torch.bfloat16
+    assert cu.dtype == torch.int32 and cu.is_contiguous()
+    G = cu.numel()
+    g0, g1 = (0, G) if groups is None else groups
+    args = GemmArgs()
+    args.cu_seqlens = cu.data_ptr()
+    args.G, args.N, args.K, args.M_w = G, N, K, M_w
+    args.b_group_rows, args.accumulate = b_group_rows, 1 if accumulate else 0
+    args.g_begin, args.g_end = g0, g1
+    args.out, args.out2 = out.data_ptr(), _native.ptr(out2)
+    args.row_scale, args.ldo = _native.ptr(row_scale), ldo
+    args.status = _status(a.device).data_ptr()
+    from ..engine import wait_budget_ns
+    args.budget_ns = wait_budget_ns()
+    a_rows = a.shape[0]
+    a_ld = a.stride(0)
+    a_cols = a.shape[1] if a_cols is None else a_cols
+    rc = lib.mep_grouped_gemm(mode, C.c_void_p(a.data_ptr()), C.c_int64(a_rows), C.c_int64(a_cols), C.c_int64(a_ld),
+                              C.c_void_p(b0.data_ptr()), C.c_void_p(_native.ptr(b1)), C.c_int64(b_rows),
+                              C.c_int64(b_cols), C.c_int64(b_ld), C.byref(args),
+                              num_ctas or _num_sms(a.device), _native.cur_stream())
+    _native.check(rc, "grouped_gemm")
+
+
+def _w2d(w):
+    assert w.dim() == 3 and w.is_contiguous(), "weights must be contiguous [G, in, out]"
+    return w.shape[0] * w.shape[1], w.shape[2]
+
+
+def gate_up(x, wg, wu, cu, act_out, gu_out=None, row_scale=None, groups=None, num_ctas=None):
+    """``act_out[r] = row_scale[r] * silu(x[r] Wg[g]) * (x[r] Wu[g])``; optionally stores the
+    pre-activations ``gu_out = [x Wg | x Wu]`` (``[NvS, 2*out]``) for the backward pass."""
+    G, K, N = wg.shape
+    assert wu.shape == wg.shape and x.shape[1] == K and N % 128 == 0 and K % 64 == 0
+    rows, cols = _w2d(wg)
+    _launch(GATE_UP, x, wg, wu, cu, N=N, K=K, b_group_rows=K, out=act_out, out2=gu_out, row_scale=row_scale,
+            ldo=act_out.stride(0), b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
+
+
+def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None):
+    """``out[r] = row_scale[r] * (act[r] Wd[g])`` with ``Wd [G, inner, hidden]``."""
+    G, K, N = wd.shape
+    assert act.shape[1] == K and N % 256 == 0 and K % 64 == 0
+    rows, cols = _w2d(wd)
+    _launch(DOWN, act, wd, None, cu, N=N, K=K, b_group_rows=K, out=out, row_scale=row_scale, ldo=out.stride(0),
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
+
+
+def dgrad(dy, w, cu, out, groups=None, num_ctas=None):
+    """``out[r] = dy[r] W[g]^T`` with ``W [G, in, out]`` -> ``out [NvS, in]``."""
+    G, N, K = w.shape
+    assert dy.shape[1] == K and N % 256 == 0 and K % 64 == 0
+    rows, cols = _w2d(w)
+    _launch(DGRAD, dy, w, None, cu, N=N, K=K, b_group_rows=N, out=out, ldo=out.stride(0),
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
+
+
+def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None):
+    """``out[r] = dG[r] Wg[g]^T + dU[r] Wu[g]^T`` with ``dgu = [dG | dU]`` (``[NvS, 2*inner]``)."""
+    G, N, Kh = wg.shape
+    assert dgu.shape[1] == 2 * Kh and N % 256 == 0 and Kh % 64 == 0
+    rows, cols = _w2d(wg)
+    _launch(DGRAD_GU, dgu, wg, wu, cu, N=N, K=2 * Kh, b_group_rows=N, out=out, ldo=out.stride(0),
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
+
+
+def wgrad(x, dy, cu, out, accumulate=False, groups=None, num_ctas=None):
+    """``out[g] (+)= x_g^T dy_g`` in fp32; ``out [G, in, out_dim]``.  ``dy`` may be a column slice
+    of a wider matrix (row pitch = ``dy.stride(0)``).  Groups without rows are left untouched."""
+    G, M, N = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous()
+    assert x.shape[1] == M and dy.shape[1] == N and M % 128 == 0 and N % 256 == 0
+    assert dy.stride(1) == 1 and x.stride(1) == 1
+    _launch(WGRAD, x, dy, None, cu, N=N, M_w=M, out=out, accumulate=accumulate,
+            b_rows=dy.shape[0], b_cols=N, b_ld=dy.stride(0), groups=groups, num_ctas=num_ctas)
+
+
+def swiglu_bwd(dA, gu, w, dgu, dw, cu, num_blocks=None):
+    """Backward of ``act = w * silu(g) * u``: fills ``dgu = [dG | dU]`` and ``dw[row]``."""
+    lib = _native.load()
+    Hp = dA.shape[1]
+    nb = num_blocks or 4 * _num_sms(dA.device)
+    _native.check(lib.mep_swiglu_bwd(C.c_void_p(dA.data_ptr()), C.c_void_p(gu.data_ptr()), C.c_void_p(_native.ptr(w)),
+                                     C.c_void_p(dgu.data_ptr()), C.c_void_p(_native.ptr(dw)), C.c_void_p(cu.data_ptr()),
+                                     cu.numel(), Hp, nb, _native.cur_stream()), "swiglu_bwd")
+
+
+def sgd_step(p, g, lr, num_blocks=None):
+    lib = _native.load()
+    assert p.dtype == torch.bfloat16 and g.dtype == torch.float32 and p.numel() == g.numel()
+    assert p.is_contiguous() and g.is_contiguous()
+    nb = num_blocks or 8 * _num_sms(p.device)
+    _native.check(lib.mep_sgd_step(C.c_void_p(p.data_ptr()), C.c_void_p(g.data_ptr()), C.c_float(lr),
+                                   C.c_int64(p.numel()), nb, _native.cur_stream()), "sgd_step")

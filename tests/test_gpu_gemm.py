@@ -1,0 +1,119 @@
+"""Numerics of the tcgen05 grouped GEMM against a plain fp32 PyTorch reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(G, rows_per_group, K, N, seed=0, dev="cuda"):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    cu, tot = [], 0
+    for r in rows_per_group:
+        tot += r
+        cu.append(tot)
+    cu = torch.tensor(cu, dtype=torch.int32, device=dev)
+    rows = tot + 128          # extra undefined tail rows must not be touched
+    x = (torch.randn(rows, K, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    return cu, tot, rows, x, g
+
+
+def _group_slices(rows_per_group):
+    s = 0
+    for gi, r in enumerate(rows_per_group):
+        yield gi, s, s + r
+        s += r
+
+
+def _relerr(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+@pytest.mark.parametrize("rpg", [[128, 0, 256, 128], [384, 128, 0, 0, 128, 256]])
+def test_gate_up_down(rpg, cuda_device):
+    from moonep_b200.ops import grouped_gemm as gg
+    G, K, N = len(rpg), 256, 256
+    cu, tot, rows, x, g = _setup(G, rpg, K, N)
+    wg = (torch.randn(G, K, N, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(G, K, N, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(G, N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    scale = torch.rand(rows, device="cuda", generator=g) + 0.5
+    act = torch.full((rows, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    gu = torch.full((rows, 2 * N), 7.0, dtype=torch.bfloat16, device="cuda")
+    gg.gate_up(x, wg, wu, cu, act, gu, row_scale=scale)
+    y = torch.full((rows, K), 7.0, dtype=torch.bfloat16, device="cuda")
+    gg.down(act, wd, cu, y)
+    torch.cuda.synchronize()
+    gg.check_status()
+    for gi, a, b in _group_slices(rpg):
+        if a == b:
+            continue
+        xf = x[a:b].float()
+        gr, ur = xf @ wg[gi].float(), xf @ wu[gi].float()
+        ar = torch.nn.functional.silu(gr) * ur * scale[a:b, None]
+        assert _relerr(gu[a:b, :N], gr) < 1e-2 and _relerr(gu[a:b, N:], ur) < 1e-2, f"group {gi}: pre-activations"
+        assert _relerr(act[a:b], ar) < 1.5e-2, f"group {gi}: swiglu"
+        yr = act[a:b].float() @ wd[gi].float()
+        assert _relerr(y[a:b], yr) < 1e-2, f"group {gi}: down"
+    assert (act[tot:] == 7.0).all() and (y[tot:] == 7.0).all(), "rows beyond cu_seqlens[-1] were written"
+
+
+def test_dgrad_and_wgrad(cuda_device):
+    from moonep_b200.ops import grouped_gemm as gg
+    rpg = [256, 128, 0, 384]
+    G, H, Hp = len(rpg), 256, 256
+    cu, tot, rows, x, g = _setup(G, rpg, H, Hp, seed=1)
+    wg = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(G, Hp, H, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    dy = (torch.randn(rows, H, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    dgu = (torch.randn(rows, 2 * Hp, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    dA = torch.zeros(rows, Hp, dtype=torch.bfloat16, device="cuda")
+    gg.dgrad(dy, wd, cu, dA)
+    dx = torch.zeros(rows, H, dtype=torch.bfloat16, device="cuda")
+    gg.dgrad_gate_up(dgu, wg, wu, cu, dx)
+    dWg = torch.full((G, H, Hp), 3.0, device="cuda")
+    dWu = torch.full((G, H, Hp), 3.0, device="cuda")
+    gg.wgrad(x, dgu[:, :Hp], cu, dWg, accumulate=False)
+    gg.wgrad(x, dgu[:, Hp:], cu, dWu, accumulate=True)
+    torch.cuda.synchronize()
+    gg.check_status()
+    for gi, a, b in _group_slices(rpg):
+        if a == b:
+            assert (dWg[gi] == 3.0).all() and (dWu[gi] == 3.0).all(), "empty group's grads must stay untouched"
+            continue
+        assert _relerr(dA[a:b], dy[a:b].float() @ wd[gi].float().T) < 1e-2, f"group {gi}: dgrad"
+        ref = dgu[a:b, :Hp].float() @ wg[gi].float().T + dgu[a:b, Hp:].float() @ wu[gi].float().T
+        assert _relerr(dx[a:b], ref) < 1e-2, f"group {gi}: dgrad gate/up"
+        assert _relerr(dWg[gi], x[a:b].float().T @ dgu[a:b, :Hp].float()) < 2e-3, f"group {gi}: wgrad"
+        assert _relerr(dWu[gi], 3.0 + x[a:b].float().T @ dgu[a:b, Hp:].float()) < 2e-3, f"group {gi}: wgrad accumulate"
+
+
+def test_swiglu_bwd(cuda_device):
+    from moonep_b200.ops import grouped_gemm as gg
+    rows, Hp = 256, 128
+    g = torch.Generator(device="cuda").manual_seed(2)
+    cu = torch.tensor([128, 256], dtype=torch.int32, device="cuda")
+    gu = torch.randn(rows, 2 * Hp, device="cuda", generator=g).to(torch.bfloat16)
+    dA = torch.randn(rows, Hp, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.rand(rows, device="cuda", generator=g)
+    dgu = torch.zeros(rows, 2 * Hp, dtype=torch.bfloat16, device="cuda")
+    dw = torch.zeros(rows, device="cuda")
+    gg.swiglu_bwd(dA, gu, w, dgu, dw, cu)
+    torch.cuda.synchronize()
+    gf = gu[:, :Hp].float().requires_grad_(True)
+    uf = gu[:, Hp:].float().requires_grad_(True)
+    wf = w.clone().requires_grad_(True)
+    act = wf[:, None] * torch.nn.functional.silu(gf) * uf
+    act.backward(dA.float())
+    assert _relerr(dgu[:, :Hp], gf.grad) < 1e-2 and _relerr(dgu[:, Hp:], uf.grad) < 1e-2
+    assert _relerr(dw, wf.grad) < 1e-3
+
+
+def test_sgd(cuda_device):
+    from moonep_b200.ops import grouped_gemm as gg
+    p = torch.randn(4096, device="cuda").to(torch.bfloat16)
+    g = torch.randn(4096, device="cuda")
+    ref = (p.float() - 0.1 * g).to(torch.bfloat16)
+    gg.sgd_step(p, g, 0.1)
+    torch.cuda.synchronize()
+    assert torch.equal(p, ref)
