@@ -33,6 +33,8 @@ struct GemmArgs {
   int32_t b_group_rows;        // rows one group occupies in the flattened 2-D weight tensor(s)
   int32_t accumulate;          // WGRAD: 1 -> out += acc, 0 -> out = acc
   int32_t g_begin, g_end;      // only groups in [g_begin, g_end) are computed
+  int32_t zero_empty_below;    // WGRAD without accumulate: empty groups g < this get zeros
+  int32_t pad_;
   void* out;                   // bf16 [rows, ldo]; WGRAD: fp32 [G, M_w, N]
   void* out2;                  // GATE_UP: optional bf16 [rows, 2N] pre-activations (gate | up)
   const float* row_scale;      // GATE_UP / DOWN: optional per-row factor [rows]
@@ -76,7 +78,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     fence_mbar_init();
     if (MODE == GEMM_WGRAD) {
       int n = 0, prev = 0;
-      for (int g = 0; g < G; ++g) { const int e = args.cu_seqlens[g]; if (e > prev && g >= args.g_begin && g < args.g_end) s_start[n++] = g; prev = e; }
+      for (int g = 0; g < G; ++g) { const int e = args.cu_seqlens[g]; const bool in = g >= args.g_begin && g < args.g_end;
+        if (in && (e > prev || (!args.accumulate && g < args.zero_empty_below))) s_start[n++] = g; prev = e; }
       s_nact = n;
       s_ntiles = n * (args.M_w / kBM) * (args.N / kBN);
     } else {
@@ -176,6 +179,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int it = 0, tcnt = 0, gcur = 0; TileInfo ti;
       for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x, ++tcnt) {
         get_tile(t, gcur, ti);
+        if (ti.kblocks == 0) { --tcnt; continue; }     // empty group: the epilogue writes zeros on its own
         const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
         if (!mbar_wait_bounded(&tempty_bar[acc], aph ^ 1u, args.budget_ns)) { fail(2, t); break; }
         tc::fence_after_sync();
@@ -205,6 +209,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     int tcnt = 0, gcur = 0; TileInfo ti;
     for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x, ++tcnt) {
       get_tile(t, gcur, ti);
+      if (ti.kblocks == 0) {
+        if (MODE == GEMM_WGRAD) {
+          float* orow = (float*)args.out + ((size_t)ti.g * args.M_w + ti.m0 + r_in_tile) * args.N + ti.n0;
+          for (int j = 0; j < kBN / 4; ++j) reinterpret_cast<float4*>(orow)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        --tcnt; continue;
+      }
       const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
       int ok = 1;
       if (lane == 0) ok = mbar_wait_bounded(&tfull_bar[acc], aph, args.budget_ns) ? 1 : 0;

@@ -23,7 +23,7 @@ _sm_cache: dict = {}
 class GemmArgs(C.Structure):
     _fields_ = [("cu_seqlens", C.c_void_p), ("G", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
                 ("M_w", C.c_int32), ("b_group_rows", C.c_int32), ("accumulate", C.c_int32),
-                ("g_begin", C.c_int32), ("g_end", C.c_int32),
+                ("g_begin", C.c_int32), ("g_end", C.c_int32), ("zero_empty_below", C.c_int32), ("pad_", C.c_int32),
                 ("out", C.c_void_p), ("out2", C.c_void_p), ("row_scale", C.c_void_p), ("ldo", C.c_int64),
                 ("status", C.c_void_p), ("budget_ns", C.c_uint64)]
 
@@ -50,7 +50,7 @@ def check_status(device="cuda") -> None:
 
 
 def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=None, row_scale=None, ldo=0,
-            accumulate=False, a_cols=None, b_rows=None, b_cols=None, b_ld=None, groups=None, num_ctas=None):
+            accumulate=False, zero_empty_below=0, a_cols=None, b_rows=None, b_cols=None, b_ld=None, groups=None, num_ctas=None):
     lib = _native.load()
     assert a.dtype == torch.bfloat16 and b0.dtype == torch.bfloat16
     assert cu.dtype == torch.int32 and cu.is_contiguous()
@@ -61,6 +61,7 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
     args.G, args.N, args.K, args.M_w = G, N, K, M_w
     args.b_group_rows, args.accumulate = b_group_rows, 1 if accumulate else 0
     args.g_begin, args.g_end = g0, g1
+    args.zero_empty_below = zero_empty_below
     args.out, args.out2 = out.data_ptr(), _native.ptr(out2)
     args.row_scale, args.ldo = _native.ptr(row_scale), ldo
     args.status = _status(a.device).data_ptr()
@@ -118,14 +119,16 @@ def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None):
             b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
 
 
-def wgrad(x, dy, cu, out, accumulate=False, groups=None, num_ctas=None):
+def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num_ctas=None):
     """``out[g] (+)= x_g^T dy_g`` in fp32; ``out [G, in, out_dim]``.  ``dy`` may be a column slice
-    of a wider matrix (row pitch = ``dy.stride(0)``).  Groups without rows are left untouched."""
+    of a wider matrix (row pitch = ``dy.stride(0)``).  Groups without rows are left untouched,
+    except that with ``accumulate=False`` empty groups ``g < zero_empty_below`` are zeroed (local
+    experts that received no token must end with a zero gradient)."""
     G, M, N = out.shape
     assert out.dtype == torch.float32 and out.is_contiguous()
     assert x.shape[1] == M and dy.shape[1] == N and M % 128 == 0 and N % 256 == 0
     assert dy.stride(1) == 1 and x.stride(1) == 1
-    _launch(WGRAD, x, dy, None, cu, N=N, M_w=M, out=out, accumulate=accumulate,
+    _launch(WGRAD, x, dy, None, cu, N=N, M_w=M, out=out, accumulate=accumulate, zero_empty_below=zero_empty_below,
             b_rows=dy.shape[0], b_cols=N, b_ld=dy.stride(0), groups=groups, num_ctas=num_ctas)
 
 

@@ -75,11 +75,14 @@ def test_dgrad_and_wgrad(cuda_device):
     dWu = torch.full((G, H, Hp), 3.0, device="cuda")
     gg.wgrad(x, dgu[:, :Hp], cu, dWg, accumulate=False)
     gg.wgrad(x, dgu[:, Hp:], cu, dWu, accumulate=True)
+    dWz = torch.full((G, H, Hp), 3.0, device="cuda")
+    gg.wgrad(x, dgu[:, :Hp], cu, dWz, accumulate=False, zero_empty_below=G)
     torch.cuda.synchronize()
     gg.check_status()
     for gi, a, b in _group_slices(rpg):
         if a == b:
             assert (dWg[gi] == 3.0).all() and (dWu[gi] == 3.0).all(), "empty group's grads must stay untouched"
+            assert (dWz[gi] == 0.0).all(), "empty group must be zeroed when requested"
             continue
         assert _relerr(dA[a:b], dy[a:b].float() @ wd[gi].float().T) < 1e-2, f"group {gi}: dgrad"
         ref = dgu[a:b, :Hp].float() @ wg[gi].float().T + dgu[a:b, Hp:].float() @ wu[gi].float().T
