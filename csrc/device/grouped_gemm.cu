@@ -354,5 +354,6 @@ extern "C" int mep_grouped_gemm(int mode, const void* a, int64_t a_rows, int64_t
   }
 #undef MEP_GEMM_CASE
   MEP_CUDA_CHECK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;
 }

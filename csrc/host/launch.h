@@ -5,12 +5,14 @@
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <atomic>
 #include <string>
 #include "../mep_types.h"
 
 namespace mep {
 
 std::string& last_error();
+extern std::atomic<long long> g_launches;
 int set_error(const char* fmt, ...);
 
 #define MEP_CUDA_CHECK(expr)                                                              \
@@ -41,6 +43,7 @@ int launch_cooperative(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   if (smem > 16 * 1024)
     MEP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   MEP_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;
 }
 
@@ -53,6 +56,7 @@ int launch_plain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
   if (smem > 16 * 1024)
     MEP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   MEP_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;
 }
 
