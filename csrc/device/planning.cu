@@ -18,24 +18,11 @@
 //       slot; per token, later entries to an already used rank are marked duplicates and
 //       (primary, duplicates) groups are appended to the destination's staging tables.
 #include "prims.cuh"
+#include "planning_args.h"
 #include "../host/launch.h"
 #include <limits.h>
 
 namespace mep {
-
-struct PlanArgs {
-  const int32_t* topk;        // [N]
-  const int32_t* tpe;         // [E]
-  int32_t* dst;               // [N]
-  int32_t* cu_seqlens;        // [2epn]
-  int32_t* experts_to_copy;   // [R, epn]
-  int32_t* zero_fill;         // [2epn, 2]
-  int32_t* remote_stats;      // [2]
-};
-struct PlanArgsPack { PlanArgs a[MEP_MAX_VRANKS]; };
-
-constexpr int kPlanThreads = 1024;
-constexpr int kSmemECap = 8192;   // per-expert scratch lives in shared memory up to this E
 
 __device__ __forceinline__ int vload(const int* p) { return *(const volatile int*)p; }
 __device__ __forceinline__ void vstore(int* p, int v) { *(volatile int*)p = v; }
