@@ -49,7 +49,9 @@ constexpr int kBBytes = kBN * kBK * 2;            // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kAtomBytes = 64 * kBK * 2;          // one 64-wide MN-major atom: 64 k-rows x 128 B
 constexpr int kGemmThreads = 192;
-constexpr int kMaxGroups = 1024;
+constexpr int kMaxGroups = 256;
+constexpr int kSlabBytes = 32 * 128;             // epilogue staging: 32 rows x 128 B per warp and buffer
+constexpr int kStagingBytes = 4 * 2 * kSlabBytes;  // 4 epilogue warps x 2 buffers
 constexpr int kTmemCols = 512;
 
 struct TileInfo { int g, row0, m0, n0, kblocks; };
@@ -57,7 +59,7 @@ struct TileInfo { int g, row0, m0, n0, kblocks; };
 template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b0,
-                    const __grid_constant__ CUtensorMap tma_b1, GemmArgs args) {
+                    const __grid_constant__ CUtensorMap tma_b1, const __grid_constant__ CUtensorMap tma_out, GemmArgs args) {
   constexpr bool A_MN = MODE == GEMM_WGRAD;
   constexpr bool B_MN = MODE == GEMM_GATE_UP || MODE == GEMM_DOWN || MODE == GEMM_WGRAD;
   extern __shared__ unsigned char smem_raw[];
@@ -89,7 +91,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       s_start[G] = run;
       s_ntiles = run;
     }
-    tc::prefetch_tmap(&tma_a); tc::prefetch_tmap(&tma_b0); tc::prefetch_tmap(&tma_b1);
+    tc::prefetch_tmap(&tma_a); tc::prefetch_tmap(&tma_b0); tc::prefetch_tmap(&tma_b1); tc::prefetch_tmap(&tma_out);
   }
   if (warp == 1) { tc::tmem_alloc(&s_tmem_base, kTmemCols); tc::tmem_relinquish(); }
   tc::fence_before_sync();
@@ -206,6 +208,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // ---------------- epilogue warps (TMEM lane quarter = warp % 4)
     const int q = warp & 3;
     const int r_in_tile = q * 32 + lane;
+    // coalesced output: each warp transposes its 32-row slab through shared memory (128-byte
+    // swizzle) and one lane writes it with a TMA store, double-buffered per warp
+    const uint32_t stg = smem_u32(smem + (size_t)kStages * kStageBytes) + (uint32_t)(warp - 2) * 2 * kSlabBytes;
+    int chunk_no = 0;
     int tcnt = 0, gcur = 0; TileInfo ti;
     for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x, ++tcnt) {
       get_tile(t, gcur, ti);
@@ -254,43 +260,60 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           }
         }
       } else if (MODE == GEMM_WGRAD) {
-        float* orow = (float*)args.out + ((size_t)ti.g * args.M_w + ti.m0 + r_in_tile) * args.N + ti.n0;
+        const int orow0 = ti.g * args.M_w + ti.m0 + q * 32;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 8; ++c, ++chunk_no) {
+          const uint32_t buf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;
+          if (lane == 0) bulk_wait_read<1>();          // the store issued two chunks ago has read this buffer
+          __syncwarp();
           uint32_t r[32];
           tc::tmem_ld32(taddr + c * 32, r);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-            float4* p = reinterpret_cast<float4*>(orow + c * 32 + j * 4);
-            if (args.accumulate) { const float4 old = *p; v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w; }
-            *p = v;
+          for (int j = 0; j < 8; ++j)
+            tc::st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          tc::fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (args.accumulate) tc::tma_reduce_add_2d(&tma_out, buf, ti.n0 + c * 32, orow0);
+            else tc::tma_store_2d(&tma_out, buf, ti.n0 + c * 32, orow0);
+            bulk_commit();
           }
         }
       } else {
         const size_t row = (size_t)ti.row0 + r_in_tile;
-        __nv_bfloat16* orow = (__nv_bfloat16*)args.out + row * args.ldo + ti.n0;
         const float sc = (MODE == GEMM_DOWN && args.row_scale) ? args.row_scale[row] : 1.f;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          uint32_t r[32];
-          tc::tmem_ld32(taddr + c * 32, r);
+        for (int c = 0; c < 4; ++c, ++chunk_no) {       // 64 output columns (128 B of bf16) per chunk
+          const uint32_t buf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;
+          if (lane == 0) bulk_wait_read<1>();
+          __syncwarp();
+          uint32_t r[64];
+          tc::tmem_ld32(taddr + c * 64, r);
+          tc::tmem_ld32(taddr + c * 64 + 32, r + 32);
           tc::tmem_ld_wait();
-          uint32_t o[16];
+          uint32_t o[32];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < 32; ++j) {
             __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * sc, __uint_as_float(r[2 * j + 1]) * sc);
             o[j] = *reinterpret_cast<uint32_t*>(&h);
           }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) st_v4(orow + c * 32 + j * 8, make_int4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+          for (int j = 0; j < 8; ++j)
+            tc::st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          tc::fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tc::tma_store_2d(&tma_out, buf, ti.n0 + c * 64, ti.row0 + q * 32);
+            bulk_commit();
+          }
         }
       }
       tc::fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
+    if (lane == 0) bulk_wait_all<0>();       // shared memory must outlive the stores reading it
   }
 
   // ---------------- teardown: everyone joins, then the allocating warp frees TMEM
@@ -300,15 +323,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   if (warp == 1) tc::tmem_dealloc(tmem_base, kTmemCols);
 }
 
-static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
+static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows,
+                    bool f32 = false) {
   const DriverApi* d = driver(); if (!d) return -1;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const int es_bytes = f32 ? 4 : 2;
+  cuuint64_t strides[1] = {(cuuint64_t)ld * es_bytes};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t es[2] = {1, 1};
-  MEP_REQUIRE(((uintptr_t)base & 15) == 0 && (ld * 2) % 16 == 0 && ld >= cols,
+  MEP_REQUIRE(((uintptr_t)base & 15) == 0 && (ld * es_bytes) % 16 == 0 && ld >= cols,
               "gemm: tensor base/stride must be 16-byte aligned");
-  MEP_CU_CHECK(d->TensorMapEncodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+  MEP_CU_CHECK(d->TensorMapEncodeTiled(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
   return 0;
@@ -326,7 +351,7 @@ extern "C" int mep_grouped_gemm(int mode, const void* a, int64_t a_rows, int64_t
   using namespace mep;
   GemmArgs args = *args_in;
   MEP_REQUIRE(args.G >= 1 && args.G <= kMaxGroups, "gemm: G=%d out of range [1,%d]", args.G, kMaxGroups);
-  CUtensorMap ma, mb0, mb1;
+  CUtensorMap ma, mb0, mb1, mo;
   const bool b_mn = mode == GEMM_GATE_UP || mode == GEMM_DOWN || mode == GEMM_WGRAD;
   if (mode == GEMM_WGRAD) {
     MEP_REQUIRE(args.M_w % kBM == 0 && args.N % kBN == 0, "wgrad: weight shape [%d,%d] must be multiples of [128,256]", args.M_w, args.N);
@@ -340,12 +365,16 @@ extern "C" int mep_grouped_gemm(int mode, const void* a, int64_t a_rows, int64_t
   else      { if (make_map(&mb0, b0, b_rows, b_cols, b_ld, 64, kBN)) return -1; }
   if (b1) { if (make_map(&mb1, b1, b_rows, b_cols, b_ld, 64, b_mn ? 64 : kBN)) return -1; }
   else mb1 = mb0;
-  const size_t smem = (size_t)kStages * kStageBytes + 1024;
+  // output map: one 32-row x 128-byte box per epilogue warp and chunk
+  if (mode == GEMM_WGRAD) { if (make_map(&mo, args.out, (int64_t)args.G * args.M_w, args.N, args.N, 32, 32, true)) return -1; }
+  else if (mode == GEMM_GATE_UP) mo = ma;
+  else { if (make_map(&mo, args.out, a_rows, args.N, args.ldo, 64, 32)) return -1; }
+  const size_t smem = (size_t)kStages * kStageBytes + kStagingBytes + 1024;
   dim3 grid(num_ctas), block(kGemmThreads);
 #define MEP_GEMM_CASE(M)                                                                             \
   case M:                                                                                            \
     MEP_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    grouped_gemm_kernel<M><<<grid, block, smem, stream>>>(ma, mb0, mb1, args);                       \
+    grouped_gemm_kernel<M><<<grid, block, smem, stream>>>(ma, mb0, mb1, mo, args);                       \
     break;
   switch (mode) {
     MEP_GEMM_CASE(GEMM_GATE_UP) MEP_GEMM_CASE(GEMM_DOWN) MEP_GEMM_CASE(GEMM_DGRAD)
