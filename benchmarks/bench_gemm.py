@@ -34,6 +34,8 @@ def main():
     ap.add_argument("--Hp", type=int, default=2048)
     ap.add_argument("--groups", type=int, default=32)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--only", default="", help="comma-separated subset of modes")
     a = ap.parse_args()
     G, H, Hp, rows = a.groups, a.H, a.Hp, a.rows
     per = rows // G // 128 * 128
@@ -62,13 +64,19 @@ def main():
         "wgrad_gate": (lambda: gg.wgrad(x, gu[:, :Hp], cu, dWg), 2 * rows * H * Hp),
         "wgrad_down": (lambda: gg.wgrad(act, y, cu, dWd), 2 * rows * H * Hp),
     }
+    only = [m for m in a.only.split(",") if m]
     for name, (fn, flops) in cases.items():
-        ms = timed(fn, iters=a.iters)
+        if only and name not in only:
+            continue
+        ms = timed(fn, warmup=a.warmup, iters=a.iters)
         tf = flops / ms / 1e9
         row = {"mode": name, "ms": round(ms, 4), "tflops": round(tf, 1)}
         if peak:
             row["frac_of_measured_cublas_peak"] = round(tf / peak, 3)
         print(json.dumps(row))
+    if only:
+        gg.check_status()
+        return
     t = torch.matmul  # cuBLAS reference point at a comparable dense shape
     a_ = torch.randn(rows, H, **bf); b_ = torch.randn(H, Hp, **bf)
     ms = timed(lambda: t(a_, b_), iters=a.iters)

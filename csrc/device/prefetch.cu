@@ -37,11 +37,20 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
   const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x;
   const int R = c.R, epn = c.epn, lo = c.rank * epn;
 
-  if (tid == 0) s_n = 0;
-  __syncthreads();
-  for (int i = tid; i < R * epn; i += nt) {
-    const int e = a.etc[i];
-    if (e >= lo && e < lo + epn && i / epn != c.rank) s_list[atomicAdd(&s_n, 1)] = i;
+  // Slot list in ascending (rank, slot) order. Every CTA must build the IDENTICAL list, because
+  // work unit u is mapped to list entry u / chunks_per_slot on whichever CTA owns u: one warp
+  // compacts with ballots (no atomics, whose arrival order could differ between CTAs).
+  if (tid < 32) {
+    int n = 0;
+    for (int i0 = 0; i0 < R * epn; i0 += 32) {
+      const int i = i0 + tid;
+      bool has = false;
+      if (i < R * epn) { const int e = a.etc[i]; has = e >= lo && e < lo + epn && i / epn != c.rank; }
+      const unsigned bal = __ballot_sync(0xffffffffu, has);
+      if (has) s_list[n + __popc(bal & lanemask_lt())] = i;
+      n += __popc(bal);
+    }
+    if (tid == 0) s_n = n;
   }
   __syncthreads();
   const int nslots = s_n;

@@ -108,7 +108,13 @@ int mep_chunk_create(int dev, size_t bytes, int kind, void** chunk_out, unsigned
   MEP_REQUIRE(bytes > 0 && bytes % gran == 0, "chunk size %zu is not a multiple of the granularity %zu", bytes, gran);
   LocalChunk* c = new LocalChunk{dev, bytes, kind, 0, false};
   CUresult r = d->MemCreate(&c->handle, bytes, &p, 0);
-  if (r != CUDA_SUCCESS) { delete c; MEP_CU_CHECK(r); }
+  if (r != CUDA_SUCCESS) {
+    delete c;
+    size_t fr = 0, tot = 0; cudaMemGetInfo(&fr, &tot);
+    const char* es = nullptr; d->GetErrorString(r, &es);
+    return set_error("cuMemCreate(%zu bytes) failed: %s (device %d: %zu MiB free of %zu MiB)", bytes, es ? es : "?", dev,
+                     fr >> 20, tot >> 20);
+  }
   c->handle_live = true;
   memset(shareable, 0, 64);
   if (kind == kHandleFabric) {

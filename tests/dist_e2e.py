@@ -22,6 +22,35 @@ from moonep_b200.sim import plan_cluster, dup_table_from_arrays, ops as simops  
 from gpu_helpers import traceable_hidden, defined_rows  # noqa: E402
 
 
+class StageFailed(Exception):
+    pass
+
+
+ERRORS = []
+
+
+def chk(cond, msg):
+    if not bool(cond):
+        ERRORS.append(str(msg))
+
+
+def safe_check(buf):
+    try:
+        buf.check()
+    except Exception as exc:  # a bounded wait expired on this rank: report it collectively
+        ERRORS.append(f"{type(exc).__name__}: {exc}")
+
+
+def stage(name):
+    """Collective: every rank learns whether ANY rank failed a check, so that all of them stop
+    together between steps (a rank must never exit while peers still touch its memory)."""
+    torch.cuda.synchronize()
+    ok = torch.tensor([0 if ERRORS else 1], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok) == 0:
+        raise StageFailed(name)
+
+
 def main():
     dist.init_process_group("nccl")
     rank, R = dist.get_rank(), dist.get_world_size()
@@ -31,6 +60,30 @@ def main():
     E = R * epn
     Hp = 128
     buf = Buffer(S, H, K, E, R, num_sms=16, token_padding=pad)
+    pools = None
+    try:
+        pools = run_scenario(buf, rank, R, dev, S, H, K, epn, pad, E, Hp)
+        failed = None
+    except StageFailed as exc:
+        failed = str(exc)
+    # every rank reaches this point with no kernel in flight on any peer
+    torch.cuda.synchronize()
+    dist.barrier()
+    if pools is not None:
+        pools.destroy()
+    buf.destroy()
+    dist.barrier()
+    if failed is not None:
+        for e in ERRORS:
+            print(f"[dist_e2e] rank {rank}: FAILED in stage '{failed}': {e}", flush=True)
+        dist.destroy_process_group()
+        sys.exit(1)
+    if rank == 0:
+        print(f"[dist_e2e] PASS on {R} ranks")
+    dist.destroy_process_group()
+
+
+def run_scenario(buf, rank, R, dev, S, H, K, epn, pad, E, Hp):
 
     topk_all = [routing.lognormal_topk(S, K, E, R, 1.5, 7, r)[0] for r in range(R)]
     cp = plan_cluster(np.stack([t.numpy() for t in topk_all]), E, pad)
@@ -43,25 +96,26 @@ def main():
     # ---- fresh dispatch, sync
     h1, w1, cu1, plan1 = buf.dispatch(hidden, weights, topk, tpe)
     torch.cuda.synchronize()
-    buf.check()
-    assert torch.equal(plan1.dst.cpu().long(), torch.from_numpy(cp.dst[rank])), "dst"
-    assert torch.equal(cu1.cpu().long(), torch.from_numpy(cp.cu_seqlens[rank])), "cu_seqlens"
-    assert torch.equal(plan1.experts_to_copy.cpu().long(), torch.from_numpy(cp.experts_to_copy)), "experts_to_copy"
-    assert torch.equal(plan1.remote_stats.cpu().long(), torch.from_numpy(cp.remote_stats[rank])), "remote_stats"
+    safe_check(buf)
+    chk(torch.equal(plan1.dst.cpu().long(), torch.from_numpy(cp.dst[rank])), "dst")
+    chk(torch.equal(cu1.cpu().long(), torch.from_numpy(cp.cu_seqlens[rank])), "cu_seqlens")
+    chk(torch.equal(plan1.experts_to_copy.cpu().long(), torch.from_numpy(cp.experts_to_copy)), "experts_to_copy")
+    chk(torch.equal(plan1.remote_stats.cpu().long(), torch.from_numpy(cp.remote_stats[rank])), "remote_stats")
     got = dup_table_from_arrays(plan1.dup_groups.cpu().numpy(), plan1.dup_loffs.cpu().numpy(), plan1.dup_counts.cpu().numpy())
-    assert got == {k: tuple(sorted(v)) for k, v in cp.dup_tables[rank].items()}, "dup tables"
+    chk(got == {k: tuple(sorted(v)) for k, v in cp.dup_tables[rank].items()}, "dup tables")
     eh, ew = simops.dispatch(cp, [h.view(torch.int16).float() for h in hidden_all],
                              [w.view(torch.int32).float() for w in weights_all], fill=-1.0)
     m = defined_rows(cp, rank)
-    assert torch.equal(h1.cpu().view(torch.int16).float()[m], eh[rank][m]), "dispatched rows"
-    assert torch.equal(w1.cpu().view(torch.int32).float()[m], ew[rank][m]), "dispatched weights"
+    chk(torch.equal(h1.cpu().view(torch.int16).float()[m], eh[rank][m]), "dispatched rows")
+    chk(torch.equal(w1.cpu().view(torch.int32).float()[m], ew[rank][m]), "dispatched weights")
+    stage("fresh dispatch")
     snap = plan1.clone()
 
     # ---- async must equal sync
     h2, w2, cu2, plan2, ev = buf.dispatch(hidden, weights, topk, tpe, async_finish=True)
     ev.wait(torch.cuda.current_stream())
     torch.cuda.synchronize()
-    assert torch.equal(h2[m.to(dev)], h1[m.to(dev)]) and torch.equal(cu2, cu1) and torch.equal(plan2.dst, plan1.dst)
+    chk(torch.equal(h2[m.to(dev)], h1[m.to(dev)]) and torch.equal(cu2, cu1) and torch.equal(plan2.dst, plan1.dst), 'torch.equal(h2[m.to(dev)], h1[m.to(dev)]) and torch.equal(cu')
 
     # ---- pools, prefetch (sync + async), untouched slots when not requested
     pools = ExpertPools(epn, (H, Hp), (H, Hp), (Hp, H), group=None, with_grads=True)
@@ -73,7 +127,7 @@ def main():
     dist.barrier()
     buf.prefetch_weight(plan=snap, **pools.prefetch_kwargs())
     torch.cuda.synchronize()
-    buf.check()
+    safe_check(buf)
     dist.barrier()
     for i, n in enumerate(("gate", "up", "down")):
         shape = pools.local_weight(n)[0].shape
@@ -82,34 +136,36 @@ def main():
             slot = pools.prefetch_view(n)[rank, b]
             if e >= 0:
                 want = (float(e) * 3 + i + torch.arange(slot.numel(), device=dev).view(shape) % 5).to(torch.bfloat16)
-                assert torch.equal(slot, want), f"{n}: slot {b} does not hold expert {e}"
+                chk(torch.equal(slot, want), f"{n}: slot {b} does not hold expert {e}")
             else:
-                assert (slot == -9.0).all(), f"{n}: unused slot {b} was written"
+                chk((slot == -9.0).all(), f"{n}: unused slot {b} was written")
+    stage("prefetch")
     # compute view = [local | prefetch]
     cv = pools.compute_weight("gate")
-    assert cv.shape[0] == 2 * epn and cv[:epn].data_ptr() == pools.local_weight("gate").data_ptr()
-    assert cv[epn:].data_ptr() == pools.prefetch_view("gate")[rank].data_ptr()
+    chk(cv.shape[0] == 2 * epn and cv[:epn].data_ptr() == pools.local_weight("gate").data_ptr(), 'cv.shape[0] == 2 * epn and cv[:epn].data_ptr() == pools.loca')
+    chk(cv[epn:].data_ptr() == pools.prefetch_view("gate")[rank].data_ptr(), 'cv[epn:].data_ptr() == pools.prefetch_view("gate")[rank].dat')
 
     # ---- plan reuse (backward of combine): no planning, plan untouched
     before = snap.clone()
     hr, wr, cur, pr = buf.dispatch(hidden, plan=snap)
     torch.cuda.synchronize()
-    assert wr is None and cur is None and pr is snap
-    assert torch.equal(hr[m.to(dev)], h1[m.to(dev)])
+    chk(wr is None and cur is None and pr is snap, 'wr is None and cur is None and pr is snap')
+    chk(torch.equal(hr[m.to(dev)], h1[m.to(dev)]), 'torch.equal(hr[m.to(dev)], h1[m.to(dev)])')
     for f in ("dst", "dup_groups", "dup_loffs", "dup_counts"):
-        assert torch.equal(getattr(snap, f), getattr(before, f))
+        chk(torch.equal(getattr(snap, f), getattr(before, f)), 'torch.equal(getattr(snap, f), getattr(before, f))')
+    stage("plan reuse")
 
     # ---- combine: identity FFN, zero-copy and copy paths agree; weights gather exact
     hz, wz, _, planz = buf.dispatch(hidden, weights, topk, tpe, zero_copy=True, router_weights_zero_copy=True)
-    assert hz.data_ptr() == buf.hidden_nvsh_buffer_view.data_ptr()
+    chk(hz.data_ptr() == buf.hidden_nvsh_buffer_view.data_ptr(), 'hz.data_ptr() == buf.hidden_nvsh_buffer_view.data_ptr()')
     oz, wsk, _ = buf.combine(plan=planz, hidden_nvsh=hz, route_weights_nvs=wz, zero_copy=True, router_weights_zero_copy=True)
     torch.cuda.synchronize()
-    assert torch.equal(wsk.view(torch.int32), weights.view(torch.int32)), "gathered weights"
+    chk(torch.equal(wsk.view(torch.int32), weights.view(torch.int32)), "gathered weights")
     hc, wc, _, planc = buf.dispatch(hidden, weights, topk, tpe)
     oc, _, evc = buf.combine(plan=planc, hidden_nvsh=hc, async_finish=True)
     evc.wait(torch.cuda.current_stream())
     torch.cuda.synchronize()
-    assert torch.equal(oc, oz), "copy vs zero-copy combine"
+    chk(torch.equal(oc, oz), "copy vs zero-copy combine")
     # numeric combine check with small integers
     y = torch.zeros(cp.NvS, H, dtype=torch.bfloat16)
     y[:] = ((torch.arange(cp.NvS) % 7) + 1 + rank)[:, None].to(torch.bfloat16)
@@ -121,7 +177,8 @@ def main():
     on, _, _ = buf.combine(plan=snap, hidden_nvsh=y.to(dev))
     torch.cuda.synchronize()
     eo, _ = simops.combine(cp, ys)
-    assert torch.equal(on.cpu().float(), eo[rank]), "combine sum"
+    chk(torch.equal(on.cpu().float(), eo[rank]), "combine sum")
+    stage("combine")
 
     # ---- reduce_grad
     g = torch.Generator().manual_seed(11)
@@ -135,27 +192,24 @@ def main():
     ev = buf.reduce_grad(plan=snap, async_finish=True, **pools.reduce_kwargs())
     ev.wait(torch.cuda.current_stream())
     torch.cuda.synchronize()
-    buf.check()
+    safe_check(buf)
     dist.barrier()
     for n in ("gate", "up", "down"):
         el = [x.clone() for x in lg_all[n]]
         er = [x.clone() for x in rb_all[n]]
         simops.reduce_grad(cp, el, er)
-        assert torch.equal(pools.local_grad(n).cpu(), el[rank]), f"{n}: reduced grads (bitwise)"
-        assert torch.equal(pools.reduce_view(n)[rank].cpu(), er[rank]), f"{n}: reduce slots"
+        chk(torch.equal(pools.local_grad(n).cpu(), el[rank]), f"{n}: reduced grads (bitwise)")
+        chk(torch.equal(pools.reduce_view(n)[rank].cpu(), er[rank]), f"{n}: reduce slots")
+    stage("reduce_grad")
 
     # ---- repeated ops keep working (barrier epochs), then teardown
     for _ in range(3):
         buf.dispatch(hidden, weights, topk, tpe, zero_copy=True)
         buf.combine(plan=snap, hidden_nvsh=buf.hidden_nvsh_buffer_view, zero_copy=True)
     torch.cuda.synchronize()
-    buf.check()
-    pools.destroy()
-    buf.destroy()
-    dist.barrier()
-    if rank == 0:
-        print(f"[dist_e2e] PASS on {R} ranks")
-    dist.destroy_process_group()
+    safe_check(buf)
+    stage("repeat")
+    return pools
 
 
 if __name__ == "__main__":
