@@ -1,0 +1,268 @@
+"""Reference arm: the same MoE-layer training step as bench.py, but every communication op
+goes through the UNMODIFIED reference package's public API (``moonep.Buffer``: dispatch,
+prefetch_weight, combine, reduce_grad) and the expert FFN -- which the reference leaves to the
+integrating framework -- is plain PyTorch (``torch._grouped_mm`` library kernels driven by the
+device-side ``cu_seqlens``; per-group ``torch.matmul`` if that op is missing).  Same shapes,
+routing generator, loss, optimizer step, timing rules and JSON line as the main arm.
+Imported only by bench_reference.py after ``baseline/_ref`` has been put on ``sys.path``.
+"""
+
+import json
+import os
+import time
+
+import torch
+import torch.distributed as dist
+
+CFG = {"deepseek_v3": dict(H=7168, Hp=2048, K=8, epn=32, S=4096)}
+SWEEP = (0.0, 0.5, 1.0, 2.0, 3.0)
+
+
+def _gmm(a, b, offs):
+    """a [M, K] x b [G, K, N] grouped by row offsets -> [M, N] (rows past offs[-1] undefined)."""
+    if hasattr(torch, "_grouped_mm"):
+        return torch._grouped_mm(a, b, offs=offs)
+    out = torch.zeros(a.shape[0], b.shape[2], dtype=a.dtype, device=a.device)
+    s = 0
+    for g, e in enumerate(offs.tolist()):
+        if e > s:
+            out[s:e] = a[s:e] @ b[g]
+        s = e
+    return out
+
+
+def _gmm_wgrad(x, dy, offs, G):
+    """per group x_g^T dy_g -> [G, K, N]."""
+    if hasattr(torch, "_grouped_mm"):
+        return torch._grouped_mm(x.t(), dy, offs=offs)
+    out = torch.zeros(G, x.shape[1], dy.shape[1], dtype=x.dtype, device=x.device)
+    s = 0
+    for g, e in enumerate(offs.tolist()):
+        if e > s:
+            out[g] = x[s:e].t() @ dy[s:e]
+        s = e
+    return out
+
+
+def run(args):
+    from moonep import Buffer
+    from moonep.buffer import create_nvl_dist_tensor
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    dist.init_process_group("nccl")
+    dev = torch.device("cuda", local)
+    c = CFG[args.model]
+    S, H, Hp, K, epn = c["S"], c["H"], c["Hp"], c["K"], c["epn"]
+    E, R = epn * world, world
+    buffer = Buffer(S=S, H=H, K=K, E=E, num_ep_ranks=R, num_sms=32, token_padding=128)
+
+    def pool(rows, cols, dtype):
+        t = create_nvl_dist_tensor([2 * epn, rows, cols], dtype, rank, R)
+        return t.view(R, 2 * epn, rows, cols)
+
+    g = torch.Generator(device=dev).manual_seed(rank)
+    shapes = {"gate": (H, Hp), "up": (H, Hp), "down": (Hp, H)}
+    W, Gd = {}, {}
+    for n, (r_, c_) in shapes.items():
+        W[n] = pool(r_, c_, torch.bfloat16)
+        W[n][rank, :epn].copy_((torch.randn(epn, r_, c_, device=dev, generator=g) * 0.02).to(torch.bfloat16))
+        Gd[n] = pool(r_, c_, torch.float32)
+        Gd[n][rank].zero_()
+    gs = torch.Generator(device=dev).manual_seed(0)
+    router = (torch.randn(H, E, device=dev, generator=gs) * 0.02).to(torch.bfloat16).requires_grad_(True)
+    bias_base = torch.randn(E, device=dev, generator=torch.Generator(device=dev).manual_seed(1234)).float()
+    state = {"bias": bias_base * 0.0}
+    torch.cuda.synchronize()
+    dist.barrier()
+
+    def route(x):
+        logits = (x @ router).float() + state["bias"]
+        probs = torch.softmax(logits, dim=-1)
+        w, topk = torch.topk(probs, K, dim=-1)
+        w = (w / w.sum(dim=-1, keepdim=True)).contiguous()
+        topk = topk.to(torch.int32).contiguous()
+        tpe = torch.zeros(E, dtype=torch.int32, device=dev)
+        tpe.scatter_add_(0, topk.reshape(-1).long(), torch.ones(topk.numel(), dtype=torch.int32, device=dev))
+        return w, topk, tpe
+
+    def prefetch_kwargs():
+        kw = {}
+        for n in shapes:
+            kw[f"local_{n}_weight"] = W[n][rank, :epn]
+            kw[f"{n}_prefetch_buffer"] = W[n][:, epn:]
+        return kw
+
+    def reduce_kwargs():
+        kw = {}
+        for n in shapes:
+            kw[f"local_{n}_grad"] = Gd[n][rank, :epn]
+            kw[f"{n}_reduce_buffer"] = Gd[n][:, epn:]
+        return kw
+
+    class MoE(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, hidden, w_sk, topk, tpe):
+            x, w_nvs, cu, plan = buffer.dispatch(hidden, w_sk, topk, tpe)
+            buffer.prefetch_weight(plan=plan, **prefetch_kwargs())
+            Wg, Wu, Wd = W["gate"][rank], W["up"][rank], W["down"][rank]
+            gp, up = _gmm(x, Wg, cu), _gmm(x, Wu, cu)
+            act = torch.nn.functional.silu(gp.float()) * up.float() * w_nvs[:, None]
+            act = act.to(torch.bfloat16)
+            y = _gmm(act, Wd, cu)
+            out, _, _ = buffer.combine(plan=plan, hidden_nvsh=y)
+            ctx.saved = (plan, cu, x, w_nvs, act, gp, up)
+            return out
+
+        @staticmethod
+        def backward(ctx, grad_out):
+            plan, cu, x, w_nvs, act, gp, up = ctx.saved
+            Wg, Wu, Wd = W["gate"][rank], W["up"][rank], W["down"][rank]
+            dy, _, _, _ = buffer.dispatch(grad_out.contiguous(), plan=plan)
+            dA = _gmm(dy, Wd.transpose(1, 2), cu).float()
+            Gd["down"][rank].copy_(_gmm_wgrad(act, dy, cu, 2 * epn))
+            gf, uf = gp.float(), up.float()
+            sig = torch.sigmoid(gf)
+            silu = gf * sig
+            dw = (dA * silu * uf).sum(dim=1)
+            d = dA * w_nvs[:, None]
+            dg = (d * uf * sig * (1 + gf * (1 - sig))).to(torch.bfloat16)
+            du = (d * silu).to(torch.bfloat16)
+            dx = _gmm(dg, Wg.transpose(1, 2), cu) + _gmm(du, Wu.transpose(1, 2), cu)
+            Gd["gate"][rank].copy_(_gmm_wgrad(x, dg, cu, 2 * epn))
+            Gd["up"][rank].copy_(_gmm_wgrad(x, du, cu, 2 * epn))
+            gh, gw, _ = buffer.combine(plan=plan, hidden_nvsh=dx, route_weights_nvs=dw.contiguous())
+            if R > 1:
+                buffer.reduce_grad(plan=plan, **reduce_kwargs())
+            return gh, gw, None, None
+
+    lr = 1e-3
+
+    def step(x):
+        x.requires_grad_(True)
+        w, topk, tpe = route(x)
+        y = MoE.apply(x, w, topk, tpe)
+        loss = (y.float() ** 2).mean()
+        loss.backward()
+        with torch.no_grad():
+            for n in shapes:
+                p = W[n][rank, :epn]
+                p.copy_((p.float() - lr * Gd[n][rank, :epn]).to(torch.bfloat16))
+            router.add_(router.grad.to(router.dtype), alpha=-lr)
+            router.grad = None
+        x.grad = None
+        return loss.detach()
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def mx(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def maxvio_of(tpe):
+        t = tpe.clone().double()
+        if world > 1:
+            dist.all_reduce(t)
+        return float(t.max() / t.mean() - 1.0)
+
+    def calibrate(x, target):
+        def mv(scale):
+            state["bias"] = bias_base * scale
+            with torch.no_grad():
+                return maxvio_of(route(x)[2])
+        floor = mv(0.0)
+        if target <= floor:
+            state["bias"] = bias_base * 0.0
+            return floor
+        lo, hi, best = 1e-3, 50.0, (0.0, floor)
+        for _ in range(40):
+            mid = (lo * hi) ** 0.5
+            v = mv(mid)
+            if abs(v - target) < abs(best[1] - target):
+                best = (mid, v)
+            if abs(v - target) <= max(0.02 * target, 0.005):
+                break
+            lo, hi = (mid, hi) if v < target else (lo, mid)
+        state["bias"] = bias_base * best[0]
+        return best[1]
+
+    gen = torch.Generator().manual_seed(100 + rank)
+    host = [torch.randn(S, H, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(2)]
+    devb = [b.cuda() for b in host]
+    realised = calibrate(devb[0], args.maxvio)
+    W_ = max(3, args.warmup)
+    for _ in range(W_):
+        step(devb[0].detach())
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(devb[i % 2].detach())
+    e1.record()
+    sync()
+    ms = mx(e0.elapsed_time(e1) / args.steps)
+    sync()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        lv = step(host[i % 2].to("cuda", non_blocking=True)).item()
+    sync()
+    e2e_ms = mx((time.perf_counter() - t0) * 1e3 / args.steps)
+    sweep = []
+    if not args.no_sweep:
+        for mv in SWEEP:
+            real = calibrate(devb[0], mv)
+            step(devb[0].detach())
+            sync()
+            e0.record()
+            for i in range(3):
+                step(devb[i % 2].detach())
+            e1.record()
+            sync()
+            sms = mx(e0.elapsed_time(e1) / 3)
+            with torch.no_grad():
+                w, topk, tpe = route(devb[0])
+
+            def comm():
+                h, wn, cu, plan = buffer.dispatch(devb[0], w, topk, tpe, zero_copy=True, router_weights_zero_copy=True)
+                if world > 1:
+                    buffer.prefetch_weight(plan=plan, **prefetch_kwargs())
+                buffer.combine(plan=plan, hidden_nvsh=h, route_weights_nvs=wn, zero_copy=True, router_weights_zero_copy=True)
+
+            for _ in range(3):
+                comm()
+            sync()
+            e0.record()
+            for _ in range(5):
+                comm()
+            e1.record()
+            sync()
+            sweep.append({"maxvio_target": mv, "maxvio": round(real, 3), "step_ms": round(sms, 3),
+                          "dispatch_combine_us": round(mx(e0.elapsed_time(e1) / 5 * 1e3), 1)})
+    tokens = S * world
+    out = {"metric": "moe_layer_train_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+           "n_gpus": world, "steps": args.steps, "warmup": W_, "ms_per_step": ms, "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+           "config": {"model": f"{args.model}-shape MoE layer (H={H}, H'={Hp}, K={K}, E={E}, epn={epn})",
+                      "global_batch": tokens, "seq_len": S, "parallelism": f"ep{world}", "token_padding": 128,
+                      "num_sms": 32, "maxvio_target": args.maxvio, "maxvio": round(realised, 3),
+                      "comm": "reference moonep.Buffer (unmodified)", "expert_ffn": "torch._grouped_mm" if hasattr(torch, "_grouped_mm") else "torch.matmul per group"},
+           "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                   "h2d_bytes_per_step": S * H * 2, "d2h_bytes_per_step": 4},
+           "loss": lv, "maxvio_sweep": sweep}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    buffer.destroy()
+    dist.destroy_process_group()

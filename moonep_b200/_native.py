@@ -101,6 +101,20 @@ def load(build_if_missing: bool = True):
             "the CUDA kernels are the only implementation of the device ops")
     lib = C.CDLL(str(p), mode=C.RTLD_GLOBAL)
     lib.mep_last_error.restype = C.c_char_p
+    lib.mep_launch_count.restype = C.c_longlong
+    # size_t / pointer arguments must not be squeezed through the default C int conversion
+    vp, sz, i32 = C.c_void_p, C.c_size_t, C.c_int
+    lib.mep_vmm_granularity.argtypes = [i32, i32, C.POINTER(sz)]
+    lib.mep_multicast_granularity.argtypes = [i32, i32, i32, sz, C.POINTER(sz)]
+    lib.mep_chunk_create.argtypes = [i32, sz, i32, C.POINTER(vp), C.POINTER(C.c_ubyte)]
+    lib.mep_chunk_release.argtypes = [vp]
+    lib.mep_map_all.argtypes = [i32, i32, i32, vp, C.POINTER(C.c_ubyte), C.POINTER(vp), C.POINTER(C.c_ulonglong)]
+    lib.mep_unmap_all.argtypes = [vp]
+    lib.mep_mc_create.argtypes = [i32, i32, sz, i32, C.POINTER(vp), C.POINTER(C.c_ubyte)]
+    lib.mep_mc_import.argtypes = [i32, sz, i32, C.POINTER(C.c_ubyte), C.POINTER(vp)]
+    lib.mep_mc_add_device.argtypes = [vp]
+    lib.mep_mc_bind_map.argtypes = [vp, vp, C.POINTER(C.c_ulonglong)]
+    lib.mep_mc_destroy.argtypes = [vp]
     _LIB = lib
     return lib
 

@@ -168,7 +168,7 @@ class SymmetricHeap:
                                f"({[int.from_bytes(s, 'little') for s in sizes]})")
         chunk = C.c_void_p()
         share = (C.c_ubyte * 64)()
-        _native.check(lib.mep_chunk_create(dev, h.chunk_bytes, kind, C.byref(chunk), share), "chunk create")
+        _native.check(lib.mep_chunk_create(dev, h.chunk_bytes, kind, C.byref(chunk), share), "chunk create")  # argtypes: size_t
         h._chunk = chunk
         my_fd = -1
         try:
