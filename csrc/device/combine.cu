@@ -26,6 +26,55 @@ __device__ __forceinline__ int4 pack_bf16x8(const float* acc) {
   return o;
 }
 
+
+// Sum `np` bf16 rows (row pointers held by the lanes flagged in `prim`, ascending lane order)
+// into one bf16 row. PB rows x CB 16-byte column chunks are loaded per lane before any add, so
+// PB*CB loads are in flight per lane whatever the number of rows; fp32 accumulation, one
+// rounding. `PEER` selects loads that bypass L1 for rows other GPUs may have written.
+template <int PB, int CB, bool PEER>
+__device__ __forceinline__ void reduce_rows(const char* myrow, unsigned prim, int np, char* orow, int nvec, int lane) {
+  for (int v0 = 0; v0 < nvec; v0 += 32 * CB) {
+    float acc[CB][8];
+#pragma unroll
+    for (int cx = 0; cx < CB; ++cx)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[cx][i] = 0.f;
+    unsigned rest = prim;
+    for (int j0 = 0; j0 < np; j0 += PB) {
+      int4 x[PB][CB];
+#pragma unroll
+      for (int j = 0; j < PB; ++j) {
+        const bool on = j0 + j < np;
+        const int src = on ? __ffs(rest) - 1 : 0;
+        if (on) rest &= rest - 1;
+        const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)myrow, src);
+#pragma unroll
+        for (int cx = 0; cx < CB; ++cx) {
+          const int v = v0 + cx * 32 + lane;
+          x[j][cx] = make_int4(0, 0, 0, 0);
+          if (on && v < nvec) x[j][cx] = PEER ? ld_peer_v4(rp + (size_t)v * 16) : ld_nc_v4(rp + (size_t)v * 16);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < PB; ++j)
+#pragma unroll
+        for (int cx = 0; cx < CB; ++cx) acc_bf16x8(acc[cx], x[j][cx]);
+    }
+#pragma unroll
+    for (int cx = 0; cx < CB; ++cx) {
+      const int v = v0 + cx * 32 + lane;
+      if (v < nvec) st_na_v4(orow + (size_t)v * 16, pack_bf16x8(acc[cx]));
+    }
+  }
+}
+
+template <bool PEER>
+__device__ __forceinline__ void reduce_rows_auto(const char* myrow, unsigned prim, int np, char* orow, int nvec, int lane) {
+  if (np <= 2) reduce_rows<2, 4, PEER>(myrow, prim, np, orow, nvec, lane);
+  else if (np <= 4) reduce_rows<4, 2, PEER>(myrow, prim, np, orow, nvec, lane);
+  else reduce_rows<8, 1, PEER>(myrow, prim, np, orow, nvec, lane);
+}
+
 // ------------------------------------------------------------------ dup_reduce
 struct DupArgs { __nv_bfloat16* buf; const int32_t* dup_groups; const int32_t* dup_loffs; const int32_t* dup_counts; };
 struct DupArgsPack { DupArgs a[MEP_MAX_VRANKS]; };
@@ -42,16 +91,15 @@ __global__ void __launch_bounds__(256) dup_reduce_kernel(MepCtxPack P, DupArgsPa
   for (int g = gw; g < ng; g += nw) {
     const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
     if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
-    char* prow = base + (size_t)p * row_bytes;
-    for (int v = lane; v < nvec; v += 32) {
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      acc_bf16x8(acc, ld_nc_v4(prow + (size_t)v * 16));
-      for (int j = 0; j < n; ++j) {
-        const int q = a.dup_loffs[st + j];
-        if ((unsigned)q < (unsigned)c.NvS) acc_bf16x8(acc, ld_nc_v4(base + (size_t)q * row_bytes + (size_t)v * 16));
-      }
-      st_v4(prow + (size_t)v * 16, pack_bf16x8(acc));
+    // lane 0 holds the primary row, lanes 1..n the duplicates in table order
+    const char* myrow = nullptr;
+    if (lane == 0) myrow = base + (size_t)p * row_bytes;
+    else if (lane <= n) {
+      const int q = a.dup_loffs[st + lane - 1];
+      if ((unsigned)q < (unsigned)c.NvS) myrow = base + (size_t)q * row_bytes;
     }
+    const unsigned rows = __ballot_sync(0xffffffffu, myrow != nullptr);
+    reduce_rows_auto<false>(myrow, rows, __popc(rows), base + (size_t)p * row_bytes, nvec, lane);
   }
 }
 
@@ -65,7 +113,6 @@ struct CombineArgs {
 struct CombineArgsPack { CombineArgs a[MEP_MAX_VRANKS]; };
 
 constexpr int kCombThreads = 512;
-constexpr int kCombBatch = 4;      // primaries loaded per batch (x2 column chunks per lane)
 
 __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, CombineArgsPack A) {
   const MepRankCtx& c = *P.ctx[blockIdx.y];
@@ -89,30 +136,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, 
       if (dval >= 0) myrow = peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes;
     }
     const unsigned prim = __ballot_sync(0xffffffffu, myrow != nullptr);
-    const int np = __popc(prim);
-    char* orow = (char*)a.out + (size_t)s * row_bytes;
-    for (int v0 = 0; v0 < nvec; v0 += 64) {
-      const int va = v0 + lane, vb = v0 + 32 + lane;
-      float acc0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, acc1[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      unsigned rest = prim;
-      for (int j0 = 0; j0 < np; j0 += kCombBatch) {
-        int4 x0[kCombBatch], x1[kCombBatch];
-#pragma unroll
-        for (int j = 0; j < kCombBatch; ++j) {
-          const bool on = j0 + j < np;
-          const int src = on ? __ffs(rest) - 1 : 0;
-          if (on) rest &= rest - 1;
-          const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)myrow, src);
-          x0[j] = make_int4(0, 0, 0, 0); x1[j] = make_int4(0, 0, 0, 0);
-          if (on && va < nvec) x0[j] = ld_peer_v4(rp + (size_t)va * 16);
-          if (on && vb < nvec) x1[j] = ld_peer_v4(rp + (size_t)vb * 16);
-        }
-#pragma unroll
-        for (int j = 0; j < kCombBatch; ++j) { acc_bf16x8(acc0, x0[j]); acc_bf16x8(acc1, x1[j]); }
-      }
-      if (va < nvec) st_na_v4(orow + (size_t)va * 16, pack_bf16x8(acc0));
-      if (vb < nvec) st_na_v4(orow + (size_t)vb * 16, pack_bf16x8(acc1));
-    }
+    reduce_rows_auto<true>(myrow, prim, __popc(prim), (char*)a.out + (size_t)s * row_bytes, nvec, lane);
   }
 }
 

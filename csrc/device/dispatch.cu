@@ -47,6 +47,7 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[kSendWarps * kMaxStages];
   __shared__ int s_err;
+  __shared__ int s_znext, s_ztotal;
   const int nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = c.K, S = c.S, NvS = c.NvS;
   const uint32_t row_bytes = (uint32_t)c.H * 2u;
@@ -54,8 +55,45 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   if (tid == 0) s_err = 0;
   if (tid < kSendWarps * kMaxStages) mbar_init(&s_bar[tid], 1);
   fence_mbar_init();
+  // padding-row table of the local shard: s_zstart[g] = first padding row of group g,
+  // s_zpre[g] = number of padding rows in groups < g (so a flat row index maps to (g, j))
+  const int ngroups = 2 * c.epn;
+  int* s_zpre = reinterpret_cast<int*>(smem + (size_t)kSendWarps * stages * row_bytes);
+  int* s_zstart = s_zpre + ngroups + 1;
+  for (int g = tid; g < ngroups; g += blockDim.x) { s_zstart[g] = a.zero_fill[2 * g]; s_zpre[g + 1] = a.zero_fill[2 * g + 1]; }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int g = 0; g < ngroups; ++g) { const int n = s_zpre[g + 1]; s_zpre[g] = run; run += n; }
+    s_zpre[ngroups] = run; s_ztotal = run; s_znext = 0;
+  }
   __syncthreads();
 
+  // Zero the padding rows (and their weight slots) that fall to this CTA (flat index = CTA id
+  // mod grid). Any warp may call it; rows are handed out through a shared counter, so the
+  // dedicated warp starts at once and the sender warps join when their tokens are on the wire.
+  auto zero_fill_work = [&]() {
+    char* hid = peer_ptr(c, c.rank, c.off_hidden);
+    float* wts = (float*)peer_ptr(c, c.rank, c.off_weights);
+    const int vec_per_row = (int)(row_bytes >> 4);
+    const int4 z = make_int4(0, 0, 0, 0);
+    const int total = s_ztotal;
+    for (;;) {
+      int k = 0;
+      if (lane == 0) k = atomicAdd(&s_znext, 1);
+      k = __shfl_sync(0xffffffffu, k, 0);
+      const long long rr = (long long)blockIdx.x + (long long)k * nb;
+      if (rr >= total) break;
+      int lo = 0, hi = ngroups - 1;                 // last g with s_zpre[g] <= rr
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (s_zpre[mid] <= (int)rr) lo = mid; else hi = mid - 1; }
+      const int prow = s_zstart[lo] + ((int)rr - s_zpre[lo]);
+      char* row = hid + (size_t)prow * row_bytes;
+      for (int v = lane; v < vec_per_row; v += 32) st_v4(row + (size_t)v * 16, z);
+      if (lane == 0 && a.weights) wts[prow] = 0.f;
+    }
+  };
+
+  if (tid == 0) trace_mark(c, MEP_K_DISPATCH, 1);
   if (a.entry_barrier) { if (!cross_rank_barrier(c, nb, 1, MEP_K_DISPATCH, 10)) return; }
 
   if (a.fresh && blockIdx.x == 0) {
@@ -70,19 +108,35 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   if (warp < kSendWarps) {
     unsigned char* ring = smem + (size_t)warp * stages * row_bytes;
     uint64_t* bars = s_bar + warp * kMaxStages;
-    char* my_hidden = nullptr; (void)my_hidden;
-    int it = 0;
-    for (int s = blockIdx.x * kSendWarps + warp; s < S; s += nb * kSendWarps, ++it) {
+    const int first = blockIdx.x * kSendWarps + warp, stride = nb * kSendWarps;
+    const int ntok = first < S ? (S - first + stride - 1) / stride : 0;
+    // Software pipeline over this warp's tokens. Bulk-group g holds the stores of token g. At
+    // iteration `it` the slot of token it-1-D is reloaded with token it+pre (pre = stages-1-D):
+    // its stores only need to have finished READING shared memory, so at most the D most recent
+    // groups may still be pending (D = 1 when the ring is deep enough to skip the newest group).
+    const int D = stages >= 3 ? 1 : 0;
+    const int pre = stages - 1 - D;
+    if (lane == 0) {
+      for (int i = 0; i < pre && i < ntok; ++i) {
+        mbar_expect_tx(&bars[i], row_bytes);
+        bulk_g2s(ring + (size_t)i * row_bytes, a.hidden + (size_t)(first + i * stride) * c.H, row_bytes, &bars[i]);
+      }
+    }
+    for (int it = 0; it < ntok; ++it) {
+      const int s = first + it * stride;
       const int st = it % stages;
       const uint32_t parity = (uint32_t)(it / stages) & 1u;
       int dval = 0; float w = 0.f;
       if (lane < K) { dval = a.dst[(size_t)s * K + lane]; if (a.weights) w = a.weights[(size_t)s * K + lane]; }
       bool ok = true;
       if (lane == 0) {
-        // ring slot `st` was last read by the stores issued `stages` iterations ago
-        wait_read_dyn(stages - 1);
-        mbar_expect_tx(&bars[st], row_bytes);
-        bulk_g2s(ring + (size_t)st * row_bytes, a.hidden + (size_t)s * c.H, row_bytes, &bars[st]);
+        const int nxt = it + pre;
+        if (nxt < ntok) {
+          if (D) bulk_wait_read<1>(); else bulk_wait_read<0>();
+          const int ns = nxt % stages;
+          mbar_expect_tx(&bars[ns], row_bytes);
+          bulk_g2s(ring + (size_t)ns * row_bytes, a.hidden + (size_t)(first + nxt * stride) * c.H, row_bytes, &bars[ns]);
+        }
         ok = mbar_wait_bounded(&bars[st], parity, c.wait_budget_ns);
         if (!ok) { report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_DISPATCH, 20, s, 0, 0); s_err = 1; }
       }
@@ -103,26 +157,15 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       }
       if (lane == 0) bulk_commit();
     }
-    if (lane == 0) { bulk_wait_all<0>(); fence_proxy_async(); }
+    if (lane == 0) trace_mark(c, MEP_K_DISPATCH, 2);
+    zero_fill_work();
+    if (lane == 0) { bulk_wait_all<0>(); fence_proxy_async(); trace_mark(c, MEP_K_DISPATCH, 3); }
   } else {
-    // zero-fill warp: padding rows (and their weight slots) of the local shard
-    const int ngroups = 2 * c.epn;
-    char* hid = peer_ptr(c, c.rank, c.off_hidden);
-    float* wts = (float*)peer_ptr(c, c.rank, c.off_weights);
-    const int vec_per_row = (int)(row_bytes >> 4);
-    const int4 z = make_int4(0, 0, 0, 0);
-    int rr = 0;   // running row counter to spread rows over CTAs
-    for (int g = 0; g < ngroups; ++g) {
-      const int p0 = a.zero_fill[2 * g], n = a.zero_fill[2 * g + 1];
-      for (int j = 0; j < n; ++j, ++rr) {
-        if (rr % nb != (int)blockIdx.x) continue;
-        char* row = hid + (size_t)(p0 + j) * row_bytes;
-        for (int v = lane; v < vec_per_row; v += 32) st_v4(row + (size_t)v * 16, z);
-        if (lane == 0 && a.weights) wts[p0 + j] = 0.f;
-      }
-    }
+    zero_fill_work();
   }
+  if (lane == 0 && warp == kSendWarps) trace_mark(c, MEP_K_DISPATCH, 4);
   cross_rank_barrier(c, nb, 1, MEP_K_DISPATCH, 30);
+  if (tid == 0) trace_mark(c, MEP_K_DISPATCH, 5);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -177,11 +220,19 @@ __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPa
     const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
     if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
     const char* src = base + (size_t)p * row_bytes;
-    for (int v = lane; v < nvec; v += 32) {
-      const int4 x = ld_nc_v4(src + (size_t)v * 16);
-      for (int j = 0; j < n; ++j) {
-        const int q = a.dup_loffs[st + j];
-        if ((unsigned)q < (unsigned)c.NvS) st_na_v4(base + (size_t)q * row_bytes + (size_t)v * 16, x);
+    // duplicate offsets of this group live in lanes 0..n-1
+    int myq = -1;
+    if (lane < n) { myq = a.dup_loffs[st + lane]; if ((unsigned)myq >= (unsigned)c.NvS) myq = -1; }
+    for (int v0 = 0; v0 < nvec; v0 += 128) {          // 4 x 16-byte loads in flight per lane
+      int4 x[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const int v = v0 + j * 32 + lane; if (v < nvec) x[j] = ld_nc_v4(src + (size_t)v * 16); }
+      for (int d = 0; d < n; ++d) {
+        const int q = __shfl_sync(0xffffffffu, myq, d);
+        if (q < 0) continue;
+        char* drow = base + (size_t)q * row_bytes;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const int v = v0 + j * 32 + lane; if (v < nvec) st_na_v4(drow + (size_t)v * 16, x[j]); }
       }
     }
   }
@@ -200,12 +251,14 @@ extern "C" int mep_dispatch_smem_stages(int H, int* stages_out, size_t* smem_out
 }
 
 extern "C" int mep_launch_dispatch(int nv, const MepRankCtx* const* ctxs, const mep::DispatchArgs* args,
-                                   int num_sms, int H, cudaStream_t stream) {
+                                   int num_sms, int H, int epn, cudaStream_t stream) {
   MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "dispatch: nv=%d out of range", nv);
   MepCtxPack P = {}; mep::DispatchArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
   int stages; size_t smem;
   if (mep_dispatch_smem_stages(H, &stages, &smem)) return -1;
+  smem += (size_t)(4 * epn + 2) * sizeof(int);      // padding-row tables behind the rings
+  MEP_REQUIRE(smem <= 226 * 1024, "dispatch: epn=%d padding tables do not fit shared memory", epn);
   return mep::launch_cooperative(mep::dispatch_kernel, dim3(num_sms, nv), dim3(mep::kDispThreads), smem,
                                  stream, false, P, A, stages);
 }

@@ -28,7 +28,8 @@ struct GradReduceArgs {
 struct GradReduceArgsPack { GradReduceArgs a[MEP_MAX_VRANKS]; };
 
 constexpr int kRedThreads = 512;
-constexpr int64_t kRedChunk = 4096;   // floats per work unit (2 float4 per thread)
+constexpr int kRedVec = 4;            // float4 per thread and pass
+constexpr int64_t kRedChunk = (int64_t)kRedThreads * kRedVec * 4;   // floats per work unit
 
 __device__ __forceinline__ float4 f4add(float4 a, const int4& b) {
   a.x += __int_as_float(b.x); a.y += __int_as_float(b.y); a.z += __int_as_float(b.z); a.w += __int_as_float(b.w);
@@ -89,28 +90,39 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
     float* lp = T.local + (int64_t)le * T.expert_elems + beg;
     const int64_t ebytes = T.expert_elems * 4;
     const int nvec = (int)(len >> 2);
-    for (int v0 = 0; v0 < nvec; v0 += 2 * nt) {
-      const int va = v0 + tid, vb = v0 + nt + tid;
-      float4 acc0 = make_float4(0, 0, 0, 0), acc1 = acc0;
-      if (va < nvec) acc0 = *reinterpret_cast<const float4*>(lp + (size_t)va * 4);
-      if (vb < nvec) acc1 = *reinterpret_cast<const float4*>(lp + (size_t)vb * 4);
-      for (int j0 = 0; j0 < ns; j0 += 4) {
-        int4 x0[4], x1[4];
+    for (int v0 = 0; v0 < nvec; v0 += kRedVec * nt) {
+      float4 acc[kRedVec];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          x0[j] = make_int4(0, 0, 0, 0); x1[j] = x0[j];
-          if (j0 + j < ns) {
-            const int idx = srcs[j0 + j], d = idx / epn, b = idx - d * epn;
-            const char* rp = T.pool + (int64_t)d * T.rank_stride + (int64_t)b * ebytes + beg * 4;
-            if (va < nvec) x0[j] = ld_peer_v4(rp + (size_t)va * 16);
-            if (vb < nvec) x1[j] = ld_peer_v4(rp + (size_t)vb * 16);
+      for (int q = 0; q < kRedVec; ++q) {
+        const int v = v0 + q * nt + tid;
+        acc[q] = v < nvec ? *reinterpret_cast<const float4*>(lp + (size_t)v * 4) : make_float4(0, 0, 0, 0);
+      }
+      for (int j0 = 0; j0 < ns; j0 += 2) {          // 2 sources x kRedVec vectors in flight per thread
+        int4 x[2][kRedVec];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const bool on = j0 + j < ns;
+          const int idx = on ? srcs[j0 + j] : 0, d = idx / epn, b = idx - d * epn;
+          const char* rp = T.pool + (int64_t)d * T.rank_stride + (int64_t)b * ebytes + beg * 4;
+#pragma unroll
+          for (int q = 0; q < kRedVec; ++q) {
+            const int v = v0 + q * nt + tid;
+            x[j][q] = make_int4(0, 0, 0, 0);
+            if (on && v < nvec) x[j][q] = ld_peer_v4(rp + (size_t)v * 16);
           }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) if (j0 + j < ns) { acc0 = f4add(acc0, x0[j]); acc1 = f4add(acc1, x1[j]); }
+        for (int j = 0; j < 2; ++j)
+          if (j0 + j < ns) {
+#pragma unroll
+            for (int q = 0; q < kRedVec; ++q) acc[q] = f4add(acc[q], x[j][q]);
+          }
       }
-      if (va < nvec) *reinterpret_cast<float4*>(lp + (size_t)va * 4) = acc0;
-      if (vb < nvec) *reinterpret_cast<float4*>(lp + (size_t)vb * 4) = acc1;
+#pragma unroll
+      for (int q = 0; q < kRedVec; ++q) {
+        const int v = v0 + q * nt + tid;
+        if (v < nvec) *reinterpret_cast<float4*>(lp + (size_t)v * 4) = acc[q];
+      }
     }
     for (int64_t i = ((int64_t)nvec << 2) + tid; i < len; i += nt) {   // ragged tail
       float acc = lp[i];

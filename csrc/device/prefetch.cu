@@ -3,9 +3,9 @@
 // Counterpart of the reference's PrefetchKernel (moonep/prefetch.py:45-470): one launch
 // copies up to six tensors (gate/up/down and optionally their block scales) of every local
 // expert that the plan placed in some rank's slot (experts_to_copy[d, b] in this rank's id
-// range) to pool[d, b]. Expert payloads are contiguous, so the copy is 1-D: 32 KB chunks are
+// range) to pool[d, b]. Expert payloads are contiguous, so the copy is 1-D: 64 KB chunks are
 // dealt round-robin to the CTAs and moved with 16-byte local loads and 16-byte peer stores
-// (four per thread in flight) -- no TMA touches peer memory. Dtype-agnostic (bytes).
+// (eight per thread in flight) -- no TMA touches peer memory. Dtype-agnostic (bytes).
 // Ends with a cross-rank barrier: on return every rank's slots are complete.
 #include "prims.cuh"
 #include "../host/launch.h"
@@ -27,7 +27,8 @@ struct PrefetchArgs {
 struct PrefetchArgsPack { PrefetchArgs a[MEP_MAX_VRANKS]; };
 
 constexpr int kCopyThreads = 512;
-constexpr int64_t kChunk = 32768;
+constexpr int64_t kChunk = 65536;
+constexpr int kVec = 8;               // 16-byte vectors per thread in flight
 
 __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P, PrefetchArgsPack A) {
   const MepRankCtx& c = *P.ctx[blockIdx.y];
@@ -70,12 +71,12 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
     const char* src = T.local + (int64_t)le * T.expert_bytes + beg;
     char* dstp = T.pool + (int64_t)d * T.rank_stride + (int64_t)b * T.expert_bytes + beg;
     const int nvec = (int)(len >> 4);
-    for (int v0 = 0; v0 < nvec; v0 += 4 * nt) {
-      int4 x[4];
+    for (int v0 = 0; v0 < nvec; v0 += kVec * nt) {
+      int4 x[kVec];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) x[j] = ld_nc_v4(src + (size_t)v * 16); }
+      for (int j = 0; j < kVec; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) x[j] = ld_nc_v4(src + (size_t)v * 16); }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) st_na_v4(dstp + (size_t)v * 16, x[j]); }
+      for (int j = 0; j < kVec; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) st_na_v4(dstp + (size_t)v * 16, x[j]); }
     }
     for (int64_t i = ((int64_t)nvec << 4) + tid; i < len; i += nt) dstp[i] = src[i];   // ragged tail
   }

@@ -91,6 +91,18 @@ __device__ __forceinline__ bool bounded_wait(const MepRankCtx& c, Cond cond) {
   }
 }
 
+// ---------------------------------------------------------------- tracing
+// One record per call (call it from a single thread of the warp/CTA you want to stamp).
+__device__ __forceinline__ void trace_mark(const MepRankCtx& c, int kernel, int site) {
+  if (c.trace == nullptr) return;
+  const unsigned long long i = atomicAdd(c.trace, 1ull);
+  if ((int64_t)i < c.trace_cap) {
+    c.trace[1 + 2 * i] = globaltimer_ns();
+    c.trace[2 + 2 * i] = ((unsigned long long)kernel << 48) | ((unsigned long long)site << 32) |
+                         ((unsigned long long)blockIdx.x << 8) | (unsigned long long)(threadIdx.x >> 5);
+  }
+}
+
 // ---------------------------------------------------------------- grid barrier
 // All `nblocks` CTAs of one rank (blockIdx.x in [0, nblocks)) must call it; CTAs must be
 // co-resident (cooperative launch). Self-resetting: CTA 0 adds 0x80000000-(n-1), the

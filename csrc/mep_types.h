@@ -63,6 +63,10 @@ typedef struct MepRankCtx {
   unsigned long long* send_cnt;  // [R] (groups<<32 | loffs) emitted to each destination
   MepStatus* status;
   uint64_t wait_budget_ns;
+  // optional device-timestamp ring (null = tracing off): word 0 = number of records written,
+  // then 2 words per record: %globaltimer ns, (kernel << 48 | site << 32 | cta << 8 | warp)
+  unsigned long long* trace;
+  int64_t trace_cap;
 } MepRankCtx;
 
 typedef struct MepCtxPack { const MepRankCtx* ctx[MEP_MAX_VRANKS]; } MepCtxPack;

@@ -127,7 +127,7 @@ class OpsMixin:
                                entry_barrier=(not fresh) and inter_rank_sync)
         if fresh:
             engine.launch_dup_finalize(st, plans)
-        engine.launch_dup_expand(st, [s.hidden_local for s in st], plans, self._num_sms_dedup)
+        engine.launch_dup_expand(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4)
         out_h, out_w = [], []
         for i in range(n):
             if zero_copy:
@@ -172,7 +172,7 @@ class OpsMixin:
                 st[i].hidden_local.copy_(hidden_nvsh[i])
             if have_w and not w_zero_copy:
                 st[i].weights_local.copy_(weights_nvs[i])
-        engine.launch_dup_reduce(st, [s.hidden_local for s in st], plans, self._num_sms_dedup)
+        engine.launch_dup_reduce(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4)
         outs = [torch.empty(g.S, g.H, dtype=torch.bfloat16, device=s.device) for s in st]
         outw = [torch.empty(g.S, g.K, dtype=torch.float32, device=s.device) for s in st] if have_w else None
         engine.launch_combine(st, plans, outs, outw, entry_barrier=True)

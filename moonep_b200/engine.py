@@ -98,6 +98,10 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
         setattr(c, name, s[name].data_ptr())
     c.status = st.status.data_ptr()
     c.wait_budget_ns = wait_budget_ns() if budget_ns is None else budget_ns
+    if os.environ.get("MOONEP_TRACE") == "1":
+        cap = int(os.environ.get("MOONEP_TRACE_RECORDS", "65536"))
+        s["trace"] = torch.zeros(1 + 2 * cap, dtype=torch.int64, device=dev)
+        c.trace, c.trace_cap = s["trace"].data_ptr(), cap
     st.ctx_host = c
     raw = bytes(c)
     st.ctx_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
@@ -112,6 +116,23 @@ def read_status(st: RankState) -> dict | None:
         return None
     return dict(code=v[0], kernel=v[1], site=v[2], rank=v[3], peer=v[4],
                 observed=v[5] & 0xFFFFFFFF, expected=v[6] & 0xFFFFFFFF)
+
+
+def read_trace(st: RankState, reset: bool = True):
+    """Device timestamps recorded since the last reset: list of ``(ns, kernel, site, cta, warp)``
+    sorted by time (needs ``MOONEP_TRACE=1`` when the Buffer was created). Synchronises."""
+    t = st.scratch.get("trace")
+    if t is None:
+        return []
+    v = t.cpu()
+    n = min(int(v[0]), (v.numel() - 1) // 2)
+    out = []
+    for i in range(n):
+        ns, tag = int(v[1 + 2 * i]), int(v[2 + 2 * i])
+        out.append((ns, (tag >> 48) & 0xFFFF, (tag >> 32) & 0xFFFF, (tag >> 8) & 0xFFFFFF, tag & 0xFF))
+    if reset:
+        t[0] = 0
+    return sorted(out)
 
 
 def _pack(states):
@@ -157,7 +178,7 @@ def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry
         args[i] = DispatchArgs(ptr(hidden_list[i]), ptr(w), ptr(plans[i].dst), ptr(plans[i].zero_fill_ranges),
                                1 if fresh else 0, 1 if entry_barrier else 0)
     g = states[0].geo
-    _native.check(lib.mep_launch_dispatch(n, _pack(states), args, g.num_sms, g.H, _native.cur_stream()), "dispatch")
+    _native.check(lib.mep_launch_dispatch(n, _pack(states), args, g.num_sms, g.H, g.epn, _native.cur_stream()), "dispatch")
 
 
 def launch_dup_finalize(states, plans):
