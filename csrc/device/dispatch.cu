@@ -29,6 +29,7 @@ struct DispatchArgsPack { DispatchArgs a[MEP_MAX_VRANKS]; };
 constexpr int kSendWarps = 6;                 // sender warps per CTA
 constexpr int kDispThreads = (kSendWarps + 1) * 32;   // + one zero-fill warp
 constexpr int kMaxStages = 8;
+constexpr int kMetaTokens = 32;   // tokens per warp whose plan entries / weights are staged at once
 
 template <int N> __device__ __forceinline__ void wait_read_le() { bulk_wait_read<N>(); }
 __device__ __forceinline__ void wait_read_dyn(int n) {
@@ -42,7 +43,7 @@ __device__ __forceinline__ void wait_read_dyn(int n) {
 
 __global__ void __launch_bounds__(kDispThreads, 1)
 dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
-  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const DispatchArgs& a = A.a[blockIdx.y];
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[kSendWarps * kMaxStages];
@@ -60,6 +61,7 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   const int ngroups = 2 * c.epn;
   int* s_zpre = reinterpret_cast<int*>(smem + (size_t)kSendWarps * stages * row_bytes);
   int* s_zstart = s_zpre + ngroups + 1;
+  int* s_meta_all = s_zstart + ngroups;            // [warps][kMetaTokens][K] dst, then the same for weights
   for (int g = tid; g < ngroups; g += blockDim.x) { s_zstart[g] = a.zero_fill[2 * g]; s_zpre[g + 1] = a.zero_fill[2 * g + 1]; }
   __syncthreads();
   if (tid == 0) {
@@ -122,12 +124,25 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
         bulk_g2s(ring + (size_t)i * row_bytes, a.hidden + (size_t)(first + i * stride) * c.H, row_bytes, &bars[i]);
       }
     }
+    int* m_dst = s_meta_all + (size_t)warp * 2 * kMetaTokens * K;
+    float* m_w = reinterpret_cast<float*>(m_dst + kMetaTokens * K);
     for (int it = 0; it < ntok; ++it) {
       const int s = first + it * stride;
       const int st = it % stages;
       const uint32_t parity = (uint32_t)(it / stages) & 1u;
+      if ((it % kMetaTokens) == 0) {       // stage the next chunk of plan entries (all loads in flight at once)
+        const int cnt = (ntok - it < kMetaTokens ? ntok - it : kMetaTokens) * K;
+        __syncwarp();
+        for (int i = lane; i < cnt; i += 32) {
+          const int tt = i / K, k = i - tt * K;
+          const size_t e = (size_t)(first + (it + tt) * stride) * K + k;
+          m_dst[i] = a.dst[e];
+          m_w[i] = a.weights ? a.weights[e] : 0.f;
+        }
+        __syncwarp();
+      }
       int dval = 0; float w = 0.f;
-      if (lane < K) { dval = a.dst[(size_t)s * K + lane]; if (a.weights) w = a.weights[(size_t)s * K + lane]; }
+      if (lane < K) { dval = m_dst[(it % kMetaTokens) * K + lane]; w = m_w[(it % kMetaTokens) * K + lane]; }
       bool ok = true;
       if (lane == 0) {
         const int nxt = it + pre;
@@ -176,7 +191,7 @@ struct DupFinalizeArgs { int32_t* dup_groups; int32_t* dup_loffs; int32_t* dup_c
 struct DupFinalizeArgsPack { DupFinalizeArgs a[MEP_MAX_VRANKS]; };
 
 __global__ void dup_finalize_kernel(MepCtxPack P, DupFinalizeArgsPack A) {
-  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const DupFinalizeArgs& a = A.a[blockIdx.y];
   __shared__ int s_goff[MEP_MAX_RANKS + 1], s_loff[MEP_MAX_RANKS + 1];
   const int* cnt = (const int*)peer_ptr(c, c.rank, c.off_dupcnt);
@@ -208,7 +223,7 @@ struct DupArgs { __nv_bfloat16* buf; const int32_t* dup_groups; const int32_t* d
 struct DupArgsPack { DupArgs a[MEP_MAX_VRANKS]; };
 
 __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPack A) {
-  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const DupArgs& a = A.a[blockIdx.y];
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
@@ -242,7 +257,7 @@ __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPa
 
 extern "C" int mep_dispatch_smem_stages(int H, int* stages_out, size_t* smem_out) {
   const size_t row = (size_t)H * 2;
-  const size_t budget = 200 * 1024;
+  const size_t budget = 180 * 1024;
   int stages = (int)(budget / (row * mep::kSendWarps));
   if (stages > mep::kMaxStages) stages = mep::kMaxStages;
   MEP_REQUIRE(stages >= 1, "dispatch: H=%d rows (%zu B) do not fit the shared-memory ring", H, row);
@@ -258,6 +273,7 @@ extern "C" int mep_launch_dispatch(int nv, const MepRankCtx* const* ctxs, const 
   int stages; size_t smem;
   if (mep_dispatch_smem_stages(H, &stages, &smem)) return -1;
   smem += (size_t)(4 * epn + 2) * sizeof(int);      // padding-row tables behind the rings
+  smem += (size_t)mep::kSendWarps * 2 * mep::kMetaTokens * MEP_MAX_TOPK * sizeof(int);   // per-warp plan staging
   MEP_REQUIRE(smem <= 226 * 1024, "dispatch: epn=%d padding tables do not fit shared memory", epn);
   return mep::launch_cooperative(mep::dispatch_kernel, dim3(num_sms, nv), dim3(mep::kDispThreads), smem,
                                  stream, false, P, A, stages);

@@ -37,7 +37,7 @@ __device__ __forceinline__ float4 f4add(float4 a, const int4& b) {
 }
 
 __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack P, GradReduceArgsPack A) {
-  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const GradReduceArgs& a = A.a[blockIdx.y];
   extern __shared__ int s_mem[];
   const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x;

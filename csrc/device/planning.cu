@@ -163,7 +163,7 @@ __device__ void solve(const MepRankCtx& c, const PlanArgs& a, int* s_e, bool e_i
 }
 
 __global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P, PlanArgsPack A) {
-  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const PlanArgs& a = A.a[blockIdx.y];
   extern __shared__ int s_e[];
   __shared__ int s_raw[kPlanThreads];

@@ -31,7 +31,7 @@ constexpr int64_t kChunk = 65536;
 constexpr int kVec = 8;               // 16-byte vectors per thread in flight
 
 __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P, PrefetchArgsPack A) {
-  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const PrefetchArgs& a = A.a[blockIdx.y];
   extern __shared__ int s_list[];
   __shared__ int s_n;

@@ -76,18 +76,25 @@ __device__ __forceinline__ bool aborted(const MepRankCtx& c) {
   return *(volatile int32_t*)&c.status->code != 0;
 }
 
-// Spin helper: `cond()` is polled; every 64 polls the clock and the abort word are
-// checked. Returns false when the budget ran out or another waiter already failed.
+// Wait budgets are given in nanoseconds but measured with the SM cycle counter (reading
+// %globaltimer costs about a microsecond, far too slow for a polling loop): cycles = ns * 2.2
+// over-estimates the budget at any clock the part can run at, which is the safe direction.
+__device__ __forceinline__ long long budget_cycles(uint64_t ns) { return (long long)(ns * 22 / 10); }
+
+// Spin helper: `cond()` is polled; after a first burst of polls the cycle counter and the abort
+// word are checked every 64 polls. Returns false when the budget ran out or another waiter
+// already failed.
 template <class Cond>
 __device__ __forceinline__ bool bounded_wait(const MepRankCtx& c, Cond cond) {
-  if (cond()) return true;
-  const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  for (int i = 0; i < 256; ++i) { if (cond()) return true; }
+  const long long t0 = clock64(), lim = budget_cycles(c.wait_budget_ns);
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) { if (cond()) return true; }
     if (aborted(c)) return false;
-    if (globaltimer_ns() - t0 > c.wait_budget_ns) return false;
-    __nanosleep(32);
+    if (clock64() - t0 > lim) return false;
+    __nanosleep(20);
   }
 }
 
@@ -98,6 +105,17 @@ __device__ __forceinline__ void trace_mark(const MepRankCtx& c, int kernel, int 
   const unsigned long long i = atomicAdd(c.trace, 1ull);
   if ((int64_t)i < c.trace_cap) {
     c.trace[1 + 2 * i] = globaltimer_ns();
+    c.trace[2 + 2 * i] = ((unsigned long long)kernel << 48) | ((unsigned long long)site << 32) |
+                         ((unsigned long long)blockIdx.x << 8) | (unsigned long long)(threadIdx.x >> 5);
+  }
+}
+
+// Same record format, but the first word carries a caller-supplied value (e.g. accumulated cycles).
+__device__ __forceinline__ void trace_value(const MepRankCtx& c, int kernel, int site, unsigned long long value) {
+  if (c.trace == nullptr) return;
+  const unsigned long long i = atomicAdd(c.trace, 1ull);
+  if ((int64_t)i < c.trace_cap) {
+    c.trace[1 + 2 * i] = value;
     c.trace[2 + 2 * i] = ((unsigned long long)kernel << 48) | ((unsigned long long)site << 32) |
                          ((unsigned long long)blockIdx.x << 8) | (unsigned long long)(threadIdx.x >> 5);
   }
@@ -179,14 +197,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded mbarrier wait without a rank context (budget in polls; ~a few seconds).
+// Bounded mbarrier wait (budget in nanoseconds, see budget_cycles).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t budget_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  for (int i = 0; i < 512; ++i) { if (mbar_try_wait(bar, parity)) return true; }
+  const long long t0 = clock64(), lim = budget_cycles(budget_ns);
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i) { if (mbar_try_wait(bar, parity)) return true; }
-    if (globaltimer_ns() - t0 > budget_ns) return false;
+    if (clock64() - t0 > lim) return false;
   }
 }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }

@@ -217,7 +217,7 @@ def launch_combine(states, plans, outs, out_weights, entry_barrier: bool = True)
     for i in range(n):
         ow = out_weights[i] if out_weights is not None else None
         args[i] = CombineArgs(ptr(plans[i].dst), ptr(outs[i]), ptr(ow), 1 if entry_barrier else 0)
-    _native.check(lib.mep_launch_combine(n, _pack(states), args, states[0].geo.num_sms, _native.cur_stream()), "combine")
+    _native.check(lib.mep_launch_combine(n, _pack(states), args, states[0].geo.num_sms, states[0].geo.H, _native.cur_stream()), "combine")
 
 
 def launch_rank_sync(states):
