@@ -7,8 +7,8 @@
 // token's rows; duplicates of one destination rank are summed in fp32 and rounded to bf16
 // once into the primary row, the per-rank partial sums are then added in fp32 (ascending k)
 // and rounded once; the optional [S,K] channel gathers the per-slot fp32 route weights back
-// bit-exactly. Peer rows are pulled by a producer warp with plain (single-CTA) bulk copies into a
-// shared-memory ring and summed by consumer warps.
+// bit-exactly. Peer rows are pulled with per-lane asynchronous 16-byte copies into shared memory
+// (see combine_kernel); bulk copies are not used for peer reads.
 #include "prims.cuh"
 #include "../host/launch.h"
 #include <stdlib.h>
@@ -113,178 +113,76 @@ struct CombineArgs {
 };
 struct CombineArgsPack { CombineArgs a[MEP_MAX_VRANKS]; };
 
-constexpr int kCombConsumers = 128;                 // 4 accumulate warps
-constexpr int kCombThreads = 32 + kCombConsumers + 32;   // + producer warp + route-weight gather warp
-constexpr int kCombMaxStages = 16;
-constexpr int kCombSegVecs = 1024;                  // a stage holds at most 16 KB of one row
-constexpr int kCombMetaTokens = 128;                // tokens whose plan entries are staged at once
+constexpr int kCombWarps = 12;
+constexpr int kCombThreads = kCombWarps * 32;
+constexpr int kCombSlots = 32;                      // 16-byte vectors per lane in one warp stage (16 KB per warp)
 
-// One producer warp keeps up to `stages` row segments in flight with bulk copies (peer or local
-// memory -> this CTA's shared memory ring); four consumer warps add the arriving rows of a token
-// in fp32 registers (ascending k) and write the bf16 result once. In-flight data lives in shared
-// memory, so the bytes outstanding per SM are not limited by registers.
-__global__ void __launch_bounds__(kCombThreads, 1)
-combine_kernel(MepCtxPack P, CombineArgsPack A, int stages, int nseg, int seg_vecs, int dbg) {
+__device__ __forceinline__ void cp_async16(uint32_t saddr, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(saddr), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// Each warp owns a 16 KB shared-memory stage and walks its tokens: for a token with np rows it
+// fetches, per pass, floor(32/np) 16-byte vectors per lane from EVERY row with asynchronous
+// 16-byte copies (peer or local memory -> shared memory, no registers held while in flight),
+// waits for its own copies, adds the rows in fp32 (ascending k) and stores the bf16 result.
+// A lane only ever reads back what it copied itself, so no cross-lane synchronisation is needed.
+// With 12 warps per CTA up to 192 KB per SM are in flight, which is what hides NVLink latency.
+__global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, CombineArgsPack A) {
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const CombineArgs& a = A.a[blockIdx.y];
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full_bar[kCombMaxStages], empty_bar[kCombMaxStages];
-  __shared__ int s_tok[kCombMaxStages], s_meta[kCombMaxStages];   // meta: seg << 2 | last << 1 | sentinel
-  __shared__ volatile int s_abort;
-  __shared__ long long s_tp[64], s_tc[64], s_td[64];
   const int nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = c.K, S = c.S, NvS = c.NvS;
   const size_t row_bytes = (size_t)c.H * 2;
   const int nvec = (int)(row_bytes >> 4);
-  const size_t seg_bytes = (size_t)seg_vecs * 16;
+  const int vpl = (nvec + 31) >> 5;                  // vectors per lane in a full row
 
-  if (tid == 0) {
-    s_abort = 0;
-    for (int i = 0; i < kCombMaxStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], kCombConsumers / 32); }
-    fence_mbar_init();
-  }
-  __syncthreads();
   if (tid == 0) trace_mark(c, MEP_K_COMBINE, 1);
   if (a.entry_barrier) { if (!cross_rank_barrier(c, nb, 2, MEP_K_COMBINE, 10)) return; }
   if (tid == 0) trace_mark(c, MEP_K_COMBINE, 2);
 
-  if (warp == 0) {
-    // ---------------- producer
-    int it = 0;
-    long long dbg_wait = 0, dbg_issue = 0; const long long dbg_t0 = clock64();
-    // plan entries are staged in shared memory one chunk of tokens at a time (all loads of a
-    // chunk in flight together), so no global-memory latency sits between two row copies
-    int* s_dst = reinterpret_cast<int*>(smem + (size_t)stages * seg_bytes);
-    const int ntok = blockIdx.x < S ? (S - blockIdx.x + nb - 1) / nb : 0;
-    for (int t = 0; t < ntok && !s_abort; ++t) {
-      const int s = blockIdx.x + t * nb;
-      if ((t % kCombMetaTokens) == 0) {
-        const int cnt = (ntok - t < kCombMetaTokens ? ntok - t : kCombMetaTokens) * K;
-        __syncwarp();
-        for (int i = lane; i < cnt; i += 32) {
-          const int tt = i / K, k = i - tt * K;
-          s_dst[i] = a.dst[((size_t)blockIdx.x + (size_t)(t + tt) * nb) * K + k];
-        }
-        __syncwarp();
-      }
-      const int dval = lane < K ? s_dst[(t % kCombMetaTokens) * K + lane] : -1;
-      const char* myrow = nullptr;
-      if (lane < K && dval >= 0) {
-        const int d = dval / NvS, loff = dval - d * NvS;
-        myrow = peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes;
-      }
-      const unsigned prim = __ballot_sync(0xffffffffu, myrow != nullptr);
-      const int np = __popc(prim);
-      for (int sg = 0; sg < nseg; ++sg) {
-        const int v_beg = sg * seg_vecs;
-        const uint32_t bytes = (uint32_t)((nvec - v_beg < seg_vecs ? nvec - v_beg : seg_vecs) * 16);
-        unsigned rest = prim;
-        for (int j = 0; j < np; ++j, ++it) {
-          const int src = __ffs(rest) - 1; rest &= rest - 1;
-          const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)myrow, src);
-          const int st = it % stages; const uint32_t ph = (uint32_t)(it / stages) & 1u;
-          int ok = 1;
-          if (lane == 0) {
-            const long long tw0 = clock64();
-            ok = mbar_wait_bounded(&empty_bar[st], ph ^ 1u, c.wait_budget_ns) ? 1 : 0;
-            dbg_wait += clock64() - tw0;
-            if (ok) {
-              const long long ti0 = clock64();
-              s_tok[st] = s; s_meta[st] = (sg << 2) | ((j == np - 1) ? 2 : 0);
-              mbar_expect_tx(&full_bar[st], (dbg & 4) ? 1024u : bytes);
-              bulk_g2s(smem + (size_t)st * seg_bytes, rp + (size_t)v_beg * 16, (dbg & 4) ? 1024u : bytes, &full_bar[st]);
-              dbg_issue += clock64() - ti0;
-              if (it < 64) s_tp[it] = clock64();
-            } else { report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_COMBINE, 20, s, 0, 0); s_abort = 1; }
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) break;
-        }
-        if (s_abort) break;
-      }
+  const uint32_t stage = smem_u32(smem) + (uint32_t)warp * (kCombSlots * 32 * 16);
+  const unsigned char* stage_g = smem + (size_t)warp * (kCombSlots * 32 * 16);
+  for (int s = blockIdx.x * kCombWarps + warp; s < S; s += nb * kCombWarps) {
+    int dval = -1;
+    if (lane < K) dval = a.dst[(size_t)s * K + lane];
+    const char* myrow = nullptr;
+    if (lane < K) {
+      const int raw = dval >= 0 ? dval : -dval - 1;
+      const int d = raw / NvS, loff = raw - d * NvS;
+      if (a.out_weights)
+        a.out_weights[(size_t)s * K + lane] = __ldcg((const float*)peer_ptr(c, d, c.off_weights) + loff);
+      if (dval >= 0) myrow = peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes;
     }
-    // sentinel stage: tells the consumers that no more rows follow
-    if (lane == 0 && !s_abort) {
-      const int st = it % stages; const uint32_t ph = (uint32_t)(it / stages) & 1u;
-      if (mbar_wait_bounded(&empty_bar[st], ph ^ 1u, c.wait_budget_ns)) { s_meta[st] = 1; mbar_arrive(&full_bar[st]); }
-      else { report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_COMBINE, 21, -1, 0, 0); s_abort = 1; }
-      trace_mark(c, MEP_K_COMBINE, 3);
-      trace_value(c, MEP_K_COMBINE, 20, (unsigned long long)dbg_wait);
-      trace_value(c, MEP_K_COMBINE, 24, (unsigned long long)dbg_issue);
-      trace_value(c, MEP_K_COMBINE, 21, (unsigned long long)(clock64() - dbg_t0));
-    }
-  } else if (warp == kCombThreads / 32 - 1) {
-    // ---------------- route-weight gather: [S, K] fp32 pulled from the slots' owners
-    if (a.out_weights) {
-      const int ntok = blockIdx.x < S ? (S - blockIdx.x + nb - 1) / nb : 0;
-      const int total = ntok * K;
-      for (int i0 = 0; i0 < total; i0 += 128) {
-        float w[4]; long long pos[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * 32 + lane;
-          pos[u] = -1; w[u] = 0.f;
-          if (i < total) {
-            const int t = i / K, k = i - t * K;
-            pos[u] = ((long long)blockIdx.x + (long long)t * nb) * K + k;
-            const int dv = a.dst[pos[u]];
-            const int raw = dv >= 0 ? dv : -dv - 1;
-            const int d = raw / NvS, loff = raw - d * NvS;
-            w[u] = __ldcg((const float*)peer_ptr(c, d, c.off_weights) + loff);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) if (pos[u] >= 0) a.out_weights[pos[u]] = w[u];
-      }
-    }
-    if (lane == 0) trace_mark(c, MEP_K_COMBINE, 5);
-  } else {
-    // ---------------- consumers
-    const int ct = tid - 32;
-    float acc[8][8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[q][i] = 0.f;
-    long long dbg_cw = 0; const long long dbg_c0 = clock64();
-    for (int it = 0; !s_abort; ++it) {
-      const int st = it % stages; const uint32_t ph = (uint32_t)(it / stages) & 1u;
-      int ok = 1;
-      const long long tw0 = clock64();
-      if (lane == 0) ok = mbar_wait_bounded(&full_bar[st], ph, c.wait_budget_ns) ? 1 : 0;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      dbg_cw += clock64() - tw0;
-      if (it < 64 && tid == 32) s_tc[it] = clock64();
-      if (!ok) { if (lane == 0) { report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_COMBINE, 22, it, 0, 0); s_abort = 1; } break; }
-      const int meta = s_meta[st];
-      if (meta & 1) break;
-      const int sg = meta >> 2, v_beg = sg * seg_vecs;
-      const int len = nvec - v_beg < seg_vecs ? nvec - v_beg : seg_vecs;
-      const unsigned char* stage = smem + (size_t)st * seg_bytes;
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const int v = ct + q * kCombConsumers;
-        if (v < len && !(dbg & 2)) acc_bf16x8(acc[q], *reinterpret_cast<const int4*>(stage + (size_t)v * 16));
-      }
-      if (meta & 2) {
-        char* orow = (char*)a.out + (size_t)s_tok[st] * row_bytes + (size_t)v_beg * 16;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const int v = ct + q * kCombConsumers;
-          if (v < len && !(dbg & 1)) st_na_v4(orow + (size_t)v * 16, pack_bf16x8(acc[q]));
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[q][i] = 0.f;
+    const unsigned prim = __ballot_sync(0xffffffffu, myrow != nullptr);
+    const int np = __popc(prim);
+    int per = kCombSlots / np;                       // vectors per lane and row in one pass
+    if (per > vpl) per = vpl;
+    char* orow = (char*)a.out + (size_t)s * row_bytes;
+    for (int j0 = 0; j0 < vpl; j0 += per) {
+      const int nj = vpl - j0 < per ? vpl - j0 : per;
+      unsigned rest = prim;
+      for (int r = 0; r < np; ++r) {
+        const int src = __ffs(rest) - 1; rest &= rest - 1;
+        const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)myrow, src);
+        for (int j = 0; j < nj; ++j) {
+          const int v = (j0 + j) * 32 + lane;
+          if (v < nvec) cp_async16(stage + (uint32_t)((r * per + j) * 32 + lane) * 16, rp + (size_t)v * 16);
         }
       }
-      __syncwarp();
-      if (it < 64 && tid == 32) s_td[it] = clock64();
-      if (lane == 0) mbar_arrive(&empty_bar[st]);
+      cp_async_commit_wait_all();
+      for (int j = 0; j < nj; ++j) {
+        const int v = (j0 + j) * 32 + lane;
+        if (v >= nvec) continue;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int r = 0; r < np; ++r)
+          acc_bf16x8(acc, *reinterpret_cast<const int4*>(stage_g + (size_t)((r * per + j) * 32 + lane) * 16));
+        st_na_v4(orow + (size_t)v * 16, pack_bf16x8(acc));
+      }
     }
-    if (lane == 0) { trace_mark(c, MEP_K_COMBINE, 4); trace_value(c, MEP_K_COMBINE, 22, (unsigned long long)dbg_cw); trace_value(c, MEP_K_COMBINE, 23, (unsigned long long)(clock64() - dbg_c0)); }
-  }
-  __syncthreads();
-  if (blockIdx.x == 0 && tid == 0 && c.trace) {
-    for (int i = 0; i < 64; ++i) { trace_value(c, MEP_K_COMBINE, 30, (unsigned long long)(s_tp[i] - s_tp[0])); trace_value(c, MEP_K_COMBINE, 31, (unsigned long long)(s_tc[i] - s_tp[0])); trace_value(c, MEP_K_COMBINE, 32, (unsigned long long)(s_td[i] - s_tp[0])); }
   }
 }
 
@@ -318,18 +216,12 @@ extern "C" int mep_launch_dup_reduce(int nv, const MepRankCtx* const* ctxs, cons
 extern "C" int mep_launch_combine(int nv, const MepRankCtx* const* ctxs, const mep::CombineArgs* args,
                                   int num_sms, int H, cudaStream_t stream) {
   MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "combine: nv=%d out of range", nv);
+  (void)H;
   MepCtxPack P = {}; mep::CombineArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  const int nvec = H / 8;
-  const int nseg = (nvec + mep::kCombSegVecs - 1) / mep::kCombSegVecs;
-  const int seg_vecs = (nvec + nseg - 1) / nseg;
-  const size_t meta = (size_t)mep::kCombMetaTokens * MEP_MAX_TOPK * sizeof(int);
-  int stages = (int)((200 * 1024 - meta) / ((size_t)seg_vecs * 16));
-  if (stages > mep::kCombMaxStages) stages = mep::kCombMaxStages;
-  MEP_REQUIRE(stages >= 2, "combine: H=%d does not fit the shared-memory ring", H);
-  const size_t smem = (size_t)stages * seg_vecs * 16 + meta;
+  const size_t smem = (size_t)mep::kCombWarps * mep::kCombSlots * 32 * 16;
   return mep::launch_cooperative(mep::combine_kernel, dim3(num_sms, nv), dim3(mep::kCombThreads), smem,
-                                 stream, false, P, A, stages, nseg, seg_vecs, getenv("MEP_DBG_COMBINE") ? atoi(getenv("MEP_DBG_COMBINE")) : 0);
+                                 stream, false, P, A);
 }
 
 extern "C" int mep_launch_rank_sync(int nv, const MepRankCtx* const* ctxs, cudaStream_t stream) {
