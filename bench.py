@@ -141,12 +141,12 @@ def run_ours(args):
         return max_over_ranks(e0.elapsed_time(e1) / n, world), (lib.mep_launch_count() - c0)
 
     scale, realised = calibrate_skew(blk, dev_batches[0], args.maxvio, world)
+    sampler = ClockSampler(local).start()      # nvidia-smi needs a moment to come up: start before the warm-up
     for _ in range(max(3, args.warmup)):
         step(dev_batches[0].detach())
     torch.cuda.synchronize()
     blk.buf.check(); gg.check_status()
 
-    sampler = ClockSampler(local).start()
     ms, launches = timed_steps(args.steps)
     # end to end through the public API: inputs come from pinned host memory every step and the
     # loss is read back every step

@@ -43,31 +43,41 @@ struct GemmArgs {
   uint64_t budget_ns;
 };
 
-constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4;
+constexpr int kBM = 128, kBN = 256, kBK = 64;
 constexpr int kABytes = kBM * kBK * 2;            // 16 KB
 constexpr int kBBytes = kBN * kBK * 2;            // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kStageBytes = kABytes + kBBytes;   // 48 KB per ring stage
 constexpr int kAtomBytes = 64 * kBK * 2;          // one 64-wide MN-major atom: 64 k-rows x 128 B
-constexpr int kGemmThreads = 192;
-constexpr int kMaxGroups = 256;
+// WGRAD has a short K loop (rows of one group) and a large fp32 tile to drain, so it runs 8
+// epilogue warps (two per TMEM lane quarter, each draining half of the columns) on a 3-stage ring;
+// the other modes run 4 epilogue warps on a 4-stage ring.
+template <int MODE> struct GemmCfg {
+  static constexpr int kEpiWarps = MODE == 4 ? 8 : 4;
+  static constexpr int kRing = MODE == 4 ? 3 : 4;
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr size_t kSmem = (size_t)kRing * (16384 + 32768) + (size_t)kEpiWarps * 2 * 4096 + 1024;
+};
+constexpr int kMaxGroups = 192;
 constexpr int kSlabBytes = 32 * 128;             // epilogue staging: 32 rows x 128 B per warp and buffer
-constexpr int kStagingBytes = 4 * 2 * kSlabBytes;  // 4 epilogue warps x 2 buffers
 constexpr int kTmemCols = 512;
 
 struct TileInfo { int g, row0, m0, n0, kblocks; };
 
 template <int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(GemmCfg<MODE>::kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b0,
                     const __grid_constant__ CUtensorMap tma_b1, const __grid_constant__ CUtensorMap tma_out, GemmArgs args) {
   constexpr bool A_MN = MODE == GEMM_WGRAD;
   constexpr bool B_MN = MODE == GEMM_GATE_UP || MODE == GEMM_DOWN || MODE == GEMM_WGRAD;
+  constexpr int kStages = GemmCfg<MODE>::kRing;       // shadows the file-scope default
+  constexpr int kEpiWarps = GemmCfg<MODE>::kEpiWarps;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], tfull_bar[2], tempty_bar[2];
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
   __shared__ int s_ntiles, s_nact;
+  __shared__ int s_cu[kMaxGroups + 1];      // s_cu[g] = first row of group g (s_cu[G] = end)
   __shared__ int s_start[kMaxGroups + 1];   // non-WGRAD: first tile of group; WGRAD: active group ids
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = args.G;
@@ -76,18 +86,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int i = 0; i < kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], kEpiWarps); }
     fence_mbar_init();
+    s_cu[0] = 0;
+    for (int g = 0; g < G; ++g) s_cu[g + 1] = args.cu_seqlens[g];
     if (MODE == GEMM_WGRAD) {
       int n = 0, prev = 0;
-      for (int g = 0; g < G; ++g) { const int e = args.cu_seqlens[g]; const bool in = g >= args.g_begin && g < args.g_end;
+      for (int g = 0; g < G; ++g) { const int e = s_cu[g + 1]; const bool in = g >= args.g_begin && g < args.g_end;
         if (in && (e > prev || (!args.accumulate && g < args.zero_empty_below))) s_start[n++] = g; prev = e; }
       s_nact = n;
       s_ntiles = n * (args.M_w / kBM) * (args.N / kBN);
     } else {
       const int nblk = MODE == GEMM_GATE_UP ? args.N / 128 : args.N / kBN;
       int run = 0, prev = 0;
-      for (int g = 0; g < G; ++g) { const int e = args.cu_seqlens[g]; s_start[g] = run; if (g >= args.g_begin && g < args.g_end) run += ((e - prev) / kBM) * nblk; prev = e; }
+      for (int g = 0; g < G; ++g) { const int e = s_cu[g + 1]; s_start[g] = run; if (g >= args.g_begin && g < args.g_end) run += ((e - prev) / kBM) * nblk; prev = e; }
       s_start[G] = run;
       s_ntiles = run;
     }
@@ -111,14 +123,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const int mblk = args.M_w / kBM, per = mblk * (args.N / kBN);
       const int ai = t / per, local = t - ai * per;
       const int g = s_start[ai];
-      const int beg = g ? args.cu_seqlens[g - 1] : 0;
-      ti.g = g; ti.row0 = beg; ti.kblocks = (args.cu_seqlens[g] - beg) / kBK;
+      const int beg = s_cu[g];
+      ti.g = g; ti.row0 = beg; ti.kblocks = (s_cu[g + 1] - beg) / kBK;
       ti.m0 = (local % mblk) * kBM; ti.n0 = (local / mblk) * kBN;
     } else {
       while (gcur + 1 <= G && s_start[gcur + 1] <= t) ++gcur;
       const int g = gcur;
-      const int beg = g ? args.cu_seqlens[g - 1] : 0;
-      const int mblk = (args.cu_seqlens[g] - beg) / kBM;
+      const int beg = s_cu[g];
+      const int mblk = (s_cu[g + 1] - beg) / kBM;
       const int local = t - s_start[g];
       ti.g = g; ti.row0 = beg + (local % mblk) * kBM; ti.m0 = 0;
       ti.n0 = (local / mblk) * (MODE == GEMM_GATE_UP ? 128 : kBN);
@@ -147,14 +159,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           }
           if (MODE == GEMM_GATE_UP) {
             const int r = ti.g * args.b_group_rows + k0;
-            tc::tma_load_2d(sb, &tma_b0, ti.n0, r, &full_bar[s]);
-            tc::tma_load_2d(sb + kAtomBytes, &tma_b0, ti.n0 + 64, r, &full_bar[s]);
-            tc::tma_load_2d(sb + 2 * kAtomBytes, &tma_b1, ti.n0, r, &full_bar[s]);
-            tc::tma_load_2d(sb + 3 * kAtomBytes, &tma_b1, ti.n0 + 64, r, &full_bar[s]);
+            tc::tma_load_3d(sb, &tma_b0, 0, r, ti.n0 / 64, &full_bar[s]);
+            tc::tma_load_3d(sb + 2 * kAtomBytes, &tma_b1, 0, r, ti.n0 / 64, &full_bar[s]);
           } else if (MODE == GEMM_DOWN) {
             const int r = ti.g * args.b_group_rows + k0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) tc::tma_load_2d(sb + i * kAtomBytes, &tma_b0, ti.n0 + 64 * i, r, &full_bar[s]);
+            tc::tma_load_3d(sb, &tma_b0, 0, r, ti.n0 / 64, &full_bar[s]);
           } else if (MODE == GEMM_WGRAD) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) tc::tma_load_2d(sb + i * kAtomBytes, &tma_b0, ti.n0 + 64 * i, ti.row0 + k0, &full_bar[s]);
@@ -218,7 +227,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (ti.kblocks == 0) {
         if (MODE == GEMM_WGRAD) {
           float* orow = (float*)args.out + ((size_t)ti.g * args.M_w + ti.m0 + r_in_tile) * args.N + ti.n0;
-          for (int j = 0; j < kBN / 4; ++j) reinterpret_cast<float4*>(orow)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          const int h0 = ((warp - 2) >> 2) * (kBN / 8);
+          for (int j = h0; j < h0 + kBN / 8; ++j) reinterpret_cast<float4*>(orow)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         --tcnt; continue;
       }
@@ -261,8 +271,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       } else if (MODE == GEMM_WGRAD) {
         const int orow0 = ti.g * args.M_w + ti.m0 + q * 32;
+        const int c_beg = ((warp - 2) >> 2) * 4;      // second set of four warps drains columns 128..255
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c, ++chunk_no) {
+        for (int c = c_beg; c < c_beg + 4; ++c, ++chunk_no) {
           const uint32_t buf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;
           if (lane == 0) bulk_wait_read<1>();          // the store issued two chunks ago has read this buffer
           __syncwarp();
@@ -339,6 +350,22 @@ static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols
   return 0;
 }
 
+// MN-major operand [rows (k), cols (m or n)] viewed as (64 elements, rows, cols/64): one box of
+// `atoms` 64-wide atoms x 64 rows lands in shared memory atom after atom.
+static int make_map_mn(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int atoms) {
+  const DriverApi* d = driver(); if (!d) return -1;
+  MEP_REQUIRE(cols % 64 == 0, "gemm: MN-major operand width %lld must be a multiple of 64", (long long)cols);
+  cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
+  cuuint32_t box[3] = {64, 64, (cuuint32_t)atoms};
+  cuuint32_t es[3] = {1, 1, 1};
+  MEP_REQUIRE(((uintptr_t)base & 15) == 0 && (ld * 2) % 16 == 0 && ld >= cols, "gemm: tensor base/stride must be 16-byte aligned");
+  MEP_CU_CHECK(d->TensorMapEncodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return 0;
+}
+
 }  // namespace mep
 
 // One grouped GEMM launch. `a` is a row-major bf16 matrix [a_rows, a_cols]; `b0`/`b1` are the
@@ -361,20 +388,21 @@ extern "C" int mep_grouped_gemm(int mode, const void* a, int64_t a_rows, int64_t
     MEP_REQUIRE(args.N % (mode == GEMM_GATE_UP ? 128 : kBN) == 0, "gemm: N=%d not tileable", args.N);
     if (make_map(&ma, a, a_rows, a_cols, a_ld, 64, kBM)) return -1;
   }
-  if (b_mn) { if (make_map(&mb0, b0, b_rows, b_cols, b_ld, 64, 64)) return -1; }
+  const int b_atoms = mode == GEMM_GATE_UP ? 2 : 4;
+  if (mode == GEMM_WGRAD) { if (make_map(&mb0, b0, b_rows, b_cols, b_ld, 64, 64)) return -1; }   // token-major operands: 2-D boxes are faster
+  else if (b_mn) { if (make_map_mn(&mb0, b0, b_rows, b_cols, b_ld, b_atoms)) return -1; }
   else      { if (make_map(&mb0, b0, b_rows, b_cols, b_ld, 64, kBN)) return -1; }
-  if (b1) { if (make_map(&mb1, b1, b_rows, b_cols, b_ld, 64, b_mn ? 64 : kBN)) return -1; }
+  if (b1) { if (b_mn ? make_map_mn(&mb1, b1, b_rows, b_cols, b_ld, b_atoms) : make_map(&mb1, b1, b_rows, b_cols, b_ld, 64, kBN)) return -1; }
   else mb1 = mb0;
   // output map: one 32-row x 128-byte box per epilogue warp and chunk
   if (mode == GEMM_WGRAD) { if (make_map(&mo, args.out, (int64_t)args.G * args.M_w, args.N, args.N, 32, 32, true)) return -1; }
   else if (mode == GEMM_GATE_UP) mo = ma;
   else { if (make_map(&mo, args.out, a_rows, args.N, args.ldo, 64, 32)) return -1; }
-  const size_t smem = (size_t)kStages * kStageBytes + kStagingBytes + 1024;
-  dim3 grid(num_ctas), block(kGemmThreads);
+  dim3 grid(num_ctas);
 #define MEP_GEMM_CASE(M)                                                                             \
   case M:                                                                                            \
-    MEP_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    grouped_gemm_kernel<M><<<grid, block, smem, stream>>>(ma, mb0, mb1, mo, args);                       \
+    MEP_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<M>::kSmem)); \
+    grouped_gemm_kernel<M><<<grid, dim3(GemmCfg<M>::kThreads), GemmCfg<M>::kSmem, stream>>>(ma, mb0, mb1, mo, args);                       \
     break;
   switch (mode) {
     MEP_GEMM_CASE(GEMM_GATE_UP) MEP_GEMM_CASE(GEMM_DOWN) MEP_GEMM_CASE(GEMM_DGRAD)
