@@ -177,9 +177,17 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P,
 
   // ---------------- P0
   if (blockIdx.x == 0) {
-    for (int i = tid; i < R * E; i += nt) {
-      const int p = i / E, e = i - p * E;
-      ((int*)peer_ptr(c, p, c.off_tpe))[(size_t)c.rank * E + e] = a.tpe[e];
+    if (c.mc_base != nullptr && (E & 3) == 0 && R > 1) {
+      // NVSwitch multicast: one 16-byte store per four experts reaches every rank's table
+      char* row = c.mc_base + c.off_tpe + (size_t)c.rank * E * 4;
+      for (int e4 = tid; e4 < E / 4; e4 += nt)
+        multimem_st_v4(row + (size_t)e4 * 16, *reinterpret_cast<const int4*>(a.tpe + 4 * e4));
+      fence_proxy_alias();
+    } else {
+      for (int i = tid; i < R * E; i += nt) {
+        const int p = i / E, e = i - p * E;
+        ((int*)peer_ptr(c, p, c.off_tpe))[(size_t)c.rank * E + e] = a.tpe[e];
+      }
     }
     for (int d = tid; d < R; d += nt) c.send_cnt[d] = 0ull;
   }

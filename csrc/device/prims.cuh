@@ -61,6 +61,15 @@ __device__ __forceinline__ void st_na_v4(void* p, int4 v) {
   asm volatile("st.global.L1::no_allocate.v4.s32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// ---------------------------------------------------------------- NVSwitch multicast
+// One store, delivered by the switch to the same offset of every rank's chunk.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, int4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               :: "l"(mc_addr), "f"(__int_as_float(v.x)), "f"(__int_as_float(v.y)), "f"(__int_as_float(v.z)), "f"(__int_as_float(v.w)) : "memory");
+}
+// Orders accesses made through the multicast alias against accesses through the ordinary mapping.
+__device__ __forceinline__ void fence_proxy_alias() { asm volatile("fence.proxy.alias;" ::: "memory"); }
+
 // ---------------------------------------------------------------- peer addressing
 __device__ __forceinline__ char* peer_ptr(const MepRankCtx& c, int r, int64_t off) {
   return c.heap_base + (int64_t)r * c.chunk_stride + off;

@@ -67,6 +67,9 @@ typedef struct MepRankCtx {
   // then 2 words per record: %globaltimer ns, (kernel << 48 | site << 32 | cta << 8 | warp)
   unsigned long long* trace;
   int64_t trace_cap;
+  // NVSwitch multicast alias of one chunk (null = not available): a multimem store to
+  // mc_base + off lands at offset off of EVERY rank's chunk
+  char* mc_base;
 } MepRankCtx;
 
 typedef struct MepCtxPack { const MepRankCtx* ctx[MEP_MAX_VRANKS]; } MepCtxPack;

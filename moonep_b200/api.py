@@ -208,7 +208,7 @@ class Buffer(OpsMixin):
 
     def __init__(self, S: int, H: int, K: int, E: int, num_ep_ranks: int, num_sms: int | None = None,
                  token_padding: int = 128, group=None, comm_stream_priority: int = -1,
-                 enable_pdl: bool = True, explicitly_destroy: bool = False, multicast: bool = False):
+                 enable_pdl: bool = True, explicitly_destroy: bool = False, multicast: bool | None = None):
         assert isinstance(comm_stream_priority, int), \
             f"comm_stream_priority must be an int, got {type(comm_stream_priority).__name__}"
         assert isinstance(enable_pdl, bool), f"enable_pdl must be a bool, got {type(enable_pdl).__name__}"
@@ -220,6 +220,8 @@ class Buffer(OpsMixin):
         self._heap = None
         self._comm_stream = None
         self._group = group
+        if multicast is None:      # NVSwitch multicast for the planner's histogram exchange (optional)
+            multicast = os.environ.get("MOONEP_MULTICAST", "0") == "1"
 
         num_sms, max_sms = validate_num_sms(
             num_sms, lambda: torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)

@@ -98,6 +98,7 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
         setattr(c, name, s[name].data_ptr())
     c.status = st.status.data_ptr()
     c.wait_budget_ns = wait_budget_ns() if budget_ns is None else budget_ns
+    c.mc_base = getattr(heap, "mc_base", 0) or None
     if os.environ.get("MOONEP_TRACE") == "1":
         cap = int(os.environ.get("MOONEP_TRACE_RECORDS", "65536"))
         s["trace"] = torch.zeros(1 + 2 * cap, dtype=torch.int64, device=dev)

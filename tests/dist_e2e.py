@@ -60,6 +60,8 @@ def main():
     E = R * epn
     Hp = 128
     buf = Buffer(S, H, K, E, R, num_sms=16, token_padding=pad)
+    if rank == 0:
+        print(f"[dist_e2e] multicast alias {'active' if buf._heap.mc_base else 'off'}", flush=True)
     pools = None
     try:
         pools = run_scenario(buf, rank, R, dev, S, H, K, epn, pad, E, Hp)

@@ -198,3 +198,55 @@ def test_public_buffer_r1(cuda_device):
     buf.destroy()
     assert buf.destroyed
     buf.destroy()
+
+
+def test_prefetch_with_scales_and_int8(cuda_device):
+    """Six tensors in one launch: uint8 packed weights plus their block scales (byte-typed copy)."""
+    R, epn, S, K, H = 4, 3, 150, 6, 64
+    cl, cp, plans, *_ = run_case(S, K, epn, H, R, 3, 16, "biased", sigma=2.0, with_weights=False)
+    assert (cp.experts_to_copy >= 0).any()
+    dev = cuda_device
+    g = torch.Generator().manual_seed(9)
+    shapes = [((48, 32), torch.uint8), ((48, 32), torch.uint8), ((32, 48), torch.int8),
+              ((48, 2), torch.uint8), ((48, 2), torch.uint8), ((32, 4), torch.uint8)]
+    local, pools = [], []
+    for shp, dt in shapes:
+        local.append([torch.randint(0, 100, (epn, *shp), generator=g).to(dt) for _ in range(R)])
+        pool, flat = cl.make_pool((epn, *shp), dt, pad_elems=16)
+        flat.fill_(7)
+        pools.append(pool)
+    pairs = [[(local[i][r].to(dev), pools[i]) for i in range(6)] for r in range(R)]
+    cl.prefetch(plans, pairs)
+    torch.cuda.synchronize()
+    cl.check()
+    for i, (shp, dt) in enumerate(shapes):
+        exp = [torch.full((epn, *shp), 7, dtype=dt) for _ in range(R)]
+        simops.prefetch(cp, local[i], exp)
+        for r in range(R):
+            assert torch.equal(pools[i][r].cpu(), exp[r]), f"tensor {i}: slots of rank {r} differ"
+
+
+def test_planner_large_expert_count(cuda_device):
+    """E above the shared-memory table capacity takes the global-memory code paths."""
+    from moonep_b200 import engine
+    from moonep_b200.sim import plan_cluster
+    from moonep_b200.sim.local_cluster import LocalCluster
+    import numpy as np
+    R, epn, S, K, pad = 2, 4200, 300, 4, 2
+    E = R * epn
+    g = torch.Generator().manual_seed(4)
+    topk = [torch.randint(0, E, (S, K), dtype=torch.int32, generator=g) for _ in range(R)]
+    for t in topk:                       # a few hot experts so that rank 1 needs help
+        t[:, 0] = epn + (t[:, 0] % 3)
+    tpe = [torch.bincount(t.flatten().long(), minlength=E).to(torch.int32) for t in topk]
+    cp = plan_cluster(np.stack([t.numpy() for t in topk]), E, pad)
+    cl = LocalCluster(S, 64, K, E, R, num_sms=2, token_padding=pad)
+    st = cl._states
+    plans, cus = zip(*[engine.allocate_plan(s) for s in st])
+    engine.launch_planning(st, [t.reshape(-1).to(cuda_device) for t in topk], [t.to(cuda_device) for t in tpe], list(plans), list(cus))
+    torch.cuda.synchronize()
+    cl.check()
+    for r in range(R):
+        assert torch.equal(plans[r].dst.cpu().long(), torch.from_numpy(cp.dst[r]))
+        assert torch.equal(cus[r].cpu().long(), torch.from_numpy(cp.cu_seqlens[r]))
+        assert torch.equal(plans[r].experts_to_copy.cpu().long(), torch.from_numpy(cp.experts_to_copy))
