@@ -21,7 +21,7 @@ struct DispatchArgs {
   const float* weights;          // [S, K] or null
   const int32_t* dst;            // [N] plan
   const int32_t* zero_fill;      // [2epn, 2] plan
-  int32_t fresh;                 // 1: publish duplicate-table counts to the peers
+  int32_t fresh;                 // 1 or 2: publish duplicate-table counts to the peers (value - 1 = send_cnt half)
   int32_t entry_barrier;         // 1: cross-rank barrier before the first remote write
 };
 struct DispatchArgsPack { DispatchArgs a[MEP_MAX_VRANKS]; };
@@ -101,7 +101,7 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   if (a.fresh && blockIdx.x == 0) {
     // tell every destination how many groups / duplicate offsets this rank appended
     for (int d = tid; d < c.R; d += blockDim.x) {
-      const unsigned long long v = c.send_cnt[d];
+      const unsigned long long v = c.send_cnt[(size_t)(a.fresh - 1) * c.R + d];
       int* cnt = (int*)peer_ptr(c, d, c.off_dupcnt) + 2 * c.rank;
       cnt[0] = (int)(v >> 32); cnt[1] = (int)(v & 0xffffffffu);
     }

@@ -27,9 +27,15 @@ struct GradReduceArgs {
 };
 struct GradReduceArgsPack { GradReduceArgs a[MEP_MAX_VRANKS]; };
 
-constexpr int kRedThreads = 512;
-constexpr int kRedVec = 4;            // float4 per thread and pass
-constexpr int64_t kRedChunk = (int64_t)kRedThreads * kRedVec * 4;   // floats per work unit
+constexpr int kRedThreads = 384;          // 12 warps
+constexpr int kRedSlots = 32;             // 16-byte vectors per lane in one warp stage
+
+__device__ __forceinline__ void cp_async16(uint32_t saddr, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(saddr), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
 
 __device__ __forceinline__ float4 f4add(float4 a, const int4& b) {
   a.x += __int_as_float(b.x); a.y += __int_as_float(b.y); a.z += __int_as_float(b.z); a.w += __int_as_float(b.w);
@@ -39,13 +45,14 @@ __device__ __forceinline__ float4 f4add(float4 a, const int4& b) {
 __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack P, GradReduceArgsPack A) {
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const GradReduceArgs& a = A.a[blockIdx.y];
-  extern __shared__ int s_mem[];
+  extern __shared__ __align__(128) int s_mem[];
   const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x;
   const int R = c.R, epn = c.epn, lo = c.rank * epn;
   int* s_cnt = s_mem;                 // [epn]
   int* s_off = s_mem + epn;           // [epn + 1]
   int* s_act = s_off + epn + 1;       // [epn] active local experts
   int* s_src = s_act + epn;           // [R * epn] sources grouped per expert
+  unsigned char* s_stage = reinterpret_cast<unsigned char*>(s_mem) + (((size_t)(3 * epn + 1 + R * epn) * 4 + 127) & ~(size_t)127);
   __shared__ int s_nact;
 
   for (int i = tid; i < epn; i += nt) s_cnt[i] = 0;
@@ -74,63 +81,69 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
   __syncthreads();
   const int nact = s_nact;
 
-  int64_t chunks_per_exp = 0;
-  for (int t = 0; t < a.ntensors; ++t) chunks_per_exp += (a.t[t].expert_elems + kRedChunk - 1) / kRedChunk;
-  const int64_t total = (int64_t)nact * chunks_per_exp;
-  for (int64_t u = blockIdx.x; u < total; u += nb) {
-    const int ai = (int)(u / chunks_per_exp);
-    int64_t ck = u - (int64_t)ai * chunks_per_exp;
-    int t = 0;
-    for (;; ++t) { const int64_t n = (a.t[t].expert_elems + kRedChunk - 1) / kRedChunk; if (ck < n) break; ck -= n; }
-    const ReduceTensor& T = a.t[t];
+  // Each warp owns a 16 KB shared-memory stage. Per pass it fetches P 16-byte vectors per lane from
+  // EVERY replica with asynchronous copies (no registers held while the NVLink reads are in flight),
+  // loads the same vectors of the local grad, waits for its own copies and adds the replicas in list
+  // order. 12 warps x 16 KB keep up to 192 KB per SM in flight.
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+  const int gw = blockIdx.x * nwarps + warp, gnw = nb * nwarps;
+  const uint32_t stage = smem_u32(s_stage) + (uint32_t)warp * (kRedSlots * 32 * 16);
+  const unsigned char* stage_g = s_stage + (size_t)warp * (kRedSlots * 32 * 16);
+  for (int ai = 0; ai < nact; ++ai) {
     const int le = s_act[ai];
     const int* srcs = s_src + s_off[le]; const int ns = s_off[le + 1] - s_off[le];
-    const int64_t beg = ck * kRedChunk;
-    const int64_t len = (T.expert_elems - beg) < kRedChunk ? (T.expert_elems - beg) : kRedChunk;
-    float* lp = T.local + (int64_t)le * T.expert_elems + beg;
-    const int64_t ebytes = T.expert_elems * 4;
-    const int nvec = (int)(len >> 2);
-    for (int v0 = 0; v0 < nvec; v0 += kRedVec * nt) {
-      float4 acc[kRedVec];
+    int P = kRedSlots / ns; if (P > 8) P = 8; if (P < 1) P = 1;
+    const int npass_src = (ns + kRedSlots - 1) / kRedSlots;     // > 1 only if an expert has more than 32 replicas
+    for (int t = 0; t < a.ntensors; ++t) {
+      const ReduceTensor& T = a.t[t];
+      const int64_t ebytes = T.expert_elems * 4;
+      const int64_t nvec = T.expert_elems >> 2;
+      float* lp = T.local + (int64_t)le * T.expert_elems;
+      const int64_t unit_vecs = 32 * (int64_t)P;
+      const int64_t nunits = (nvec + unit_vecs - 1) / unit_vecs;
+      for (int64_t u = gw; u < nunits; u += gnw) {
+        const int64_t v0 = u * unit_vecs;
+        float4 acc[8];
 #pragma unroll
-      for (int q = 0; q < kRedVec; ++q) {
-        const int v = v0 + q * nt + tid;
-        acc[q] = v < nvec ? *reinterpret_cast<const float4*>(lp + (size_t)v * 4) : make_float4(0, 0, 0, 0);
-      }
-      for (int j0 = 0; j0 < ns; j0 += 2) {          // 2 sources x kRedVec vectors in flight per thread
-        int4 x[2][kRedVec];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const bool on = j0 + j < ns;
-          const int idx = on ? srcs[j0 + j] : 0, d = idx / epn, b = idx - d * epn;
-          const char* rp = T.pool + (int64_t)d * T.rank_stride + (int64_t)b * ebytes + beg * 4;
-#pragma unroll
-          for (int q = 0; q < kRedVec; ++q) {
-            const int v = v0 + q * nt + tid;
-            x[j][q] = make_int4(0, 0, 0, 0);
-            if (on && v < nvec) x[j][q] = ld_peer_v4(rp + (size_t)v * 16);
+        for (int p = 0; p < 8; ++p) {
+          const int64_t v = v0 + (int64_t)p * 32 + lane;
+          acc[p] = (p < P && v < nvec) ? *reinterpret_cast<const float4*>(lp + v * 4) : make_float4(0, 0, 0, 0);
+        }
+        for (int sp = 0; sp < npass_src; ++sp) {
+          const int j_beg = sp * kRedSlots, j_end = ns < j_beg + kRedSlots ? ns : j_beg + kRedSlots;
+          for (int j = j_beg; j < j_end; ++j) {
+            const int idx = srcs[j], d = idx / epn, b = idx - d * epn;
+            const char* rp = T.pool + (int64_t)d * T.rank_stride + (int64_t)b * ebytes;
+            for (int p = 0; p < P; ++p) {
+              const int64_t v = v0 + (int64_t)p * 32 + lane;
+              if (v < nvec) cp_async16(stage + (uint32_t)(((j - j_beg) * P + p) * 32 + lane) * 16, rp + v * 16);
+            }
           }
+          cp_async_commit_wait_all();
+          for (int j = j_beg; j < j_end; ++j)
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+              const int64_t v = v0 + (int64_t)p * 32 + lane;
+              if (p < P && v < nvec)
+                acc[p] = f4add(acc[p], *reinterpret_cast<const int4*>(stage_g + (size_t)(((j - j_beg) * P + p) * 32 + lane) * 16));
+            }
         }
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          if (j0 + j < ns) {
-#pragma unroll
-            for (int q = 0; q < kRedVec; ++q) acc[q] = f4add(acc[q], x[j][q]);
+        for (int p = 0; p < 8; ++p) {
+          const int64_t v = v0 + (int64_t)p * 32 + lane;
+          if (p < P && v < nvec) *reinterpret_cast<float4*>(lp + v * 4) = acc[p];
+        }
+      }
+      if (blockIdx.x == 0) {     // ragged tail (expert size not a multiple of four floats)
+        for (int64_t i = (nvec << 2) + tid; i < T.expert_elems; i += nt) {
+          float accs = lp[i];
+          for (int j = 0; j < ns; ++j) {
+            const int idx = srcs[j], d = idx / epn, b = idx - d * epn;
+            accs += __ldcg(reinterpret_cast<const float*>(T.pool + (int64_t)d * T.rank_stride + (int64_t)b * ebytes) + i);
           }
+          lp[i] = accs;
+        }
       }
-#pragma unroll
-      for (int q = 0; q < kRedVec; ++q) {
-        const int v = v0 + q * nt + tid;
-        if (v < nvec) *reinterpret_cast<float4*>(lp + (size_t)v * 4) = acc[q];
-      }
-    }
-    for (int64_t i = ((int64_t)nvec << 2) + tid; i < len; i += nt) {   // ragged tail
-      float acc = lp[i];
-      for (int j = 0; j < ns; ++j) {
-        const int idx = srcs[j], d = idx / epn, b = idx - d * epn;
-        acc += __ldcg(reinterpret_cast<const float*>(T.pool + (int64_t)d * T.rank_stride + (int64_t)b * ebytes) + beg + i);
-      }
-      lp[i] = acc;
     }
   }
 
@@ -157,8 +170,9 @@ extern "C" int mep_launch_grad_reduce(int nv, const MepRankCtx* const* ctxs, con
   MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "grad_reduce: nv=%d out of range", nv);
   MepCtxPack P = {}; mep::GradReduceArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  const size_t smem = ((size_t)3 * epn + 1 + (size_t)R * epn) * sizeof(int);
-  MEP_REQUIRE(smem <= 160 * 1024, "grad_reduce: R*epn=%d exceeds the source-list capacity", R * epn);
+  const size_t lists = ((((size_t)3 * epn + 1 + (size_t)R * epn) * sizeof(int)) + 127) & ~(size_t)127;
+  MEP_REQUIRE(lists <= 30 * 1024, "grad_reduce: R*epn=%d exceeds the source-list capacity", R * epn);
+  const size_t smem = lists + (size_t)(mep::kRedThreads / 32) * mep::kRedSlots * 32 * 16;
   return mep::launch_cooperative(mep::grad_reduce_kernel, dim3(num_sms, nv), dim3(mep::kRedThreads), smem,
                                  stream, false, P, A);
 }

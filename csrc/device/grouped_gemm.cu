@@ -34,7 +34,8 @@ struct GemmArgs {
   int32_t accumulate;          // WGRAD: 1 -> out += acc, 0 -> out = acc
   int32_t g_begin, g_end;      // only groups in [g_begin, g_end) are computed
   int32_t zero_empty_below;    // WGRAD without accumulate: empty groups g < this get zeros
-  int32_t pad_;
+  int32_t diag;                // diagnostics only (results invalid): 1 = MMA does not wait for operands and no
+                               // TMA loads are issued, 2 = epilogue discards the accumulators
   void* out;                   // bf16 [rows, ldo]; WGRAD: fp32 [G, M_w, N]
   void* out2;                  // GATE_UP: optional bf16 [rows, 2N] pre-activations (gate | up)
   const float* row_scale;      // GATE_UP / DOWN: optional per-row factor [rows]
@@ -142,7 +143,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // ---------------- TMA producer (one thread)
     if (lane == 0) {
       int it = 0, gcur = 0; TileInfo ti;
-      for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x) {
+      for (int t = blockIdx.x; t < ntiles && !s_abort && !(args.diag & 1); t += gridDim.x) {
         get_tile(t, gcur, ti);
         for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
@@ -198,7 +199,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         bool ok = true;
         for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
-          if (!mbar_wait_bounded(&full_bar[s], ph, args.budget_ns)) { fail(3, t); ok = false; break; }
+          if (!(args.diag & 1) && !mbar_wait_bounded(&full_bar[s], ph, args.budget_ns)) { fail(3, t); ok = false; break; }
           tc::fence_after_sync();
           const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kABytes;
 #pragma unroll
@@ -207,7 +208,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const uint64_t bd = B_MN ? tc::smem_desc(sb + k * 2048, kAtomBytes, 1024) : tc::smem_desc(sb + k * 32, 16, 1024);
             tc::mma_bf16(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
           }
-          tc::mma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
+          if (!(args.diag & 1)) tc::mma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
         }
         if (!ok) break;
         tc::mma_commit(&tfull_bar[acc]);      // accumulator complete
@@ -239,7 +240,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (!ok) { if (lane == 0) fail(4, t); break; }
       tc::fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * kBN;
-      if (MODE == GEMM_GATE_UP) {
+      if (args.diag & 2) {
+        // diagnostics: hand the accumulator back untouched
+      } else if (MODE == GEMM_GATE_UP) {
         const size_t row = (size_t)ti.row0 + r_in_tile;
         __nv_bfloat16* orow = (__nv_bfloat16*)args.out + row * args.ldo + ti.n0;
         __nv_bfloat16* grow = args.out2 ? (__nv_bfloat16*)args.out2 + row * (size_t)(2 * args.N) + ti.n0 : nullptr;

@@ -28,7 +28,7 @@ __device__ __forceinline__ int vload(const int* p) { return *(const volatile int
 __device__ __forceinline__ void vstore(int* p, int v) { *(volatile int*)p = v; }
 
 // ---- P1 on CTA 0: receiver selection, expert split, layout (see file header).
-__device__ void solve(const MepRankCtx& c, const PlanArgs& a, int* s_e, bool e_in_smem) {
+__device__ void solve(const MepRankCtx& c, const PlanArgs& a, int* s_e, bool e_in_smem, bool emit = true) {
   __shared__ int s_bal[MEP_MAX_RANKS];
   __shared__ int s_recv_from[MEP_MAX_RANKS];
   __shared__ int s_quota[MEP_MAX_RANKS];
@@ -118,7 +118,7 @@ __device__ void solve(const MepRankCtx& c, const PlanArgs& a, int* s_e, bool e_i
   for (int d = warp; d < R; d += nwarps) {
     const int h = s_recv_from[d];
     int* etc = c.etc_all + (size_t)d * epn;
-    for (int b = lane; b < epn; b += 32) { vstore(etc + b, -1); a.experts_to_copy[(size_t)d * epn + b] = -1; }
+    for (int b = lane; b < epn; b += 32) { vstore(etc + b, -1); if (emit) a.experts_to_copy[(size_t)d * epn + b] = -1; }
     __syncwarp();
     int nrem = 0;
     if (h >= 0) {
@@ -129,7 +129,7 @@ __device__ void solve(const MepRankCtx& c, const PlanArgs& a, int* s_e, bool e_i
         if (has) {
           const int pos = nrem + __popc(bal & lanemask_lt());
           vstore(etc + pos, h * epn + j);
-          a.experts_to_copy[(size_t)d * epn + pos] = h * epn + j;
+          if (emit) a.experts_to_copy[(size_t)d * epn + pos] = h * epn + j;
         }
         nrem += __popc(bal);
       }
@@ -147,7 +147,7 @@ __device__ void solve(const MepRankCtx& c, const PlanArgs& a, int* s_e, bool e_i
       const int beg = start + incl - padded, end = start + incl;
       if (g < 2 * epn) {
         if (cnt > 0) c.expert_off[(size_t)d * E + e] = beg;
-        if (d == c.rank) {
+        if (d == c.rank && emit) {
           a.cu_seqlens[g] = end;
           const bool haspad = cnt > 0 && padded > cnt;
           a.zero_fill[2 * g] = haspad ? beg + cnt : 0;
@@ -158,78 +158,32 @@ __device__ void solve(const MepRankCtx& c, const PlanArgs& a, int* s_e, bool e_i
     }
   }
   __syncthreads();
-  if (tid == 0) { a.remote_stats[0] = s_recvn[c.rank]; a.remote_stats[1] = s_send[c.rank]; }
+  if (tid == 0 && emit) { a.remote_stats[0] = s_recvn[c.rank]; a.remote_stats[1] = s_send[c.rank]; }
   for (int r = tid; r < R; r += nt) { c.stats_all[2 * r] = s_recvn[r]; c.stats_all[2 * r + 1] = s_send[r]; }
 }
 
-__global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P, PlanArgsPack A) {
-  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
-  const PlanArgs& a = A.a[blockIdx.y];
-  extern __shared__ int s_e[];
-  __shared__ int s_raw[kPlanThreads];
-  __shared__ unsigned char s_dest[kPlanThreads];
-  __shared__ int s_pos[kPlanThreads];                 // CTA-local (group<<16 | loff) position of a primary's group
-  __shared__ unsigned long long s_cnt[MEP_MAX_RANKS]; // groups<<32 | loffs reserved by this CTA per destination
-  __shared__ unsigned long long s_base[MEP_MAX_RANKS];
-  const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
+struct PlanTables { const int* tpe_prefix; const int* alloc_cumsum; const int* expert_off; };
+template <bool SM> __device__ __forceinline__ int ldt(const int* p) { return SM ? *p : __ldcg(p); }
+
+struct PlanSmem {
+  int raw[kPlanThreads];
+  unsigned char dest[kPlanThreads];
+  int pos[kPlanThreads];                 // CTA-local (group<<16 | loff) position of a primary's group
+  unsigned long long cnt[MEP_MAX_RANKS]; // groups<<32 | loffs reserved by this CTA per destination
+  unsigned long long base[MEP_MAX_RANKS];
+};
+
+// P2 for one block of entries: `cnt[e]` holds, on entry, the number of entries of expert e in earlier
+// blocks of this rank. FAST: the lookup tables live in this CTA's shared memory.
+template <bool FAST>
+__device__ __forceinline__ void assign_vblock(const MepRankCtx& c, const PlanArgs& a, const PlanTables& T, int v,
+                                              int* cnt, PlanSmem& sm, int* tbl = nullptr) {
+  int* s_raw = sm.raw; unsigned char* s_dest = sm.dest; int* s_pos = sm.pos;
+  unsigned long long* s_cnt = sm.cnt; unsigned long long* s_base = sm.base;
+  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
   const int R = c.R, E = c.E, N = c.N, K = c.K, NvS = c.NvS, VB = c.vblock_entries;
-  const bool e_in_smem = E <= kSmemECap;
-
-  // ---------------- P0
-  if (blockIdx.x == 0) {
-    if (c.mc_base != nullptr && (E & 3) == 0 && R > 1) {
-      // NVSwitch multicast: one 16-byte store per four experts reaches every rank's table
-      char* row = c.mc_base + c.off_tpe + (size_t)c.rank * E * 4;
-      for (int e4 = tid; e4 < E / 4; e4 += nt)
-        multimem_st_v4(row + (size_t)e4 * 16, *reinterpret_cast<const int4*>(a.tpe + 4 * e4));
-      fence_proxy_alias();
-    } else {
-      for (int i = tid; i < R * E; i += nt) {
-        const int p = i / E, e = i - p * E;
-        ((int*)peer_ptr(c, p, c.off_tpe))[(size_t)c.rank * E + e] = a.tpe[e];
-      }
-    }
-    for (int d = tid; d < R; d += nt) c.send_cnt[d] = 0ull;
-  }
-  for (int v = blockIdx.x; v < c.num_vblocks; v += nb) {
-    int* row = c.hist + (size_t)v * E;
-    int* h = e_in_smem ? s_e : row;
-    for (int e = tid; e < E; e += nt) h[e] = 0;
-    __syncthreads();
-    const int i = v * VB + tid;
-    if (tid < VB && i < N) {
-      const int e = a.topk[i];
-      if ((unsigned)e < (unsigned)E) atomicAdd(&h[e], 1);
-      else report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 1, i, (uint32_t)e, (uint32_t)E);
-    }
-    __syncthreads();
-    if (e_in_smem) for (int e = tid; e < E; e += nt) row[e] = s_e[e];
-    __syncthreads();
-  }
-  if (!cross_rank_barrier(c, nb, 0, MEP_K_PLANNING, 10)) return;
-
-  // ---------------- P1
-  if (blockIdx.x == 0) { solve(c, a, s_e, e_in_smem); __syncthreads(); }
-  if (nb == 1 || blockIdx.x != 0) {
-    const int workers = nb == 1 ? 1 : nb - 1, me = nb == 1 ? 0 : blockIdx.x - 1;
-    for (int e = me * nt + tid; e < E; e += workers * nt) {
-      int run = 0;
-      for (int v = 0; v < c.num_vblocks; ++v) {
-        int* p = c.hist + (size_t)v * E + e;
-        const int t = __ldcg(p);
-        *p = run; run += t;
-      }
-    }
-  }
-  if (!grid_sync(c, nb, MEP_K_PLANNING, 20)) return;
-  if (aborted(c)) return;
-
-  // ---------------- P2
   const int tok_per_vb = VB / K;
-  for (int v = blockIdx.x; v < c.num_vblocks; v += nb) {
-    int* row = c.hist + (size_t)v * E;
-    int* cnt = e_in_smem ? s_e : row;
-    if (e_in_smem) for (int e = tid; e < E; e += nt) s_e[e] = __ldcg(row + e);
+  {
     for (int d = tid; d < R; d += nt) s_cnt[d] = 0ull;
     __syncthreads();
     const int i = v * VB + tid;
@@ -239,6 +193,26 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P,
     const int n_here = min(VB, N - v * VB);
     const int nw = (n_here + 31) >> 5;
     int local_cnt = 0;
+    if (tbl != nullptr) {
+      // table ranking (small E): tbl[w][e] = entries of expert e held by warp w; an exclusive scan
+      // over the warps (plus the count from earlier blocks) gives every warp its starting rank
+      for (int i = tid; i < 32 * E; i += nt) tbl[i] = 0;
+      __syncthreads();
+      unsigned m = 0;
+      const unsigned act = __ballot_sync(0xffffffffu, active);
+      if (active) {
+        m = __match_any_sync(act, e);
+        if (lane == __ffs(m) - 1) tbl[warp * E + e] = __popc(m);
+      }
+      __syncthreads();
+      for (int e2 = tid; e2 < E; e2 += nt) {
+        int run = cnt[e2];
+        for (int w = 0; w < 32; ++w) { const int t = tbl[w * E + e2]; tbl[w * E + e2] = run; run += t; }
+        cnt[e2] = run;
+      }
+      __syncthreads();
+      if (active) local_cnt = tbl[warp * E + e] + __popc(m & lanemask_lt());
+    } else
     for (int w = 0; w < nw; ++w) {       // warps in index order => stable ranking
       if (warp == w) {
         const unsigned act = __ballot_sync(0xffffffffu, active);
@@ -255,14 +229,14 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P,
     }
     int raw = 0, dr = 0;
     if (active) {
-      const int g = __ldcg(c.tpe_prefix + e) + local_cnt;
-      const int* ac = c.alloc_cumsum + (size_t)e * R;
+      const int g = ldt<FAST>(T.tpe_prefix + e) + local_cnt;
+      const int* ac = T.alloc_cumsum + (size_t)e * R;
       int lo = 0, hi = R - 1;
-      while (lo < hi) { const int mid = (lo + hi) >> 1; if (__ldcg(ac + mid) > g) hi = mid; else lo = mid + 1; }
+      while (lo < hi) { const int mid = (lo + hi) >> 1; if (ldt<FAST>(ac + mid) > g) hi = mid; else lo = mid + 1; }
       dr = lo;
-      const int prev = dr ? __ldcg(ac + dr - 1) : 0;
-      const int loff = __ldcg(c.expert_off + (size_t)dr * E + e) + (g - prev);
-      if ((unsigned)loff >= (unsigned)NvS || g >= __ldcg(ac + dr))
+      const int prev = dr ? ldt<FAST>(ac + dr - 1) : 0;
+      const int loff = ldt<FAST>(T.expert_off + (size_t)dr * E + e) + (g - prev);
+      if ((unsigned)loff >= (unsigned)NvS || g >= ldt<FAST>(ac + dr))
         report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 2, i, (uint32_t)loff, (uint32_t)NvS);
       raw = dr * NvS + loff;
     }
@@ -319,14 +293,191 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P,
   }
 }
 
+__global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P, PlanArgsPack A) {
+  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
+  const PlanArgs& a = A.a[blockIdx.y];
+  extern __shared__ int s_e[];
+  const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
+  const int R = c.R, E = c.E, N = c.N, K = c.K, NvS = c.NvS, VB = c.vblock_entries;
+  const bool e_in_smem = E <= kSmemECap;
+
+  // ---------------- P0
+  if (blockIdx.x == 0) {
+    if (c.mc_base != nullptr && (E & 3) == 0 && R > 1) {
+      // NVSwitch multicast: one 16-byte store per four experts reaches every rank's table
+      char* row = c.mc_base + c.off_tpe + (size_t)c.rank * E * 4;
+      for (int e4 = tid; e4 < E / 4; e4 += nt)
+        multimem_st_v4(row + (size_t)e4 * 16, *reinterpret_cast<const int4*>(a.tpe + 4 * e4));
+      fence_proxy_alias();
+    } else {
+      for (int i = tid; i < R * E; i += nt) {
+        const int p = i / E, e = i - p * E;
+        ((int*)peer_ptr(c, p, c.off_tpe))[(size_t)c.rank * E + e] = a.tpe[e];
+      }
+    }
+    for (int d = tid; d < R; d += nt) c.send_cnt[d] = 0ull;
+  }
+  for (int v = blockIdx.x; v < c.num_vblocks; v += nb) {
+    int* row = c.hist + (size_t)v * E;
+    int* h = e_in_smem ? s_e : row;
+    for (int e = tid; e < E; e += nt) h[e] = 0;
+    __syncthreads();
+    const int i = v * VB + tid;
+    if (tid < VB && i < N) {
+      const int e = a.topk[i];
+      if ((unsigned)e < (unsigned)E) atomicAdd(&h[e], 1);
+      else report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 1, i, (uint32_t)e, (uint32_t)E);
+    }
+    __syncthreads();
+    if (e_in_smem) for (int e = tid; e < E; e += nt) row[e] = s_e[e];
+    __syncthreads();
+  }
+  if (!cross_rank_barrier(c, nb, 0, MEP_K_PLANNING, 10)) return;
+
+  // ---------------- P1
+  if (blockIdx.x == 0) { solve(c, a, s_e, e_in_smem); __syncthreads(); }
+  if (nb == 1 || blockIdx.x != 0) {
+    const int workers = nb == 1 ? 1 : nb - 1, me = nb == 1 ? 0 : blockIdx.x - 1;
+    for (int e = me * nt + tid; e < E; e += workers * nt) {
+      int run = 0;
+      for (int v = 0; v < c.num_vblocks; ++v) {
+        int* p = c.hist + (size_t)v * E + e;
+        const int t = __ldcg(p);
+        *p = run; run += t;
+      }
+    }
+  }
+  if (!grid_sync(c, nb, MEP_K_PLANNING, 20)) return;
+  if (aborted(c)) return;
+
+  // ---------------- P2
+  __shared__ PlanSmem sm;
+  const PlanTables T = {c.tpe_prefix, c.alloc_cumsum, c.expert_off};
+  for (int v = blockIdx.x; v < c.num_vblocks; v += nb) {
+    int* row = c.hist + (size_t)v * E;
+    int* cnt = e_in_smem ? s_e : row;
+    if (e_in_smem) for (int e = tid; e < E; e += nt) s_e[e] = __ldcg(row + e);
+    assign_vblock<false>(c, a, T, v, cnt, sm);
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Fast path (E <= 2048, E*R <= 8192): no grid-wide barrier at all.
+//   * CTA 0 publishes this rank's histogram and then release-stores the launch epoch (counted by
+//     the host, identical on all ranks) into every peer's flag slot;
+//   * EVERY CTA waits for all peers' epochs itself and then solves the plan redundantly into its
+//     own shared memory (the solve is a few microseconds and fully deterministic), so nothing has
+//     to be exchanged between the CTAs of a rank;
+//   * the count of same-expert entries in earlier blocks is obtained by scanning the top-k prefix
+//     directly instead of exchanging block histograms.
+// send_cnt is double-buffered by epoch parity: this launch accumulates into half (epoch & 1) and
+// clears the other half for the next launch.
+__global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPack P, PlanArgsPack A) {
+  const MepRankCtx c = *P.ctx[blockIdx.y];
+  const PlanArgs a = A.a[blockIdx.y];
+  extern __shared__ int s_dyn[];
+  __shared__ PlanSmem sm;
+  __shared__ int s_fail;
+  const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x;
+  const int R = c.R, E = c.E, N = c.N, VB = c.vblock_entries;
+  int* s_cnt = s_dyn;
+  int* s_rem = s_cnt + E;
+  int* s_count = s_rem + E;
+  int* s_tpre = s_count + E;
+  int* s_etc = s_tpre + E;
+  int* s_stats = s_etc + E;
+  int* s_alloc = s_stats + 2 * MEP_MAX_RANKS;
+  int* s_acum = s_alloc + E * R;
+  int* s_expoff = s_acum + E * R;
+  int* s_tbl = E <= kFastTableE ? s_expoff + E * R : nullptr;     // [32, E] ranking table
+  const uint32_t ep = a.epoch;
+  unsigned long long* send_cur = c.send_cnt + (size_t)(ep & 1u) * R;
+
+  if (tid == 0) s_fail = 0;
+  if (blockIdx.x == 0) {
+    if (c.mc_base != nullptr && (E & 3) == 0 && R > 1) {
+      char* row = c.mc_base + c.off_tpe + (size_t)c.rank * E * 4;
+      for (int e4 = tid; e4 < E / 4; e4 += nt)
+        multimem_st_v4(row + (size_t)e4 * 16, *reinterpret_cast<const int4*>(a.tpe + 4 * e4));
+      fence_proxy_alias();
+    } else {
+      for (int i = tid; i < R * E; i += nt) {
+        const int p = i / E, e = i - p * E;
+        ((int*)peer_ptr(c, p, c.off_tpe))[(size_t)c.rank * E + e] = a.tpe[e];
+      }
+    }
+    for (int d = tid; d < R; d += nt) c.send_cnt[(size_t)((ep & 1u) ^ 1u) * R + d] = 0ull;
+    __syncthreads();
+    if (R > 1)
+      for (int p = tid; p < R; p += nt) {
+        __threadfence_system();
+        st_release_sys((uint32_t*)peer_ptr(c, p, c.off_bar) + c.rank, ep);
+      }
+  }
+
+  auto count_prefix = [&](int v) {        // s_cnt[e] = entries of expert e in blocks < v of this rank
+    for (int e = tid; e < E; e += nt) s_cnt[e] = 0;
+    __syncthreads();
+    const int lim = v * VB;
+    for (int i0 = 0; i0 < lim; i0 += nt) {          // warp-aggregated: one shared-memory add per distinct expert and warp
+      const int i = i0 + tid;
+      const bool on = i < lim;
+      int e = on ? a.topk[i] : 0;
+      if (on && (unsigned)e >= (unsigned)E) { report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 1, i, (uint32_t)e, (uint32_t)E); e = 0; }
+      const unsigned act = __ballot_sync(0xffffffffu, on);
+      if (on) {
+        const unsigned m = __match_any_sync(act, e);
+        if ((threadIdx.x & 31) == __ffs(m) - 1) atomicAdd(&s_cnt[e], __popc(m));
+      }
+    }
+    __syncthreads();
+  };
+  if ((int)blockIdx.x < c.num_vblocks) count_prefix(blockIdx.x);
+
+  if (R > 1) {
+    for (int p = tid; p < R; p += nt) {
+      const uint32_t* slot = (const uint32_t*)peer_ptr(c, c.rank, c.off_bar) + p;
+      uint32_t seen = 0;
+      const bool ok = bounded_wait(c, [&] { seen = ld_acquire_sys(slot); return (int32_t)(seen - ep) >= 0; });
+      if (!ok) { report(c, MEP_ERR_PEER_TIMEOUT, MEP_K_PLANNING, 11, p, seen, ep); s_fail = 1; }
+    }
+  }
+  __syncthreads();
+  if (s_fail) return;
+
+  MepRankCtx cl = c;
+  cl.count = s_count; cl.tpe_prefix = s_tpre; cl.remaining = s_rem; cl.alloc = s_alloc;
+  cl.alloc_cumsum = s_acum; cl.expert_off = s_expoff; cl.etc_all = s_etc; cl.stats_all = s_stats;
+  solve(cl, a, s_rem, true, blockIdx.x == 0);
+  __syncthreads();
+
+  cl.send_cnt = send_cur;
+  const PlanTables T = {s_tpre, s_acum, s_expoff};
+  for (int v = blockIdx.x; v < c.num_vblocks; v += nb) {
+    if (v != (int)blockIdx.x) count_prefix(v);
+    assign_vblock<true>(cl, a, T, v, s_cnt, sm, s_tbl);
+  }
+}
+
 }  // namespace mep
 
 extern "C" int mep_launch_planning(int nv, const MepRankCtx* const* ctxs, const mep::PlanArgs* args,
-                                   int num_sms, int E, cudaStream_t stream) {
+                                   int num_sms, int E, int R, cudaStream_t stream) {
   MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "planning: nv=%d out of range", nv);
   MepCtxPack P = {}; mep::PlanArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  if (E <= mep::kFastMaxE && (long long)E * R <= mep::kFastMaxER && args[0].epoch != 0) {
+    const size_t smem = ((size_t)6 * E + 2 * MEP_MAX_RANKS + (size_t)3 * E * R + (E <= mep::kFastTableE ? 32 * (size_t)E : 0)) * sizeof(int);
+    return mep::launch_cooperative(mep::planning_fast_kernel, dim3(num_sms, nv), dim3(mep::kPlanThreads), smem,
+                                   stream, false, P, A);
+  }
   const size_t smem = (E <= mep::kSmemECap ? (size_t)E : 1) * sizeof(int);
   return mep::launch_cooperative(mep::planning_kernel, dim3(num_sms, nv), dim3(mep::kPlanThreads), smem,
                                  stream, false, P, A);
+}
+
+// 1 if a geometry is served by the barrier-free planning kernel (the caller then counts epochs).
+extern "C" int mep_planning_is_fast(int E, int R) {
+  return (E <= mep::kFastMaxE && (long long)E * R <= mep::kFastMaxER) ? 1 : 0;
 }

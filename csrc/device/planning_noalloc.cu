@@ -111,7 +111,7 @@ extern "C" int mep_plan_single_rank_noalloc(const int32_t* topk, const int32_t* 
   MepCtxPack P = {};
   P.ctx[0] = (const MepRankCtx*)(base + o_ctx);
   mep::PlanArgsPack A = {};
-  A.a[0] = mep::PlanArgs{topk, tokens_per_expert, dst, cu_seqlens, experts_to_copy, zero_fill_ranges, remote_stats};
+  A.a[0] = mep::PlanArgs{topk, tokens_per_expert, dst, cu_seqlens, experts_to_copy, zero_fill_ranges, remote_stats, 0u, 0};
   const size_t smem = (E <= mep::kSmemECap ? (size_t)E : 1) * sizeof(int);
   return mep::launch_cooperative(mep::planning_kernel, dim3(kCtas, 1), dim3(mep::kPlanThreads), smem, stream, false, P, A);
 }

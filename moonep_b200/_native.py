@@ -45,7 +45,7 @@ class MepRankCtx(C.Structure):
 
 class PlanArgs(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("topk", "tpe", "dst", "cu_seqlens", "experts_to_copy",
-                                          "zero_fill", "remote_stats")]
+                                          "zero_fill", "remote_stats")] + [("epoch", C.c_uint32), ("pad", C.c_int32)]
 
 
 class DispatchArgs(C.Structure):

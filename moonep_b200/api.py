@@ -297,6 +297,8 @@ class Buffer(OpsMixin):
         self._heap.view(st.rank, g.off_bar, (4 * 128,), torch.int32).zero_()
         st.scratch["grid_bar"].zero_()
         st.scratch["epoch"].zero_()
+        st.scratch["send_cnt"].zero_()
+        st.plan_epoch = 0
         st.status.zero_()
         torch.cuda.synchronize()
         if self.geo.R > 1:

@@ -57,6 +57,8 @@ class RankState:
     hidden_local: torch.Tensor = None     # [NvS, H] bf16 view of this rank's shard
     weights_local: torch.Tensor = None    # [NvS] fp32 view
     status: torch.Tensor = None           # int32[8] device
+    plan_epoch: int = 0                   # fresh plans launched so far (fast planner's barrier epoch)
+    plan_fast: bool = False
 
     @property
     def ctx_ptr(self) -> int:
@@ -80,7 +82,7 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     s["expert_off"] = torch.zeros(R * E, **i32)
     s["etc_all"] = torch.zeros(R * epn, **i32)
     s["stats_all"] = torch.zeros(R * 2, **i32)
-    s["send_cnt"] = torch.zeros(R, dtype=torch.int64, device=dev)
+    s["send_cnt"] = torch.zeros(2 * R, dtype=torch.int64, device=dev)     # two halves, see planning_fast_kernel
     st.status = torch.zeros(8, **i32)
 
     c = MepRankCtx()
@@ -106,6 +108,7 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     st.ctx_host = c
     raw = bytes(c)
     st.ctx_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
+    st.plan_fast = bool(_native.load().mep_planning_is_fast(E, R))
     st.hidden_local = heap.view(rank, geo.off_hidden, (geo.NvS, geo.H), torch.bfloat16)
     st.weights_local = heap.view(rank, geo.off_weights, (geo.NvS,), torch.float32)
     return st
@@ -164,10 +167,14 @@ def launch_planning(states, topk_list, tpe_list, plans, cu_list):
     args = (PlanArgs * n)()
     for i in range(n):
         p = plans[i]
+        st = states[i]
+        if st.plan_fast:
+            st.plan_epoch += 1
         args[i] = PlanArgs(ptr(topk_list[i]), ptr(tpe_list[i]), ptr(p.dst), ptr(cu_list[i]),
-                           ptr(p.experts_to_copy), ptr(p.zero_fill_ranges), ptr(p.remote_stats))
+                           ptr(p.experts_to_copy), ptr(p.zero_fill_ranges), ptr(p.remote_stats),
+                           st.plan_epoch if st.plan_fast else 0, 0)
     g = states[0].geo
-    _native.check(lib.mep_launch_planning(n, _pack(states), args, g.num_sms, g.E, _native.cur_stream()), "planning")
+    _native.check(lib.mep_launch_planning(n, _pack(states), args, g.num_sms, g.E, g.R, _native.cur_stream()), "planning")
 
 
 def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry_barrier: bool):
@@ -176,8 +183,9 @@ def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry
     args = (DispatchArgs * n)()
     for i in range(n):
         w = weights_list[i] if weights_list is not None else None
+        half = (states[i].plan_epoch & 1) if states[i].plan_fast else 0     # send_cnt half the planner used
         args[i] = DispatchArgs(ptr(hidden_list[i]), ptr(w), ptr(plans[i].dst), ptr(plans[i].zero_fill_ranges),
-                               1 if fresh else 0, 1 if entry_barrier else 0)
+                               (1 + half) if fresh else 0, 1 if entry_barrier else 0)
     g = states[0].geo
     _native.check(lib.mep_launch_dispatch(n, _pack(states), args, g.num_sms, g.H, g.epn, _native.cur_stream()), "dispatch")
 
