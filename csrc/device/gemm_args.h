@@ -1,0 +1,29 @@
+// Argument block of the grouped GEMM kernels (shared by the 1-CTA and the 2-CTA launchers).
+#pragma once
+#include <stdint.h>
+
+namespace mep {
+
+enum GemmMode { GEMM_GATE_UP = 0, GEMM_DOWN = 1, GEMM_DGRAD = 2, GEMM_DGRAD_GU = 3, GEMM_WGRAD = 4 };
+
+struct GemmArgs {
+  const int32_t* cu_seqlens;   // [G] padded end row of each group
+  int32_t G;
+  int32_t N;                   // output columns (GATE_UP: width of act = out dim of each weight)
+  int32_t K;                   // reduction length (DGRAD_GU: 2 * inner); unused for WGRAD
+  int32_t M_w;                 // WGRAD: rows of one weight matrix
+  int32_t b_group_rows;        // rows one group occupies in the flattened 2-D weight tensor(s)
+  int32_t accumulate;          // WGRAD: 1 -> out += acc, 0 -> out = acc
+  int32_t g_begin, g_end;      // only groups in [g_begin, g_end) are computed
+  int32_t zero_empty_below;    // WGRAD without accumulate: empty groups g < this get zeros
+  int32_t diag;                // diagnostics only (results invalid): 1 = MMA does not wait for operands and no
+                               // TMA loads are issued, 2 = epilogue discards the accumulators
+  void* out;                   // bf16 [rows, ldo]; WGRAD: fp32 [G, M_w, N]
+  void* out2;                  // GATE_UP: optional bf16 [rows, 2N] pre-activations (gate | up)
+  const float* row_scale;      // GATE_UP / DOWN: optional per-row factor [rows]
+  int64_t ldo;
+  int32_t* status;             // [4] error word: code, site, block, tile
+  uint64_t budget_ns;
+};
+
+}  // namespace mep

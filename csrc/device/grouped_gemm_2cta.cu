@@ -1,0 +1,264 @@
+// Weight-gradient grouped GEMM on CTA pairs: dW[g] (+)= X_g^T dY_g with tcgen05.mma.cta_group::2.
+//
+// Two CTAs of a cluster (two SMs) compute one 256 x 256 fp32 tile: each CTA stages ITS half of both
+// operands (128 weight rows of X^T and 128 of the 256 output columns of dY, 32 KB per 64-token
+// k-block) with ordinary single-CTA TMA loads from local memory, and the pair's tensor cores read
+// both halves. Per SM that is 32 KB of shared-memory fill per k-block instead of 48 KB for the same
+// amount of math, which is what limits the single-CTA kernel (operand feed, not the tensor pipe).
+// No cluster-wide copy is used: every load lands in the issuing CTA only and merely counts its bytes
+// on the leader CTA's mbarrier. The M tile is over weight rows, so it never straddles experts.
+// Roles per CTA: warp 0 = TMA producer, warp 1 = TMEM allocation (+ MMA issue in the leader CTA),
+// warps 2-9 = epilogue (each CTA drains its own 128 accumulator rows through shared memory + TMA
+// store / reduce-add).
+#include "tcgen05.cuh"
+#include "gemm_args.h"
+#include "../host/driver_api.h"
+#include "../host/launch.h"
+
+namespace mep {
+namespace w2 {
+
+constexpr int kBK = 64, kRing = 5, kEpiWarps = 8, kThreads = 64 + 32 * kEpiWarps;
+constexpr int kHalfBytes = 128 * kBK * 2;            // 16 KB: one operand half per CTA and k-block
+constexpr int kStageBytes = 2 * kHalfBytes;          // 32 KB
+constexpr int kAtomBytes = 64 * kBK * 2;
+constexpr int kSlabBytes = 32 * 128;
+constexpr int kMaxGroups = 192;
+constexpr size_t kSmem = (size_t)kRing * kStageBytes + (size_t)kEpiWarps * 2 * kSlabBytes + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+// cta_group::2 form: the destination is this CTA's shared memory, the mbarrier may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_bar(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               :: "r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(smem_result)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma2_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on ONE barrier (own or peer CTA, given as a cluster address) when the pair's MMAs are done
+__device__ __forceinline__ void mma2_commit(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar_cluster_addr) : "memory");
+}
+
+struct Tile { int g, row0, m0, n0, kblocks; };
+
+__global__ void __launch_bounds__(kThreads, 1)
+wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                  const __grid_constant__ CUtensorMap tma_out, GemmArgs args) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[kRing], empty_bar[kRing], tfull_bar[2], tempty_bar[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+  __shared__ int s_ntiles;
+  __shared__ int s_cu[kMaxGroups + 1], s_act[kMaxGroups];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cr = cluster_ctarank();
+  const bool leader = cr == 0;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int G = args.G;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kRing; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 2 * kEpiWarps); }
+    fence_mbar_init();
+    s_cu[0] = 0;
+    for (int g = 0; g < G; ++g) s_cu[g + 1] = args.cu_seqlens[g];
+    int n = 0;
+    for (int g = 0; g < G; ++g) {
+      const bool in = g >= args.g_begin && g < args.g_end;
+      if (in && (s_cu[g + 1] > s_cu[g] || (!args.accumulate && g < args.zero_empty_below))) s_act[n++] = g;
+    }
+    s_ntiles = n * (args.M_w / 256) * (args.N / 256);
+    tc::prefetch_tmap(&tma_a); tc::prefetch_tmap(&tma_b); tc::prefetch_tmap(&tma_out);
+  }
+  if (warp == 1) { tmem_alloc2(&s_tmem_base, 512); tmem_relinquish2(); }
+  tc::fence_before_sync();
+  __syncthreads();
+  cluster_sync();                       // both CTAs' barriers exist before anyone touches the peer's
+  tc::fence_after_sync();
+  const uint32_t tmem_base = s_tmem_base;
+  const int ntiles = s_ntiles;
+
+  auto fail = [&](int site, int tile) {
+    if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = 100 + site; args.status[2] = blockIdx.x; args.status[3] = tile; }
+    s_abort = 1;
+  };
+  auto get_tile = [&](int t, Tile& ti) {
+    const int mblk = args.M_w / 256, per = mblk * (args.N / 256);
+    const int ai = t / per, local = t - ai * per;
+    const int g = s_act[ai];
+    ti.g = g; ti.row0 = s_cu[g]; ti.kblocks = (s_cu[g + 1] - s_cu[g]) / kBK;
+    ti.m0 = (local % mblk) * 256; ti.n0 = (local / mblk) * 256;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer: this CTA's halves; bytes are counted on the LEADER's barrier
+    if (lane == 0) {
+      int it = 0; Tile ti;
+      for (int t = pair; t < ntiles && !s_abort; t += npairs) {
+        get_tile(t, ti);
+        for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
+          const int s = it % kRing; const uint32_t ph = (uint32_t)(it / kRing) & 1u;
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, args.budget_ns)) { fail(1, t); break; }
+          const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kHalfBytes;
+          const uint32_t bar = mapa(smem_u32(&full_bar[s]), 0);
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * kStageBytes);     // both CTAs' bytes
+          const int k = ti.row0 + kb * kBK;
+          const int am = ti.m0 + (int)cr * 128, bn = ti.n0 + (int)cr * 128;
+          tma_load_2d_bar(sa, &tma_a, am, k, bar);
+          tma_load_2d_bar(sa + kAtomBytes, &tma_a, am + 64, k, bar);
+          tma_load_2d_bar(sb, &tma_b, bn, k, bar);
+          tma_load_2d_bar(sb + kAtomBytes, &tma_b, bn + 64, k, bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only): one instruction drives both SMs
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = tc::instr_desc_bf16(256, 256, true, true);
+      uint32_t empty_peer[kRing], tfull_peer[2];
+      for (int i = 0; i < kRing; ++i) empty_peer[i] = mapa(smem_u32(&empty_bar[i]), 1);
+      for (int i = 0; i < 2; ++i) tfull_peer[i] = mapa(smem_u32(&tfull_bar[i]), 1);
+      int it = 0, tcnt = 0; Tile ti;
+      for (int t = pair; t < ntiles && !s_abort; t += npairs, ++tcnt) {
+        get_tile(t, ti);
+        if (ti.kblocks == 0) { --tcnt; continue; }
+        const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
+        if (!mbar_wait_bounded(&tempty_bar[acc], aph ^ 1u, args.budget_ns)) { fail(2, t); break; }
+        tc::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * 256;
+        bool ok = true;
+        for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
+          const int s = it % kRing; const uint32_t ph = (uint32_t)(it / kRing) & 1u;
+          if (!mbar_wait_bounded(&full_bar[s], ph, args.budget_ns)) { fail(3, t); ok = false; break; }
+          tc::fence_after_sync();
+          const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kHalfBytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            mma2_bf16(d_tmem, tc::smem_desc(sa + k * 2048, kAtomBytes, 1024), tc::smem_desc(sb + k * 2048, kAtomBytes, 1024),
+                      idesc, (kb | k) ? 1u : 0u);
+          mma2_commit(smem_u32(&empty_bar[s]));
+          mma2_commit(empty_peer[s]);
+        }
+        if (!ok) break;
+        mma2_commit(smem_u32(&tfull_bar[acc]));
+        mma2_commit(tfull_peer[acc]);
+      }
+    }
+  } else {
+    // ---------------- epilogue: this CTA's 128 rows of the 256-row tile
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    const uint32_t stg = smem_u32(smem + (size_t)kRing * kStageBytes) + (uint32_t)(warp - 2) * 2 * kSlabBytes;
+    const uint32_t tempty_leader[2] = {mapa(smem_u32(&tempty_bar[0]), 0), mapa(smem_u32(&tempty_bar[1]), 0)};
+    int tcnt = 0, chunk_no = 0; Tile ti;
+    for (int t = pair; t < ntiles && !s_abort; t += npairs, ++tcnt) {
+      get_tile(t, ti);
+      const int orow0 = ti.g * args.M_w + ti.m0 + (int)cr * 128 + q * 32;
+      if (ti.kblocks == 0) {           // empty group that must end with a zero gradient
+        float* orow = (float*)args.out + (size_t)(orow0 + lane) * args.N + ti.n0 + half * 128;
+        for (int j = 0; j < 32; ++j) reinterpret_cast<float4*>(orow)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        --tcnt; continue;
+      }
+      const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait_bounded(&tfull_bar[acc], aph, args.budget_ns) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) fail(4, t); break; }
+      tc::fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256;
+#pragma unroll 1
+      for (int c = half * 4; c < half * 4 + 4; ++c, ++chunk_no) {
+        const uint32_t buf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        uint32_t r[32];
+        tc::tmem_ld32(taddr + c * 32, r);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          tc::st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        tc::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (args.accumulate) tc::tma_reduce_add_2d(&tma_out, buf, ti.n0 + c * 32, orow0);
+          else tc::tma_store_2d(&tma_out, buf, ti.n0 + c * 32, orow0);
+          bulk_commit();
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) remote_arrive(tempty_leader[acc]);
+    }
+    if (lane == 0) bulk_wait_all<0>();
+  }
+
+  // ---------------- teardown: nobody leaves while the peer may still signal into this CTA
+  tc::fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  tc::fence_after_sync();
+  if (warp == 1) tmem_dealloc2(tmem_base, 512);
+}
+
+static int make_map2(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows, bool f32) {
+  const DriverApi* d = driver(); if (!d) return -1;
+  const int es_bytes = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * es_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t es[2] = {1, 1};
+  MEP_REQUIRE(((uintptr_t)base & 15) == 0 && (ld * es_bytes) % 16 == 0 && ld >= cols, "wgrad: tensor base/stride must be 16-byte aligned");
+  MEP_CU_CHECK(d->TensorMapEncodeTiled(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                                       dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return 0;
+}
+
+}  // namespace w2
+}  // namespace mep
+
+// dW[g] (+)= X_g^T dY_g on CTA pairs. x: [rows, M_w] bf16 (pitch x_ld), dy: [rows, N] bf16 (pitch dy_ld),
+// args.out: fp32 [G, M_w, N]. Requires M_w % 256 == 0, N % 256 == 0 and an even CTA count.
+extern "C" int mep_grouped_wgrad_2cta(const void* x, int64_t rows, int64_t x_ld, const void* dy, int64_t dy_ld,
+                                      const mep::GemmArgs* args_in, int num_ctas, cudaStream_t stream) {
+  using namespace mep;
+  GemmArgs args = *args_in;
+  MEP_REQUIRE(args.G >= 1 && args.G <= w2::kMaxGroups, "wgrad: G=%d out of range", args.G);
+  MEP_REQUIRE(args.M_w % 256 == 0 && args.N % 256 == 0, "wgrad (2-CTA): weight shape [%d,%d] must be multiples of 256", args.M_w, args.N);
+  num_ctas &= ~1;
+  MEP_REQUIRE(num_ctas >= 2, "wgrad (2-CTA): needs at least two CTAs");
+  CUtensorMap ma, mb, mo;
+  if (w2::make_map2(&ma, x, rows, args.M_w, x_ld, 64, 64, false)) return -1;
+  if (w2::make_map2(&mb, dy, rows, args.N, dy_ld, 64, 64, false)) return -1;
+  if (w2::make_map2(&mo, args.out, (int64_t)args.G * args.M_w, args.N, args.N, 32, 32, true)) return -1;
+  MEP_CUDA_CHECK(cudaFuncSetAttribute(w2::wgrad_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)w2::kSmem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_ctas); cfg.blockDim = dim3(w2::kThreads); cfg.dynamicSmemBytes = w2::kSmem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  MEP_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w2::wgrad_2cta_kernel, ma, mb, mo, args));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}

@@ -420,15 +420,21 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPa
     for (int e = tid; e < E; e += nt) s_cnt[e] = 0;
     __syncthreads();
     const int lim = v * VB;
-    for (int i0 = 0; i0 < lim; i0 += nt) {          // warp-aggregated: one shared-memory add per distinct expert and warp
-      const int i = i0 + tid;
-      const bool on = i < lim;
-      int e = on ? a.topk[i] : 0;
-      if (on && (unsigned)e >= (unsigned)E) { report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 1, i, (uint32_t)e, (uint32_t)E); e = 0; }
-      const unsigned act = __ballot_sync(0xffffffffu, on);
-      if (on) {
-        const unsigned m = __match_any_sync(act, e);
-        if ((threadIdx.x & 31) == __ffs(m) - 1) atomicAdd(&s_cnt[e], __popc(m));
+    for (int i0 = 0; i0 < lim; i0 += 8 * nt) {      // eight independent loads per thread, then warp-aggregated adds
+      int ev[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { const int i = i0 + u * nt + tid; ev[u] = i < lim ? __ldg(a.topk + i) : -1; }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * nt + tid;
+        const bool on = i < lim;
+        int e = on ? ev[u] : 0;
+        if (on && (unsigned)e >= (unsigned)E) { report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 1, i, (uint32_t)e, (uint32_t)E); e = 0; }
+        const unsigned act = __ballot_sync(0xffffffffu, on);
+        if (on) {
+          const unsigned m = __match_any_sync(act, e);
+          if ((threadIdx.x & 31) == __ffs(m) - 1) atomicAdd(&s_cnt[e], __popc(m));
+        }
       }
     }
     __syncthreads();

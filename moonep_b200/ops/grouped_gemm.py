@@ -29,15 +29,20 @@ class GemmArgs(C.Structure):
                 ("status", C.c_void_p), ("budget_ns", C.c_uint64)]
 
 
+def _dev_index(device) -> int:
+    idx = torch.device(device).index
+    return torch.cuda.current_device() if idx is None else idx
+
+
 def _status(device) -> torch.Tensor:
-    key = torch.device(device).index
+    key = _dev_index(device)
     if key not in _status_cache:
-        _status_cache[key] = torch.zeros(4, dtype=torch.int32, device=device)
+        _status_cache[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
     return _status_cache[key]
 
 
 def _num_sms(device) -> int:
-    key = torch.device(device).index
+    key = _dev_index(device)
     if key not in _sm_cache:
         _sm_cache[key] = torch.cuda.get_device_properties(device).multi_processor_count
     return _sm_cache[key]
@@ -45,8 +50,10 @@ def _num_sms(device) -> int:
 
 def check_status(device="cuda") -> None:
     """Synchronise and raise if a GEMM pipeline wait expired."""
-    v = _status(torch.device(device) if not isinstance(device, torch.device) else device).cpu().tolist()
+    st = _status(device)
+    v = st.cpu().tolist()
     if v[0] != 0:
+        st.zero_()
         raise RuntimeError(f"grouped GEMM aborted: code {v[0]} at site {v[1]}, CTA {v[2]}, tile {v[3]}")
 
 
@@ -130,6 +137,24 @@ def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num
     assert out.dtype == torch.float32 and out.is_contiguous()
     assert x.shape[1] == M and dy.shape[1] == N and M % 128 == 0 and N % 256 == 0
     assert dy.stride(1) == 1 and x.stride(1) == 1
+    if M % 256 == 0 and os.environ.get("MOONEP_WGRAD_2CTA", "1") != "0":
+        # CTA-pair kernel (tcgen05 cta_group::2): a third less operand traffic per SM
+        lib = _native.load()
+        G0, G1 = (0, G) if groups is None else groups
+        args = GemmArgs()
+        args.cu_seqlens = cu.data_ptr()
+        args.G, args.N, args.K, args.M_w = G, N, 0, M
+        args.accumulate, args.g_begin, args.g_end = (1 if accumulate else 0), G0, G1
+        args.zero_empty_below = zero_empty_below
+        args.out = out.data_ptr()
+        args.status = _status(x.device).data_ptr()
+        from ..engine import wait_budget_ns
+        args.budget_ns = wait_budget_ns()
+        rc = lib.mep_grouped_wgrad_2cta(C.c_void_p(x.data_ptr()), C.c_int64(x.shape[0]), C.c_int64(x.stride(0)),
+                                        C.c_void_p(dy.data_ptr()), C.c_int64(dy.stride(0)), C.byref(args),
+                                        num_ctas or _num_sms(x.device), _native.cur_stream())
+        _native.check(rc, "grouped_wgrad_2cta")
+        return
     _launch(WGRAD, x, dy, None, cu, N=N, M_w=M, out=out, accumulate=accumulate, zero_empty_below=zero_empty_below,
             b_rows=dy.shape[0], b_cols=N, b_ld=dy.stride(0), groups=groups, num_ctas=num_ctas)
 
