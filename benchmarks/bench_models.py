@@ -46,12 +46,13 @@ def main():
     def step():
         x = x0.detach().requires_grad_(True)
         h = x
-        for b in blocks:
-            h = h + b.forward(h)          # residual stream between the blocks
+        for b in blocks:            # pre-norm residual stream between the blocks
+            hn = (h.float() * torch.rsqrt(h.float().pow(2).mean(dim=-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+            h = h + b.forward(hn)
         loss = (h.float() ** 2).mean()
         loss.backward()
         for b in blocks:
-            b.sgd_step(1e-3)
+            b.sgd_step(1e-5)
         return loss.detach()
 
     for mv in sweep:

@@ -28,6 +28,11 @@ class ClockSampler:
         self._proc = subprocess.Popen([exe, f"--query-gpu={QUERY}", "--format=csv,noheader,nounits",
                                        "-i", str(self.device_index), "-lms", str(self.period_ms)],
                                       stdout=open(self._path, "w"), stderr=subprocess.DEVNULL)
+        # nvidia-smi can take seconds to come up on a multi-GPU box: wait for its first sample
+        import time
+        t0 = time.time()
+        while time.time() - t0 < 20.0 and os.path.getsize(self._path) == 0 and self._proc.poll() is None:
+            time.sleep(0.05)
         return self
 
     def stop(self) -> dict:
