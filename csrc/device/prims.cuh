@@ -3,8 +3,9 @@
 //
 // Behavioural counterpart of the reference's moonep/_common.py (grid_sync :249-271,
 // cross_rank_barrier :274-346, bulk copies :414-459) with two deliberate differences:
-//  * every wait is bounded by a wall-clock budget (%globaltimer); on expiry the waiter
-//    records the site in MepStatus and the kernel returns -- it never traps;
+//  * every wait is bounded by a time budget (nanoseconds, converted to SM cycles and measured
+//    with clock64); on expiry the waiter records the site in MepStatus and the kernel returns
+//    -- it never traps;
 //  * cross-rank flags are monotone epochs (one slot per peer) instead of +/-1 counters,
 //    so a barrier needs no reset and a late or repeated arrival cannot corrupt it.
 #pragma once

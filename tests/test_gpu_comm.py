@@ -250,3 +250,31 @@ def test_planner_large_expert_count(cuda_device):
         assert torch.equal(plans[r].dst.cpu().long(), torch.from_numpy(cp.dst[r]))
         assert torch.equal(cus[r].cpu().long(), torch.from_numpy(cp.cu_seqlens[r]))
         assert torch.equal(plans[r].experts_to_copy.cpu().long(), torch.from_numpy(cp.experts_to_copy))
+
+
+def test_trace_stats_and_reset(cuda_device, monkeypatch):
+    """Device timestamp ring, plan statistics and the collective reset of barrier state."""
+    from moonep_b200 import Buffer, engine
+    monkeypatch.setenv("MOONEP_TRACE", "1")
+    S, H, K, E = 64, 128, 4, 8
+    buf = Buffer(S, H, K, E, 1, num_sms=2, token_padding=16)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    hidden = torch.randn(S, H, dtype=torch.bfloat16, device="cuda", generator=g)
+    w = torch.rand(S, K, device="cuda", generator=g)
+    topk = torch.randint(0, E, (S, K), dtype=torch.int32, device="cuda", generator=g)
+    tpe = torch.bincount(topk.flatten(), minlength=E).to(torch.int32)
+    h, wn, cu, plan = buf.dispatch(hidden, w, topk, tpe)
+    buf.combine(plan=plan, hidden_nvsh=h)
+    tr = engine.read_trace(buf._states[0])
+    kernels = {k for _, k, _, _, _ in tr}
+    assert 3 in kernels and 6 in kernels, "dispatch and combine must have left timestamps"
+    assert all(a[0] <= b[0] for a, b in zip(tr, tr[1:]))
+    st = buf.stats(plan)
+    assert st["experts_received"] == 0 and st["dup_rows"] == int(plan.dup_counts[1]) and 0 <= st["dedup_ratio"] < 1
+    buf.reset()
+    h2, _, cu2, plan2 = buf.dispatch(hidden, w, topk, tpe)
+    torch.cuda.synchronize()
+    n = int(cu[-1])
+    assert torch.equal(h2[:n], h[:n]) and torch.equal(cu2, cu) and torch.equal(plan2.dst, plan.dst)
+    buf.check()
+    buf.destroy()
