@@ -214,10 +214,24 @@ def run(args):
     e1.record()
     sync()
     ms = mx(e0.elapsed_time(e1) / args.steps)
+    copy_stream = torch.cuda.Stream()
+
+    def fetch(i):
+        with torch.cuda.stream(copy_stream):
+            x = host[i % 2].to("cuda", non_blocking=True)
+            ev = copy_stream.record_event()
+        return x, ev
+
     sync()
     t0 = time.perf_counter()
+    nxt = fetch(0)
     for i in range(args.steps):
-        lv = step(host[i % 2].to("cuda", non_blocking=True)).item()
+        x, ev = nxt
+        if i + 1 < args.steps:
+            nxt = fetch(i + 1)
+        torch.cuda.current_stream().wait_event(ev)
+        x.record_stream(torch.cuda.current_stream())
+        lv = step(x).item()
     sync()
     e2e_ms = mx((time.perf_counter() - t0) * 1e3 / args.steps)
     sweep = []
