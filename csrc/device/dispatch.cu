@@ -253,6 +253,71 @@ __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPa
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// dup_expand_fresh: the two steps above in one launch for a fresh dispatch. Every CTA derives the
+// per-source prefixes itself, all CTAs share the compaction into the plan-owned tables, and the
+// expansion reads the groups straight from the staging regions.
+struct DupFreshArgs { __nv_bfloat16* buf; int32_t* dup_groups; int32_t* dup_loffs; int32_t* dup_counts; };
+struct DupFreshArgsPack { DupFreshArgs a[MEP_MAX_VRANKS]; };
+
+__global__ void __launch_bounds__(256) dup_expand_fresh_kernel(MepCtxPack P, DupFreshArgsPack A) {
+  const MepRankCtx c = *P.ctx[blockIdx.y];
+  const DupFreshArgs& a = A.a[blockIdx.y];
+  __shared__ int s_goff[MEP_MAX_RANKS + 1], s_loff[MEP_MAX_RANKS + 1];
+  const int* cnt = (const int*)peer_ptr(c, c.rank, c.off_dupcnt);
+  if (threadIdx.x == 0) {
+    int g = 0, l = 0;
+    for (int r = 0; r < c.R; ++r) { s_goff[r] = g; s_loff[r] = l; g += __ldcg(cnt + 2 * r); l += __ldcg(cnt + 2 * r + 1); }
+    s_goff[c.R] = g; s_loff[c.R] = l;
+    if (blockIdx.x == 0) { a.dup_counts[0] = g; a.dup_counts[1] = l; }
+  }
+  __syncthreads();
+  const int* sg = (const int*)peer_ptr(c, c.rank, c.off_dupgroups);
+  const int* sl = (const int*)peer_ptr(c, c.rank, c.off_duploffs);
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gnt = gridDim.x * blockDim.x;
+  for (int r = 0; r < c.R; ++r) {
+    const int ng = s_goff[r + 1] - s_goff[r], nl = s_loff[r + 1] - s_loff[r];
+    for (int j = gtid; j < ng; j += gnt) {
+      const int* src = sg + ((size_t)r * c.dup_group_cap + j) * 3;
+      int* dstp = a.dup_groups + (size_t)(s_goff[r] + j) * 3;
+      dstp[0] = __ldcg(src); dstp[1] = __ldcg(src + 1) + s_loff[r]; dstp[2] = __ldcg(src + 2);
+    }
+    for (int j = gtid; j < nl; j += gnt)
+      a.dup_loffs[s_loff[r] + j] = __ldcg(sl + (size_t)r * c.dup_loff_cap + j);
+  }
+  // expansion, one warp per group, groups addressed through the staging regions
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
+  const int total = s_goff[c.R];
+  const size_t row_bytes = (size_t)c.H * 2;
+  const int nvec = (int)(row_bytes >> 4);
+  char* base = (char*)a.buf;
+  for (int g = gw; g < total; g += nw) {
+    int lo = 0, hi = c.R - 1;                         // source r with s_goff[r] <= g < s_goff[r+1]
+    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (s_goff[mid] <= g) lo = mid; else hi = mid - 1; }
+    const int r = lo, j = g - s_goff[r];
+    const int* grp = sg + ((size_t)r * c.dup_group_cap + j) * 3;
+    const int p = __ldcg(grp), st = __ldcg(grp + 1), n = __ldcg(grp + 2);
+    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
+    const char* src = base + (size_t)p * row_bytes;
+    int myq = -1;
+    if (lane < n) { myq = __ldcg(sl + (size_t)r * c.dup_loff_cap + st + lane); if ((unsigned)myq >= (unsigned)c.NvS) myq = -1; }
+    for (int v0 = 0; v0 < nvec; v0 += 128) {
+      int4 x[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) { const int v = v0 + jj * 32 + lane; if (v < nvec) x[jj] = ld_nc_v4(src + (size_t)v * 16); }
+      for (int d = 0; d < n; ++d) {
+        const int q = __shfl_sync(0xffffffffu, myq, d);
+        if (q < 0) continue;
+        char* drow = base + (size_t)q * row_bytes;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) { const int v = v0 + jj * 32 + lane; if (v < nvec) st_na_v4(drow + (size_t)v * 16, x[jj]); }
+      }
+    }
+  }
+}
+
 }  // namespace mep
 
 extern "C" int mep_dispatch_smem_stages(int H, int* stages_out, size_t* smem_out) {
@@ -291,4 +356,11 @@ extern "C" int mep_launch_dup_expand(int nv, const MepRankCtx* const* ctxs, cons
   MepCtxPack P = {}; mep::DupArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
   return mep::launch_plain(mep::dup_expand_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A);
+}
+
+extern "C" int mep_launch_dup_expand_fresh(int nv, const MepRankCtx* const* ctxs, const mep::DupFreshArgs* args,
+                                           int num_blocks, cudaStream_t stream) {
+  MepCtxPack P = {}; mep::DupFreshArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  return mep::launch_plain(mep::dup_expand_fresh_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A);
 }

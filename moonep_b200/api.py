@@ -126,8 +126,9 @@ class OpsMixin:
         engine.launch_dispatch(st, hidden, weights, plans, fresh=fresh,
                                entry_barrier=(not fresh) and inter_rank_sync)
         if fresh:
-            engine.launch_dup_finalize(st, plans)
-        engine.launch_dup_expand(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4)
+            engine.launch_dup_expand_fresh(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4)
+        else:
+            engine.launch_dup_expand(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4)
         out_h, out_w = [], []
         for i in range(n):
             if zero_copy:

@@ -199,6 +199,13 @@ def launch_dup_finalize(states, plans):
     _native.check(lib.mep_launch_dup_finalize(n, _pack(states), args, _native.cur_stream()), "dup_finalize")
 
 
+def launch_dup_expand_fresh(states, bufs, plans, num_blocks: int):
+    """Fresh dispatch: compact the staged duplicate groups into the plan and expand them, one launch."""
+    lib = _native.load()
+    _native.check(lib.mep_launch_dup_expand_fresh(len(states), _pack(states), _dup_args(states, bufs, plans),
+                                                  num_blocks, _native.cur_stream()), "dup_expand_fresh")
+
+
 def _dup_args(states, bufs, plans):
     n = len(states)
     args = (DupArgs * n)()
