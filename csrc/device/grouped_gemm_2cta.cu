@@ -186,17 +186,27 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       if (!ok) { if (lane == 0) fail(4, t); break; }
       tc::fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256;
-#pragma unroll 1
-      for (int c = half * 4; c < half * 4 + 4; ++c, ++chunk_no) {
+      // software pipeline over the four 32-column chunks of this warp: the TMEM load of chunk i+1 is
+      // in flight while chunk i goes through shared memory; the accumulator is handed back to the
+      // MMA warp as soon as the last chunk sits in registers
+      uint32_t r[2][32];
+      tc::tmem_ld32(taddr + (half * 4) * 32, r[0]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i, ++chunk_no) {
+        const int c = half * 4 + i;
+        tc::tmem_ld_wait();
+        if (i + 1 < 4) tc::tmem_ld32(taddr + (c + 1) * 32, r[(i + 1) & 1]);
+        else {
+          tc::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) remote_arrive(tempty_leader[acc]);
+        }
         const uint32_t buf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;
         if (lane == 0) bulk_wait_read<1>();
         __syncwarp();
-        uint32_t r[32];
-        tc::tmem_ld32(taddr + c * 32, r);
-        tc::tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          tc::st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          tc::st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), r[i & 1][4 * j], r[i & 1][4 * j + 1], r[i & 1][4 * j + 2], r[i & 1][4 * j + 3]);
         tc::fence_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -205,9 +215,6 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
           bulk_commit();
         }
       }
-      tc::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) remote_arrive(tempty_leader[acc]);
     }
     if (lane == 0) bulk_wait_all<0>();
   }

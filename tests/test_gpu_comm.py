@@ -278,3 +278,62 @@ def test_trace_stats_and_reset(cuda_device, monkeypatch):
     assert torch.equal(h2[:n], h[:n]) and torch.equal(cu2, cu) and torch.equal(plan2.dst, plan.dst)
     buf.check()
     buf.destroy()
+
+
+def test_bad_inputs_raise(cuda_device):
+    """Argument validation of the public API (messages a user can act on)."""
+    from moonep_b200 import Buffer
+    S, H, K, E = 32, 64, 2, 4
+    buf = Buffer(S, H, K, E, 1, num_sms=1, token_padding=8)
+    hidden = torch.zeros(S, H, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(S, K, device="cuda")
+    topk = torch.zeros(S, K, dtype=torch.int32, device="cuda")
+    tpe = torch.tensor([S * K, 0, 0, 0], dtype=torch.int32, device="cuda")
+    with pytest.raises(AssertionError, match="topk_experts_sk and tokens_per_expert"):
+        buf.dispatch(hidden, w)
+    with pytest.raises(AssertionError, match="bf16"):
+        buf.dispatch(hidden.float(), w, topk, tpe)
+    with pytest.raises(AssertionError, match="int32"):
+        buf.dispatch(hidden, w, topk.long(), tpe)
+    with pytest.raises(AssertionError, match=r"\[E\] int32"):
+        buf.dispatch(hidden, w, topk, tpe[:3])
+    h, wn, cu, plan = buf.dispatch(hidden, w, topk, tpe)
+    with pytest.raises(AssertionError, match="plan is required"):
+        buf.combine(hidden_nvsh=h)
+    with pytest.raises(AssertionError, match="NvS"):
+        buf.combine(plan=plan, hidden_nvsh=h[:-1].contiguous())
+    with pytest.raises(AssertionError, match="provided together"):
+        buf.prefetch_weight(plan=plan, local_gate_weight=torch.zeros(4, 8, 8, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(AssertionError, match="provided together"):
+        buf.reduce_grad(plan=plan, local_gate_grad=torch.zeros(4, 8, 8, device="cuda"))
+    other = Buffer(S, H, K + 1, E, 1, num_sms=1, token_padding=8)
+    with pytest.raises(AssertionError, match="another Buffer geometry"):
+        other.dispatch(hidden, plan=plan)
+    other.destroy()
+    buf.destroy()
+    with pytest.raises(AssertionError, match="destroyed"):
+        buf.dispatch(hidden, w, topk, tpe)
+
+
+def test_prefetch_and_reduce_beyond_2gib_offsets(cuda_device):
+    """Expert payloads whose byte offsets inside a rank's pool exceed 2^31 (64-bit addressing)."""
+    R, epn, S, K, H = 2, 3, 120, 4, 64
+    cl, cp, plans, *_ = run_case(S, K, epn, H, R, 4, 8, "all_remote", with_weights=False)
+    # force redundancy-free plan to still exercise slots: build a plan table by hand
+    etc = torch.full((R, epn), -1, dtype=torch.int32)
+    etc[0, 2] = 1 * epn + 2        # rank 0 slot 2 <- rank 1's last expert (offset > 2^31 in both pools)
+    etc[1, 1] = 0 * epn + 2        # rank 1 slot 1 <- rank 0's last expert
+    fake = [type(p)(**{**{f: getattr(p, f) for f in ("dst", "zero_fill_ranges", "remote_stats", "N", "R", "E", "NvS", "K",
+                                                        "dup_groups", "dup_loffs", "dup_counts")},
+                       "experts_to_copy": etc.to(cuda_device)}) for p in plans]
+    rows, cols = 16384, 36864     # 16384*36864*2 B = 1.125 GiB per expert: expert 2 starts at 2.25 GiB
+    local = [torch.empty(epn, rows, cols, dtype=torch.bfloat16, device=cuda_device) for _ in range(R)]
+    for r in range(R):
+        local[r][2].view(torch.int16).copy_(torch.arange(rows * cols, device=cuda_device, dtype=torch.int32).view(rows, cols).to(torch.int16) + r)
+    pool, flat = cl.make_pool((epn, rows, cols), torch.bfloat16)
+    cl.prefetch(fake, [[(local[r], pool)] for r in range(R)])
+    torch.cuda.synchronize()
+    cl.check()
+    assert torch.equal(pool[0, 2].view(torch.int16), local[1][2].view(torch.int16))
+    assert torch.equal(pool[1, 1].view(torch.int16), local[0][2].view(torch.int16))
+    assert not pool[0, 0].any() and not pool[1, 2].any()
