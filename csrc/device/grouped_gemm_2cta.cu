@@ -242,6 +242,248 @@ static int make_map2(CUtensorMap* m, const void* base, int64_t rows, int64_t col
 }
 
 }  // namespace w2
+
+// =============================================================================================
+// Token-major GEMMs (GATE_UP, DOWN, DGRAD, DGRAD_GU) on CTA pairs: a pair computes a 256-token x 256
+// output tile; CTA r stages token rows [r*128, r*128+128) of the tile and its half of the weight
+// tile (GATE_UP: CTA 0 the gate columns, CTA 1 the up columns). Expert groups are multiples of 128
+// rows, so a group with an odd number of 128-row blocks ends with a pair tile whose second half
+// belongs to the next group: that half is computed (against the wrong expert) and thrown away.
+namespace t2 {
+
+using namespace w2;
+constexpr int kTokRing = 6, kTokEpi = 4, kTokThreads = 64 + 32 * kTokEpi;
+constexpr size_t kTokSmem = (size_t)kTokRing * kStageBytes + (size_t)kTokEpi * 2 * kSlabBytes + 1024;
+
+__device__ __forceinline__ void tma_load_3d_bar(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               :: "r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+struct TTile { int g, row0, valid1, n0; };
+
+template <int MODE>
+__global__ void __launch_bounds__(kTokThreads, 1)
+tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b0,
+                const __grid_constant__ CUtensorMap tma_b1, const __grid_constant__ CUtensorMap tma_out, GemmArgs args) {
+  constexpr bool B_MN = MODE == GEMM_GATE_UP || MODE == GEMM_DOWN;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[kTokRing], empty_bar[kTokRing], tfull_bar[2], tempty_bar[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+  __shared__ int s_ntiles;
+  __shared__ int s_cu[kMaxGroups + 1], s_start[kMaxGroups + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cr = cluster_ctarank();
+  const bool leader = cr == 0;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int G = args.G;
+  const int nblk = MODE == GEMM_GATE_UP ? args.N / 128 : args.N / 256;
+  const int kblocks = args.K / kBK;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kTokRing; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 2 * kTokEpi); }
+    fence_mbar_init();
+    s_cu[0] = 0;
+    for (int g = 0; g < G; ++g) s_cu[g + 1] = args.cu_seqlens[g];
+    int run = 0;
+    for (int g = 0; g < G; ++g) {
+      s_start[g] = run;
+      if (g >= args.g_begin && g < args.g_end) run += (((s_cu[g + 1] - s_cu[g]) / 128 + 1) / 2) * nblk;
+    }
+    s_start[G] = run; s_ntiles = run;
+    tc::prefetch_tmap(&tma_a); tc::prefetch_tmap(&tma_b0); tc::prefetch_tmap(&tma_b1); tc::prefetch_tmap(&tma_out);
+  }
+  if (warp == 1) { tmem_alloc2(&s_tmem_base, 512); tmem_relinquish2(); }
+  tc::fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = s_tmem_base;
+  const int ntiles = s_ntiles;
+
+  auto fail = [&](int site, int tile) {
+    if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = 200 + site; args.status[2] = blockIdx.x; args.status[3] = tile; }
+    s_abort = 1;
+  };
+  auto get_tile = [&](int t, int& gcur, TTile& ti) {
+    while (gcur + 1 <= G && s_start[gcur + 1] <= t) ++gcur;
+    const int g = gcur, beg = s_cu[g];
+    const int mblk = (s_cu[g + 1] - beg) / 128, pairs = (mblk + 1) / 2;
+    const int local = t - s_start[g];
+    const int pt = local % pairs;
+    ti.g = g; ti.row0 = beg + pt * 256; ti.valid1 = (2 * pt + 1 < mblk) ? 1 : 0;
+    ti.n0 = (local / pairs) * (MODE == GEMM_GATE_UP ? 128 : 256);
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0, gcur = 0; TTile ti;
+      for (int t = pair; t < ntiles && !s_abort; t += npairs) {
+        get_tile(t, gcur, ti);
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % kTokRing; const uint32_t ph = (uint32_t)(it / kTokRing) & 1u;
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, args.budget_ns)) { fail(1, t); break; }
+          const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kHalfBytes;
+          const uint32_t bar = mapa(smem_u32(&full_bar[s]), 0);
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * kStageBytes);
+          const int k0 = kb * kBK;
+          tma_load_2d_bar(sa, &tma_a, k0, ti.row0 + (int)cr * 128, bar);
+          if (MODE == GEMM_GATE_UP) {
+            tma_load_3d_bar(sb, cr == 0 ? &tma_b0 : &tma_b1, 0, ti.g * args.b_group_rows + k0, ti.n0 / 64, bar);
+          } else if (MODE == GEMM_DOWN) {
+            tma_load_3d_bar(sb, &tma_b0, 0, ti.g * args.b_group_rows + k0, (ti.n0 + (int)cr * 128) / 64, bar);
+          } else if (MODE == GEMM_DGRAD) {
+            tma_load_2d_bar(sb, &tma_b0, k0, ti.g * args.b_group_rows + ti.n0 + (int)cr * 128, bar);
+          } else {
+            const int half = args.K / 2;
+            if (k0 < half) tma_load_2d_bar(sb, &tma_b0, k0, ti.g * args.b_group_rows + ti.n0 + (int)cr * 128, bar);
+            else tma_load_2d_bar(sb, &tma_b1, k0 - half, ti.g * args.b_group_rows + ti.n0 + (int)cr * 128, bar);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = tc::instr_desc_bf16(256, 256, false, B_MN);
+      uint32_t empty_peer[kTokRing], tfull_peer[2];
+      for (int i = 0; i < kTokRing; ++i) empty_peer[i] = mapa(smem_u32(&empty_bar[i]), 1);
+      for (int i = 0; i < 2; ++i) tfull_peer[i] = mapa(smem_u32(&tfull_bar[i]), 1);
+      int it = 0, tcnt = 0;
+      for (int t = pair; t < ntiles && !s_abort; t += npairs, ++tcnt) {
+        const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
+        if (!mbar_wait_bounded(&tempty_bar[acc], aph ^ 1u, args.budget_ns)) { fail(2, t); break; }
+        tc::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * 256;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % kTokRing; const uint32_t ph = (uint32_t)(it / kTokRing) & 1u;
+          if (!mbar_wait_bounded(&full_bar[s], ph, args.budget_ns)) { fail(3, t); ok = false; break; }
+          tc::fence_after_sync();
+          const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kHalfBytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t ad = tc::smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? tc::smem_desc(sb + k * 2048, kAtomBytes, 1024) : tc::smem_desc(sb + k * 32, 16, 1024);
+            mma2_bf16(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          mma2_commit(smem_u32(&empty_bar[s]));
+          mma2_commit(empty_peer[s]);
+        }
+        if (!ok) break;
+        mma2_commit(smem_u32(&tfull_bar[acc]));
+        mma2_commit(tfull_peer[acc]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r_in_half = q * 32 + lane;
+    const uint32_t stg = smem_u32(smem + (size_t)kTokRing * kStageBytes) + (uint32_t)(warp - 2) * 2 * kSlabBytes;
+    const uint32_t tempty_leader[2] = {mapa(smem_u32(&tempty_bar[0]), 0), mapa(smem_u32(&tempty_bar[1]), 0)};
+    int tcnt = 0, gcur = 0, chunk_no = 0; TTile ti;
+    for (int t = pair; t < ntiles && !s_abort; t += npairs, ++tcnt) {
+      get_tile(t, gcur, ti);
+      const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait_bounded(&tfull_bar[acc], aph, args.budget_ns) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) fail(4, t); break; }
+      tc::fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256;
+      const bool live = cr == 0 || ti.valid1;            // second half of an odd group: discard
+      const int hrow0 = ti.row0 + (int)cr * 128;
+      if (!live) {
+        // nothing to write; the accumulator is handed back below
+      } else if (MODE == GEMM_GATE_UP) {
+        const size_t row = (size_t)hrow0 + r_in_half;
+        __nv_bfloat16* orow = (__nv_bfloat16*)args.out + row * args.ldo + ti.n0;
+        __nv_bfloat16* grow = args.out2 ? (__nv_bfloat16*)args.out2 + row * (size_t)(2 * args.N) + ti.n0 : nullptr;
+        const float sc = args.row_scale ? args.row_scale[row] : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t gr[32], ur[32];
+          tc::tmem_ld32(taddr + c * 32, gr);
+          tc::tmem_ld32(taddr + 128 + c * 32, ur);
+          tc::tmem_ld_wait();
+          uint32_t o[16], og[16], ou[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g0 = __uint_as_float(gr[2 * j]), g1 = __uint_as_float(gr[2 * j + 1]);
+            const float u0 = __uint_as_float(ur[2 * j]), u1 = __uint_as_float(ur[2 * j + 1]);
+            const float a0 = g0 / (1.f + __expf(-g0)) * u0 * sc, a1 = g1 / (1.f + __expf(-g1)) * u1 * sc;
+            __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1); o[j] = *reinterpret_cast<uint32_t*>(&h);
+            __nv_bfloat162 hg = __floats2bfloat162_rn(g0, g1); og[j] = *reinterpret_cast<uint32_t*>(&hg);
+            __nv_bfloat162 hu = __floats2bfloat162_rn(u0, u1); ou[j] = *reinterpret_cast<uint32_t*>(&hu);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            st_v4(orow + c * 32 + j * 8, make_int4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+            if (grow) {
+              st_v4(grow + c * 32 + j * 8, make_int4(og[4 * j], og[4 * j + 1], og[4 * j + 2], og[4 * j + 3]));
+              st_v4(grow + args.N + c * 32 + j * 8, make_int4(ou[4 * j], ou[4 * j + 1], ou[4 * j + 2], ou[4 * j + 3]));
+            }
+          }
+        }
+      } else {
+        const size_t row = (size_t)hrow0 + r_in_half;
+        const float sc = (MODE == GEMM_DOWN && args.row_scale) ? args.row_scale[row] : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c, ++chunk_no) {
+          const uint32_t buf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;
+          if (lane == 0) bulk_wait_read<1>();
+          __syncwarp();
+          uint32_t r[64];
+          tc::tmem_ld32(taddr + c * 64, r);
+          tc::tmem_ld32(taddr + c * 64 + 32, r + 32);
+          tc::tmem_ld_wait();
+          uint32_t o[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * sc, __uint_as_float(r[2 * j + 1]) * sc);
+            o[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            tc::st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          tc::fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tc::tma_store_2d(&tma_out, buf, ti.n0 + c * 64, hrow0 + q * 32);
+            bulk_commit();
+          }
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) remote_arrive(tempty_leader[acc]);
+    }
+    if (lane == 0) bulk_wait_all<0>();
+  }
+
+  tc::fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  tc::fence_after_sync();
+  if (warp == 1) tmem_dealloc2(tmem_base, 512);
+}
+
+static int make_map_mn3(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int atoms) {
+  const DriverApi* d = driver(); if (!d) return -1;
+  MEP_REQUIRE(cols % 64 == 0, "gemm: MN-major operand width %lld must be a multiple of 64", (long long)cols);
+  cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
+  cuuint32_t box[3] = {64, 64, (cuuint32_t)atoms};
+  cuuint32_t es[3] = {1, 1, 1};
+  MEP_CU_CHECK(d->TensorMapEncodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return 0;
+}
+
+}  // namespace t2
 }  // namespace mep
 
 // dW[g] (+)= X_g^T dY_g on CTA pairs. x: [rows, M_w] bf16 (pitch x_ld), dy: [rows, N] bf16 (pitch dy_ld),
@@ -266,6 +508,46 @@ extern "C" int mep_grouped_wgrad_2cta(const void* x, int64_t rows, int64_t x_ld,
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
   MEP_CUDA_CHECK(cudaLaunchKernelEx(&cfg, w2::wgrad_2cta_kernel, ma, mb, mo, args));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+// Token-major grouped GEMMs on CTA pairs; same contract as mep_grouped_gemm for modes 0-3.
+extern "C" int mep_grouped_gemm_2cta(int mode, const void* a, int64_t a_rows, int64_t a_cols, int64_t a_ld,
+                                     const void* b0, const void* b1, int64_t b_rows, int64_t b_cols, int64_t b_ld,
+                                     const mep::GemmArgs* args_in, int num_ctas, cudaStream_t stream) {
+  using namespace mep;
+  GemmArgs args = *args_in;
+  MEP_REQUIRE(mode >= GEMM_GATE_UP && mode <= GEMM_DGRAD_GU, "gemm (2-CTA): mode %d not supported", mode);
+  MEP_REQUIRE(args.G >= 1 && args.G <= w2::kMaxGroups, "gemm: G=%d out of range", args.G);
+  MEP_REQUIRE(args.K % 64 == 0 && args.N % (mode == GEMM_GATE_UP ? 128 : 256) == 0, "gemm (2-CTA): K=%d N=%d not tileable", args.K, args.N);
+  num_ctas &= ~1;
+  MEP_REQUIRE(num_ctas >= 2, "gemm (2-CTA): needs at least two CTAs");
+  const bool b_mn = mode == GEMM_GATE_UP || mode == GEMM_DOWN;
+  CUtensorMap ma, mb0, mb1, mo;
+  if (w2::make_map2(&ma, a, a_rows, a_cols, a_ld, 64, 128, false)) return -1;
+  if (b_mn) { if (t2::make_map_mn3(&mb0, b0, b_rows, b_cols, b_ld, 2)) return -1; }
+  else      { if (w2::make_map2(&mb0, b0, b_rows, b_cols, b_ld, 64, 128, false)) return -1; }
+  if (b1) { if (b_mn ? t2::make_map_mn3(&mb1, b1, b_rows, b_cols, b_ld, 2) : w2::make_map2(&mb1, b1, b_rows, b_cols, b_ld, 64, 128, false)) return -1; }
+  else mb1 = mb0;
+  if (mode == GEMM_GATE_UP) mo = ma;
+  else if (w2::make_map2(&mo, args.out, a_rows, args.N, args.ldo, 64, 32, false)) return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_ctas); cfg.blockDim = dim3(t2::kTokThreads); cfg.dynamicSmemBytes = t2::kTokSmem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+#define MEP_T2_CASE(M)                                                                                                   \
+  case M:                                                                                                                \
+    MEP_CUDA_CHECK(cudaFuncSetAttribute(t2::tok_2cta_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t2::kTokSmem)); \
+    MEP_CUDA_CHECK(cudaLaunchKernelEx(&cfg, t2::tok_2cta_kernel<M>, ma, mb0, mb1, mo, args));                              \
+    break;
+  switch (mode) {
+    MEP_T2_CASE(GEMM_GATE_UP) MEP_T2_CASE(GEMM_DOWN) MEP_T2_CASE(GEMM_DGRAD) MEP_T2_CASE(GEMM_DGRAD_GU)
+    default: return set_error("gemm (2-CTA): unknown mode %d", mode);
+  }
+#undef MEP_T2_CASE
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;
 }

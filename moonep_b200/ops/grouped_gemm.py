@@ -79,7 +79,10 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
     a_rows = a.shape[0]
     a_ld = a.stride(0)
     a_cols = a.shape[1] if a_cols is None else a_cols
-    rc = lib.mep_grouped_gemm(mode, C.c_void_p(a.data_ptr()), C.c_int64(a_rows), C.c_int64(a_cols), C.c_int64(a_ld),
+    fn = lib.mep_grouped_gemm
+    if mode != WGRAD and os.environ.get("MOONEP_GEMM_2CTA", "0") == "1":
+        fn = lib.mep_grouped_gemm_2cta      # CTA-pair kernels (tcgen05 cta_group::2), 256-token tiles
+    rc = fn(mode, C.c_void_p(a.data_ptr()), C.c_int64(a_rows), C.c_int64(a_cols), C.c_int64(a_ld),
                               C.c_void_p(b0.data_ptr()), C.c_void_p(_native.ptr(b1)), C.c_int64(b_rows),
                               C.c_int64(b_cols), C.c_int64(b_ld), C.byref(args),
                               num_ctas or _num_sms(a.device), _native.cur_stream())
