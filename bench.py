@@ -95,6 +95,52 @@ def calibrate_skew(blk, x, target, world):
     return best
 
 
+def published_config_comm(world, rank):
+    """The configuration of the reference's published figure (EP=8, E=384, H=7168, K=8, S=8192 tokens
+    per rank, H'=2048, 32 SMs, token_padding=128, zero copy; figure/comm_vs_deepep.png, read at
+    maxvio ~1): dispatch fwd = planning + dispatch + weight prefetch, combine fwd = combine.
+    Published on H20: 2644 us and 1932 us.  Device-timed here, max over ranks."""
+    import torch
+    from moonep_b200 import Buffer, routing
+    from moonep_b200.pools import ExpertPools
+    S, H, Hp, K, epn = 8192, 7168, 2048, 8, 48
+    E = epn * world
+    buf = Buffer(S, H, K, E, world, num_sms=32, token_padding=128)
+    pools = ExpertPools(epn, (H, Hp), (H, Hp), (Hp, H))
+    scale, real = 0.0817, 1.005      # routing.solve_scale_for_maxvio(1.0, 8192, 8, 384, 8, seed=0), solved offline
+    topk, w, tpe = (t.cuda() for t in routing.softmax_topk(S, K, E, scale, 0, rank))
+    x = torch.randn(S, H, device="cuda").to(torch.bfloat16)
+    kw = pools.prefetch_kwargs()
+
+    def disp():
+        h, wn, cu, plan = buf.dispatch(x, w, topk, tpe, zero_copy=True, router_weights_zero_copy=True)
+        buf.prefetch_weight(plan=plan, **kw)
+        return h, plan
+
+    def timed(fn, n=5):
+        for _ in range(3):
+            fn()
+        barrier_sync(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier_sync(world)
+        return max_over_ranks(e0.elapsed_time(e1) / n * 1e3, world)
+
+    d_us = timed(disp)
+    h, plan = disp()
+    c_us = timed(lambda: buf.combine(plan=plan, hidden_nvsh=h, zero_copy=True))
+    buf.check()
+    pools.destroy()
+    buf.destroy()
+    return {"config": "EP=8 E=384 H=7168 K=8 S=8192 H'=2048 num_sms=32 token_padding=128 zero_copy",
+            "maxvio": round(real, 3), "dispatch_fwd_us": round(d_us, 1), "combine_fwd_us": round(c_us, 1),
+            "published_h20_dispatch_fwd_us": 2644, "published_h20_combine_fwd_us": 1932,
+            "speedup_vs_published_h20": round((2644 + 1932) / (d_us + c_us), 3)}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -210,9 +256,13 @@ def run_ours(args):
                           "slots_sent": st["slots_sent"]})
         blk.buf.check(); gg.check_status()
 
+    published = None
+    if world == 8 and not args.no_sweep:
+        published = published_config_comm(world, rank)
+
     tokens = S * world
     out = {
-        "metric": "moe_layer_train_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+        "metric": "moe_layer_train_step_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
@@ -226,6 +276,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": S * H * 2, "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches),
         "peak_mem_gib": round(peak_gb, 2), "loss": loss_val, "maxvio_sweep": sweep,
+        "published_config": published,
     }
     if rank == 0:
         print(json.dumps(out), flush=True)

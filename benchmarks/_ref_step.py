@@ -266,7 +266,7 @@ def run(args):
             sweep.append({"maxvio_target": mv, "maxvio": round(real, 3), "step_ms": round(sms, 3),
                           "dispatch_combine_us": round(mx(e0.elapsed_time(e1) / 5 * 1e3), 1)})
     tokens = S * world
-    out = {"metric": "moe_layer_train_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+    out = {"metric": "moe_layer_train_step_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
            "n_gpus": world, "steps": args.steps, "warmup": W_, "ms_per_step": ms, "higher_is_better": True,
            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
            "config": {"model": f"{args.model}-shape MoE layer (H={H}, H'={Hp}, K={K}, E={E}, epn={epn})",

@@ -14,6 +14,10 @@
 #include <stdint.h>
 #include "../mep_types.h"
 
+#ifndef MEP_POLL_SLEEP_NS
+#define MEP_POLL_SLEEP_NS 40   // pause between two polls of an mbarrier (see mbar_wait_bounded)
+#endif
+
 namespace mep {
 
 // ---------------------------------------------------------------- memory-model wrappers
@@ -214,11 +218,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   // 1106 TFLOP/s with this 40 ns pause, 875 without it -- threads spinning on barriers keep the
   // shared-memory pipe busy and slow down every other barrier / copy instruction of the CTA.
 #pragma unroll 1
-  for (int i = 0; i < 4096; ++i) { __nanosleep(40); if (mbar_try_wait(bar, parity)) return true; }
+  for (int i = 0; i < 4096; ++i) { __nanosleep(MEP_POLL_SLEEP_NS); if (mbar_try_wait(bar, parity)) return true; }
   const long long t0 = clock64(), lim = budget_cycles(budget_ns);
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i) { __nanosleep(40); if (mbar_try_wait(bar, parity)) return true; }
+    for (int i = 0; i < 32; ++i) { __nanosleep(MEP_POLL_SLEEP_NS); if (mbar_try_wait(bar, parity)) return true; }
     if (clock64() - t0 > lim) return false;
   }
 }
