@@ -113,7 +113,7 @@ struct CombineArgs {
 };
 struct CombineArgsPack { CombineArgs a[MEP_MAX_VRANKS]; };
 
-constexpr int kCombWarps = 12;
+constexpr int kCombWarps = 14;
 constexpr int kCombThreads = kCombWarps * 32;
 constexpr int kCombSlots = 32;                      // 16-byte vectors per lane in one warp stage (16 KB per warp)
 
@@ -129,7 +129,7 @@ __device__ __forceinline__ void cp_async_commit_wait_all() {
 // 16-byte copies (peer or local memory -> shared memory, no registers held while in flight),
 // waits for its own copies, adds the rows in fp32 (ascending k) and stores the bf16 result.
 // A lane only ever reads back what it copied itself, so no cross-lane synchronisation is needed.
-// With 12 warps per CTA up to 192 KB per SM are in flight, which is what hides NVLink latency.
+// With 14 warps per CTA up to 224 KB per SM are in flight, which is what hides NVLink latency.
 __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, CombineArgsPack A) {
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const CombineArgs& a = A.a[blockIdx.y];

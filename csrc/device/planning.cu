@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPa
   const uint32_t ep = a.epoch;
   unsigned long long* send_cur = c.send_cnt + (size_t)(ep & 1u) * R;
 
-  if (tid == 0) s_fail = 0;
+  if (tid == 0) { s_fail = 0; trace_mark(c, MEP_K_PLANNING, 1); }
   if (blockIdx.x == 0) {
     if (c.mc_base != nullptr && (E & 3) == 0 && R > 1) {
       char* row = c.mc_base + c.off_tpe + (size_t)c.rank * E * 4;
@@ -416,30 +416,40 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPa
       }
   }
 
-  auto count_prefix = [&](int v) {        // s_cnt[e] = entries of expert e in blocks < v of this rank
+  // Block histograms: every CTA publishes the histogram of each of its 1024-entry blocks and raises
+  // that block's flag to the launch epoch. The number of same-expert entries in earlier blocks is
+  // then a column sum over the earlier blocks' rows -- no rescan of the top-k table, no grid barrier.
+  for (int v = blockIdx.x; v < c.num_vblocks; v += nb) {
     for (int e = tid; e < E; e += nt) s_cnt[e] = 0;
     __syncthreads();
-    const int lim = v * VB;
-    for (int i0 = 0; i0 < lim; i0 += 8 * nt) {      // eight independent loads per thread, then warp-aggregated adds
-      int ev[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) { const int i = i0 + u * nt + tid; ev[u] = i < lim ? __ldg(a.topk + i) : -1; }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int i = i0 + u * nt + tid;
-        const bool on = i < lim;
-        int e = on ? ev[u] : 0;
-        if (on && (unsigned)e >= (unsigned)E) { report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 1, i, (uint32_t)e, (uint32_t)E); e = 0; }
-        const unsigned act = __ballot_sync(0xffffffffu, on);
-        if (on) {
-          const unsigned m = __match_any_sync(act, e);
-          if ((threadIdx.x & 31) == __ffs(m) - 1) atomicAdd(&s_cnt[e], __popc(m));
-        }
-      }
+    const int i = v * VB + tid;
+    if (tid < VB && i < N) {
+      const int e = __ldg(a.topk + i);
+      if ((unsigned)e < (unsigned)E) atomicAdd(&s_cnt[e], 1);
+      else report(c, MEP_ERR_BOUNDS, MEP_K_PLANNING, 1, i, (uint32_t)e, (uint32_t)E);
+    }
+    __syncthreads();
+    int* row = c.hist + (size_t)v * E;
+    for (int e = tid; e < E; e += nt) row[e] = s_cnt[e];
+    __syncthreads();
+    if (tid == 0) { __threadfence(); asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(c.vb_flags + v), "r"(ep) : "memory"); }
+  }
+  auto count_prefix = [&](int v) {        // s_cnt[e] = entries of expert e in blocks < v of this rank
+    for (int u = tid; u < v; u += nt) {
+      uint32_t seen = 0;
+      const bool ok = bounded_wait(c, [&] { seen = ld_acquire_gpu(c.vb_flags + u); return (int32_t)(seen - ep) >= 0; });
+      if (!ok) { report(c, MEP_ERR_GRID_SYNC_TIMEOUT, MEP_K_PLANNING, 12, u, seen, ep); s_fail = 1; }
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += nt) {
+      int run = 0;
+      for (int u = 0; u < v; ++u) run += __ldcg(c.hist + (size_t)u * E + e);
+      s_cnt[e] = run;
     }
     __syncthreads();
   };
   if ((int)blockIdx.x < c.num_vblocks) count_prefix(blockIdx.x);
+  if (tid == 0) trace_mark(c, MEP_K_PLANNING, 2);
 
   if (R > 1) {
     for (int p = tid; p < R; p += nt) {
@@ -451,12 +461,14 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPa
   }
   __syncthreads();
   if (s_fail) return;
+  if (tid == 0) trace_mark(c, MEP_K_PLANNING, 3);
 
   MepRankCtx cl = c;
   cl.count = s_count; cl.tpe_prefix = s_tpre; cl.remaining = s_rem; cl.alloc = s_alloc;
   cl.alloc_cumsum = s_acum; cl.expert_off = s_expoff; cl.etc_all = s_etc; cl.stats_all = s_stats;
   solve(cl, a, s_rem, true, blockIdx.x == 0);
   __syncthreads();
+  if (tid == 0) trace_mark(c, MEP_K_PLANNING, 4);
 
   cl.send_cnt = send_cur;
   const PlanTables T = {s_tpre, s_acum, s_expoff};
@@ -464,6 +476,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPa
     if (v != (int)blockIdx.x) count_prefix(v);
     assign_vblock<true>(cl, a, T, v, s_cnt, sm, s_tbl);
   }
+  if (tid == 0) trace_mark(c, MEP_K_PLANNING, 5);
 }
 
 }  // namespace mep

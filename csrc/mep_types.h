@@ -70,6 +70,8 @@ typedef struct MepRankCtx {
   // NVSwitch multicast alias of one chunk (null = not available): a multimem store to
   // mc_base + off lands at offset off of EVERY rank's chunk
   char* mc_base;
+  // fast planner: flag per 1024-entry block, set to the launch epoch once its histogram is published
+  uint32_t* vb_flags;
 } MepRankCtx;
 
 typedef struct MepCtxPack { const MepRankCtx* ctx[MEP_MAX_VRANKS]; } MepCtxPack;

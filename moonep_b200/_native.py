@@ -39,7 +39,7 @@ class MepRankCtx(C.Structure):
                                     "dup_group_cap", "dup_loff_cap")]
         + [(n, C.c_void_p) for n in ("grid_bar", "epoch", "hist", "count", "tpe_prefix", "remaining", "alloc",
                                      "alloc_cumsum", "expert_off", "etc_all", "stats_all", "send_cnt", "status")]
-        + [("wait_budget_ns", C.c_uint64), ("trace", C.c_void_p), ("trace_cap", C.c_int64), ("mc_base", C.c_void_p)]
+        + [("wait_budget_ns", C.c_uint64), ("trace", C.c_void_p), ("trace_cap", C.c_int64), ("mc_base", C.c_void_p), ("vb_flags", C.c_void_p)]
     )
 
 

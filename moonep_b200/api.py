@@ -299,6 +299,7 @@ class Buffer(OpsMixin):
         st.scratch["grid_bar"].zero_()
         st.scratch["epoch"].zero_()
         st.scratch["send_cnt"].zero_()
+        st.scratch["vb_flags"].zero_()
         st.plan_epoch = 0
         st.status.zero_()
         torch.cuda.synchronize()

@@ -74,6 +74,7 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     s["grid_bar"] = torch.zeros(4, **i32)
     s["epoch"] = torch.zeros(_native.BAR_ROWS, **i32)
     s["hist"] = torch.zeros(geo.num_vblocks * E, **i32)
+    s["vb_flags"] = torch.zeros(geo.num_vblocks, **i32)
     s["count"] = torch.zeros(E, **i32)
     s["tpe_prefix"] = torch.zeros(E, **i32)
     s["remaining"] = torch.zeros(E, **i32)
@@ -96,7 +97,7 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
         setattr(c, name, getattr(geo, name))
     c.dup_group_cap, c.dup_loff_cap = geo.dup_group_cap, geo.dup_loff_cap
     for name in ("grid_bar", "epoch", "hist", "count", "tpe_prefix", "remaining", "alloc", "alloc_cumsum",
-                 "expert_off", "etc_all", "stats_all", "send_cnt"):
+                 "expert_off", "etc_all", "stats_all", "send_cnt", "vb_flags"):
         setattr(c, name, s[name].data_ptr())
     c.status = st.status.data_ptr()
     c.wait_budget_ns = wait_budget_ns() if budget_ns is None else budget_ns
