@@ -28,9 +28,11 @@ def _relerr(a, b):
     return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
 
 
+@pytest.mark.parametrize("pair_kernels", [False, True], ids=["1cta", "cta_pairs"])
 @pytest.mark.parametrize("rpg", [[128, 0, 256, 128], [384, 128, 0, 0, 128, 256]])
-def test_gate_up_down(rpg, cuda_device):
+def test_gate_up_down(rpg, pair_kernels, cuda_device, monkeypatch):
     from moonep_b200.ops import grouped_gemm as gg
+    monkeypatch.setenv("MOONEP_GEMM_2CTA", "1" if pair_kernels else "0")
     G, K, N = len(rpg), 256, 256
     cu, tot, rows, x, g = _setup(G, rpg, K, N)
     wg = (torch.randn(G, K, N, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
@@ -57,8 +59,11 @@ def test_gate_up_down(rpg, cuda_device):
     assert (act[tot:] == 7.0).all() and (y[tot:] == 7.0).all(), "rows beyond cu_seqlens[-1] were written"
 
 
-def test_dgrad_and_wgrad(cuda_device):
+@pytest.mark.parametrize("pair_kernels", [False, True], ids=["1cta", "cta_pairs"])
+def test_dgrad_and_wgrad(pair_kernels, cuda_device, monkeypatch):
     from moonep_b200.ops import grouped_gemm as gg
+    monkeypatch.setenv("MOONEP_GEMM_2CTA", "1" if pair_kernels else "0")
+    monkeypatch.setenv("MOONEP_WGRAD_2CTA", "1" if pair_kernels else "0")
     rpg = [256, 128, 0, 384]
     G, H, Hp = len(rpg), 256, 256
     cu, tot, rows, x, g = _setup(G, rpg, H, Hp, seed=1)
