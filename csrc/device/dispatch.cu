@@ -21,7 +21,8 @@ struct DispatchArgs {
   const float* weights;          // [S, K] or null
   const int32_t* dst;            // [N] plan
   const int32_t* zero_fill;      // [2epn, 2] plan
-  int32_t fresh;                 // 1 or 2: publish duplicate-table counts to the peers (value - 1 = send_cnt half)
+  int32_t fresh;                 // non-zero: publish duplicate-table counts to the peers. 1 / 2: the planner used
+                                 // send_cnt half 0 / 1; 3: the half the fast planner's device-side epoch names
   int32_t entry_barrier;         // 1: cross-rank barrier before the first remote write
 };
 struct DispatchArgsPack { DispatchArgs a[MEP_MAX_VRANKS]; };
@@ -101,7 +102,8 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   if (a.fresh && blockIdx.x == 0) {
     // tell every destination how many groups / duplicate offsets this rank appended
     for (int d = tid; d < c.R; d += blockDim.x) {
-      const unsigned long long v = c.send_cnt[(size_t)(a.fresh - 1) * c.R + d];
+      const int half = a.fresh == 3 ? (int)(__ldcg(c.vb_flags + c.num_vblocks) & 1u) : a.fresh - 1;
+      const unsigned long long v = c.send_cnt[(size_t)half * c.R + d];
       int* cnt = (int*)peer_ptr(c, d, c.off_dupcnt) + 2 * c.rank;
       cnt[0] = (int)(v >> 32); cnt[1] = (int)(v & 0xffffffffu);
     }

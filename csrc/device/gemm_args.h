@@ -24,6 +24,10 @@ struct GemmArgs {
   int64_t ldo;
   int32_t* status;             // [4] error word: code, site, block, tile
   uint64_t budget_ns;
+  uint32_t* sched;             // [2] zero-initialised ticket counter of the dynamic tile scheduler, or null for
+                               // the static strided tile order
+  int32_t sched_ctas;          // dynamic order: CTAs over ALL launches that draw from `sched` (several launches of
+                               // one GEMM may share a counter); 0 = just this launch
 };
 
 }  // namespace mep

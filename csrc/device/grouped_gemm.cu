@@ -8,8 +8,11 @@
 //   * operands staged by 2-D tiled TMA (128-byte swizzle) from LOCAL memory into a 4-stage
 //     shared-memory ring; accumulators live in TMEM, double-buffered (2 x 256 columns) so the
 //     epilogue of tile i overlaps the main loop of tile i+1;
-//   * the tile scheduler walks `cu_seqlens` on the device (no host sync); every group is padded
-//     to a multiple of 128 rows by the planner, so a 128-row tile never straddles two experts.
+//   * the tile list comes from `cu_seqlens` on the device (no host sync); every group is padded
+//     to a multiple of 128 rows by the planner, so a 128-row tile never straddles two experts;
+//     tiles are walked in a fixed strided order or, when the launch passes a ticket counter,
+//     handed out dynamically (tile_queue.cuh) so that the kernel keeps its efficiency while a
+//     communication kernel owns some of the SMs for part of its run.
 // Tile: 128 x 256 x 64. Modes (weights stored [group, in, out], i.e. "N-contiguous"):
 //   GATE_UP   act = silu(x Wg) * (x Wu)       A K-major, B MN-major from two tensors (128+128)
 //   DOWN      y = (act Wd) * row_scale         A K-major, B MN-major
@@ -17,6 +20,7 @@
 //   DGRAD_GU  dx = dG Wg^T + dU Wu^T           A = [dG | dU] K-major, B K-major from two tensors
 //   WGRAD     dW[g] (+)= X_g^T dY_g  (fp32)    A and B MN-major, K = rows of the group
 #include "tcgen05.cuh"
+#include "tile_queue.cuh"
 #include "gemm_args.h"
 #include "../host/driver_api.h"
 #include "../host/launch.h"
@@ -59,6 +63,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
   __shared__ int s_ntiles, s_nact;
+  __shared__ tq::Ring s_ring;
   __shared__ int s_cu[kMaxGroups + 1];      // s_cu[g] = first row of group g (s_cu[G] = end)
   __shared__ int s_start[kMaxGroups + 1];   // non-WGRAD: first tile of group; WGRAD: active group ids
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -69,6 +74,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     s_abort = 0;
     for (int i = 0; i < kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], kEpiWarps); }
+    tq::init(&s_ring, 1 + kEpiWarps);
     fence_mbar_init();
     s_cu[0] = 0;
     for (int g = 0; g < G; ++g) s_cu[g + 1] = args.cu_seqlens[g];
@@ -93,6 +99,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   tc::fence_after_sync();
   const uint32_t tmem_base = s_tmem_base;
   const int ntiles = s_ntiles;
+  const bool dyn = args.sched != nullptr;
 
   auto fail = [&](int site, int tile) {
     if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = site; args.status[2] = blockIdx.x; args.status[3] = tile; }
@@ -124,7 +131,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // ---------------- TMA producer (one thread)
     if (lane == 0) {
       int it = 0, gcur = 0; TileInfo ti;
-      for (int t = blockIdx.x; t < ntiles && !s_abort && !(args.diag & 1); t += gridDim.x) {
+      tq::Scheduler<false> sched; if (dyn) sched.setup(&s_ring, args.sched, ntiles);
+      tq::Strided seq{(int)blockIdx.x, (int)gridDim.x, ntiles};
+      for (int t; !s_abort && (t = dyn ? sched.next(args.budget_ns) : seq.next()) != -1;) {
+        if (t == -2) { fail(5, sched.n); break; }
+        if (args.diag & 1) continue;
         get_tile(t, gcur, ti);
         for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
@@ -170,7 +181,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (lane == 0) {
       constexpr uint32_t idesc = tc::instr_desc_bf16(kBM, kBN, A_MN, B_MN);
       int it = 0, tcnt = 0, gcur = 0; TileInfo ti;
-      for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x, ++tcnt) {
+      tq::Consumer<false> tiles; tiles.setup(&s_ring);
+      tq::Strided seq{(int)blockIdx.x, (int)gridDim.x, ntiles};
+      for (int t; !s_abort && (t = dyn ? tiles.next(args.budget_ns) : seq.next()) != -1; ++tcnt) {
+        if (t == -2) { fail(6, tiles.n); break; }
         get_tile(t, gcur, ti);
         if (ti.kblocks == 0) { --tcnt; continue; }     // empty group: the epilogue writes zeros on its own
         const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
@@ -204,7 +218,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const uint32_t stg = smem_u32(smem + (size_t)kStages * kStageBytes) + (uint32_t)(warp - 2) * 2 * kSlabBytes;
     int chunk_no = 0;
     int tcnt = 0, gcur = 0; TileInfo ti;
-    for (int t = blockIdx.x; t < ntiles && !s_abort; t += gridDim.x, ++tcnt) {
+    tq::Consumer<false> tiles; tiles.setup(&s_ring);
+    tq::Strided seq{(int)blockIdx.x, (int)gridDim.x, ntiles};
+    for (;; ++tcnt) {
+      int t = -1;
+      if (!dyn) { if (!s_abort) t = seq.next(); }
+      else {
+        if (lane == 0 && !s_abort) { t = tiles.next(args.budget_ns); if (t == -2) fail(7, tiles.n); }
+        t = __shfl_sync(0xffffffffu, t, 0);
+      }
+      if (t < 0) break;
       get_tile(t, gcur, ti);
       if (ti.kblocks == 0) {
         if (MODE == GEMM_WGRAD) {
@@ -316,6 +339,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   __syncthreads();
   tc::fence_after_sync();
   if (warp == 1) tc::tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0) tq::scheduler_done(args.sched, args.sched_ctas > 0 ? args.sched_ctas : (int)gridDim.x);
 }
 
 static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows,

@@ -11,6 +11,7 @@
 // warps 2-9 = epilogue (each CTA drains its own 128 accumulator rows through shared memory + TMA
 // store / reduce-add).
 #include "tcgen05.cuh"
+#include "tile_queue.cuh"
 #include "gemm_args.h"
 #include "../host/driver_api.h"
 #include "../host/launch.h"
@@ -69,6 +70,7 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
   __shared__ int s_ntiles;
+  __shared__ tq::Ring s_ring;
   __shared__ int s_cu[kMaxGroups + 1], s_act[kMaxGroups];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cr = cluster_ctarank();
@@ -80,6 +82,7 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     s_abort = 0;
     for (int i = 0; i < kRing; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 2 * kEpiWarps); }
+    tq::init(&s_ring, 2 * kEpiWarps + 2);      // both CTAs' epilogue warps, the MMA issuer, the peer's producer
     fence_mbar_init();
     s_cu[0] = 0;
     for (int g = 0; g < G; ++g) s_cu[g + 1] = args.cu_seqlens[g];
@@ -98,6 +101,7 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   tc::fence_after_sync();
   const uint32_t tmem_base = s_tmem_base;
   const int ntiles = s_ntiles;
+  const bool dyn = args.sched != nullptr;
 
   auto fail = [&](int site, int tile) {
     if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = 100 + site; args.status[2] = blockIdx.x; args.status[3] = tile; }
@@ -115,7 +119,11 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     // ---------------- TMA producer: this CTA's halves; bytes are counted on the LEADER's barrier
     if (lane == 0) {
       int it = 0; Tile ti;
-      for (int t = pair; t < ntiles && !s_abort; t += npairs) {
+      tq::Scheduler<true> sched; tq::Consumer<true> follow;
+      if (dyn) { if (leader) sched.setup(&s_ring, args.sched, ntiles); else follow.setup(&s_ring); }
+      tq::Strided seq{pair, npairs, ntiles};
+      for (int t; !s_abort && (t = !dyn ? seq.next() : leader ? sched.next(args.budget_ns) : follow.next(args.budget_ns)) != -1;) {
+        if (t == -2) { fail(5, it); break; }
         get_tile(t, ti);
         for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
           const int s = it % kRing; const uint32_t ph = (uint32_t)(it / kRing) & 1u;
@@ -140,7 +148,10 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       for (int i = 0; i < kRing; ++i) empty_peer[i] = mapa(smem_u32(&empty_bar[i]), 1);
       for (int i = 0; i < 2; ++i) tfull_peer[i] = mapa(smem_u32(&tfull_bar[i]), 1);
       int it = 0, tcnt = 0; Tile ti;
-      for (int t = pair; t < ntiles && !s_abort; t += npairs, ++tcnt) {
+      tq::Consumer<true> tiles; tiles.setup(&s_ring);
+      tq::Strided seq{pair, npairs, ntiles};
+      for (int t; !s_abort && (t = dyn ? tiles.next(args.budget_ns) : seq.next()) != -1; ++tcnt) {
+        if (t == -2) { fail(6, tiles.n); break; }
         get_tile(t, ti);
         if (ti.kblocks == 0) { --tcnt; continue; }
         const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
@@ -171,7 +182,16 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     const uint32_t stg = smem_u32(smem + (size_t)kRing * kStageBytes) + (uint32_t)(warp - 2) * 2 * kSlabBytes;
     const uint32_t tempty_leader[2] = {mapa(smem_u32(&tempty_bar[0]), 0), mapa(smem_u32(&tempty_bar[1]), 0)};
     int tcnt = 0, chunk_no = 0; Tile ti;
-    for (int t = pair; t < ntiles && !s_abort; t += npairs, ++tcnt) {
+    tq::Consumer<true> tiles; tiles.setup(&s_ring);
+    tq::Strided seq{pair, npairs, ntiles};
+    for (;; ++tcnt) {
+      int t = -1;
+      if (!dyn) { if (!s_abort) t = seq.next(); }
+      else {
+        if (lane == 0 && !s_abort) { t = tiles.next(args.budget_ns); if (t == -2) fail(7, tiles.n); }
+        t = __shfl_sync(0xffffffffu, t, 0);
+      }
+      if (t < 0) break;
       get_tile(t, ti);
       const int orow0 = ti.g * args.M_w + ti.m0 + (int)cr * 128 + q * 32;
       if (ti.kblocks == 0) {           // empty group that must end with a zero gradient
@@ -225,6 +245,7 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   cluster_sync();
   tc::fence_after_sync();
   if (warp == 1) tmem_dealloc2(tmem_base, 512);
+  if (leader && threadIdx.x == 0) tq::scheduler_done(args.sched, args.sched_ctas > 0 ? args.sched_ctas / 2 : npairs);
 }
 
 static int make_map2(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows, bool f32) {
@@ -273,6 +294,7 @@ tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
   __shared__ int s_ntiles;
+  __shared__ tq::Ring s_ring;
   __shared__ int s_cu[kMaxGroups + 1], s_start[kMaxGroups + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cr = cluster_ctarank();
@@ -286,6 +308,7 @@ tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     s_abort = 0;
     for (int i = 0; i < kTokRing; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 2 * kTokEpi); }
+    tq::init(&s_ring, 2 * kTokEpi + 2);
     fence_mbar_init();
     s_cu[0] = 0;
     for (int g = 0; g < G; ++g) s_cu[g + 1] = args.cu_seqlens[g];
@@ -304,6 +327,7 @@ tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   tc::fence_after_sync();
   const uint32_t tmem_base = s_tmem_base;
   const int ntiles = s_ntiles;
+  const bool dyn = args.sched != nullptr;
 
   auto fail = [&](int site, int tile) {
     if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = 200 + site; args.status[2] = blockIdx.x; args.status[3] = tile; }
@@ -322,7 +346,11 @@ tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   if (warp == 0) {
     if (lane == 0) {
       int it = 0, gcur = 0; TTile ti;
-      for (int t = pair; t < ntiles && !s_abort; t += npairs) {
+      tq::Scheduler<true> sched; tq::Consumer<true> follow;
+      if (dyn) { if (leader) sched.setup(&s_ring, args.sched, ntiles); else follow.setup(&s_ring); }
+      tq::Strided seq{pair, npairs, ntiles};
+      for (int t; !s_abort && (t = !dyn ? seq.next() : leader ? sched.next(args.budget_ns) : follow.next(args.budget_ns)) != -1;) {
+        if (t == -2) { fail(5, it); break; }
         get_tile(t, gcur, ti);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % kTokRing; const uint32_t ph = (uint32_t)(it / kTokRing) & 1u;
@@ -353,7 +381,10 @@ tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       for (int i = 0; i < kTokRing; ++i) empty_peer[i] = mapa(smem_u32(&empty_bar[i]), 1);
       for (int i = 0; i < 2; ++i) tfull_peer[i] = mapa(smem_u32(&tfull_bar[i]), 1);
       int it = 0, tcnt = 0;
-      for (int t = pair; t < ntiles && !s_abort; t += npairs, ++tcnt) {
+      tq::Consumer<true> tiles; tiles.setup(&s_ring);
+      tq::Strided seq{pair, npairs, ntiles};
+      for (int t; !s_abort && (t = dyn ? tiles.next(args.budget_ns) : seq.next()) != -1; ++tcnt) {
+        if (t == -2) { fail(6, tiles.n); break; }
         const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
         if (!mbar_wait_bounded(&tempty_bar[acc], aph ^ 1u, args.budget_ns)) { fail(2, t); break; }
         tc::fence_after_sync();
@@ -384,7 +415,16 @@ tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const uint32_t stg = smem_u32(smem + (size_t)kTokRing * kStageBytes) + (uint32_t)(warp - 2) * 2 * kSlabBytes;
     const uint32_t tempty_leader[2] = {mapa(smem_u32(&tempty_bar[0]), 0), mapa(smem_u32(&tempty_bar[1]), 0)};
     int tcnt = 0, gcur = 0, chunk_no = 0; TTile ti;
-    for (int t = pair; t < ntiles && !s_abort; t += npairs, ++tcnt) {
+    tq::Consumer<true> tiles; tiles.setup(&s_ring);
+    tq::Strided seq{pair, npairs, ntiles};
+    for (;; ++tcnt) {
+      int t = -1;
+      if (!dyn) { if (!s_abort) t = seq.next(); }
+      else {
+        if (lane == 0 && !s_abort) { t = tiles.next(args.budget_ns); if (t == -2) fail(7, tiles.n); }
+        t = __shfl_sync(0xffffffffu, t, 0);
+      }
+      if (t < 0) break;
       get_tile(t, gcur, ti);
       const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
       int ok = 1;
@@ -468,6 +508,7 @@ tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   cluster_sync();
   tc::fence_after_sync();
   if (warp == 1) tmem_dealloc2(tmem_base, 512);
+  if (leader && threadIdx.x == 0) tq::scheduler_done(args.sched, args.sched_ctas > 0 ? args.sched_ctas / 2 : npairs);
 }
 
 static int make_map_mn3(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int atoms) {

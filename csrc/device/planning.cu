@@ -364,8 +364,11 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P,
 
 // ---------------------------------------------------------------------------------------------
 // Fast path (E <= 2048, E*R <= 8192): no grid-wide barrier at all.
-//   * CTA 0 publishes this rank's histogram and then release-stores the launch epoch (counted by
-//     the host, identical on all ranks) into every peer's flag slot;
+//   * CTA 0 publishes this rank's histogram and then release-stores the launch epoch into every
+//     peer's flag slot. The epoch lives in device memory (word `vb_flags[num_vblocks]`, the number
+//     of fast plannings this rank has completed; identical on all ranks because planning is
+//     collective): every CTA reads it on entry, and the last CTA to leave the kernel advances it,
+//     so a captured CUDA graph can be replayed without the host counting anything;
 //   * EVERY CTA waits for all peers' epochs itself and then solves the plan redundantly into its
 //     own shared memory (the solve is a few microseconds and fully deterministic), so nothing has
 //     to be exchanged between the CTAs of a rank;
@@ -391,8 +394,16 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPa
   int* s_acum = s_alloc + E * R;
   int* s_expoff = s_acum + E * R;
   int* s_tbl = E <= kFastTableE ? s_expoff + E * R : nullptr;     // [32, E] ranking table
-  const uint32_t ep = a.epoch;
+  uint32_t* const epoch_word = c.vb_flags + c.num_vblocks;      // [0] completed epochs, [1] CTAs that left
+  const uint32_t ep = __ldcg(epoch_word) + 1u;
   unsigned long long* send_cur = c.send_cnt + (size_t)(ep & 1u) * R;
+  // every exit path runs this: the last CTA out advances the epoch for the next launch
+  auto leave = [&]() {
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(epoch_word + 1, 1u) == (uint32_t)nb - 1u) { epoch_word[1] = 0u; epoch_word[0] = ep; __threadfence(); }
+    }
+  };
 
   if (tid == 0) { s_fail = 0; trace_mark(c, MEP_K_PLANNING, 1); }
   if (blockIdx.x == 0) {
@@ -460,7 +471,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPa
     }
   }
   __syncthreads();
-  if (s_fail) return;
+  if (s_fail) { leave(); return; }
   if (tid == 0) trace_mark(c, MEP_K_PLANNING, 3);
 
   MepRankCtx cl = c;
@@ -477,6 +488,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPa
     assign_vblock<true>(cl, a, T, v, s_cnt, sm, s_tbl);
   }
   if (tid == 0) trace_mark(c, MEP_K_PLANNING, 5);
+  leave();
 }
 
 }  // namespace mep
@@ -496,7 +508,7 @@ extern "C" int mep_launch_planning(int nv, const MepRankCtx* const* ctxs, const 
                                  stream, false, P, A);
 }
 
-// 1 if a geometry is served by the barrier-free planning kernel (the caller then counts epochs).
+// 1 if a geometry is served by the barrier-free planning kernel (selected with PlanArgs.epoch != 0).
 extern "C" int mep_planning_is_fast(int E, int R) {
   return (E <= mep::kFastMaxE && (long long)E * R <= mep::kFastMaxER) ? 1 : 0;
 }

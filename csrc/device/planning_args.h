@@ -13,7 +13,8 @@ struct PlanArgs {
   int32_t* experts_to_copy;   // [R, epn]
   int32_t* zero_fill;         // [2epn, 2]
   int32_t* remote_stats;      // [2]
-  uint32_t epoch;             // fast path: barrier epoch of this launch, counted by the host (same on all ranks)
+  uint32_t epoch;             // non-zero selects the barrier-free fast path where the geometry allows it (the launch
+                              // epoch itself is kept in device memory, see planning_fast_kernel)
   int32_t pad;
 };
 struct PlanArgsPack { PlanArgs a[MEP_MAX_VRANKS]; };

@@ -300,7 +300,6 @@ class Buffer(OpsMixin):
         st.scratch["epoch"].zero_()
         st.scratch["send_cnt"].zero_()
         st.scratch["vb_flags"].zero_()
-        st.plan_epoch = 0
         st.status.zero_()
         torch.cuda.synchronize()
         if self.geo.R > 1:
@@ -434,6 +433,21 @@ class Buffer(OpsMixin):
             assert l.ndim == 3
         self._check_weight_pairs(locals_, pools, (torch.float32,), "reduce_grad")
         pairs = list(zip(locals_, pools))
+        tensors = [plan.experts_to_copy] + [t for pr in pairs for t in pr]
+        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs]))
+        return ev
+
+    def reduce_grad_subset(self, plan: MoonEPCommPlan, grads, async_finish: bool = False):
+        """``reduce_grad`` for any non-empty subset of the projections: ``grads`` is a sequence of
+        ``(local_grad [epn, ...] fp32, reduce_buffer [R, epn, ...] fp32)`` pairs.  Lets a training
+        step reduce the gradient of one projection while it still computes the others.  Collective
+        like ``reduce_grad``: every rank must issue the same calls in the same order.  (Extension:
+        the reference only offers the three-projection call.)"""
+        self._st()
+        assert isinstance(plan, MoonEPCommPlan), "Buffer.reduce_grad_subset: plan is required"
+        pairs = [(l, p) for l, p in grads]
+        assert 1 <= len(pairs) <= 3, "reduce_grad_subset takes one to three (local_grad, reduce_buffer) pairs"
+        self._check_weight_pairs([l for l, _ in pairs], [p for _, p in pairs], (torch.float32,), "reduce_grad_subset")
         tensors = [plan.experts_to_copy] + [t for pr in pairs for t in pr]
         _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs]))
         return ev

@@ -57,7 +57,6 @@ class RankState:
     hidden_local: torch.Tensor = None     # [NvS, H] bf16 view of this rank's shard
     weights_local: torch.Tensor = None    # [NvS] fp32 view
     status: torch.Tensor = None           # int32[8] device
-    plan_epoch: int = 0                   # fresh plans launched so far (fast planner's barrier epoch)
     plan_fast: bool = False
 
     @property
@@ -74,7 +73,7 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     s["grid_bar"] = torch.zeros(4, **i32)
     s["epoch"] = torch.zeros(_native.BAR_ROWS, **i32)
     s["hist"] = torch.zeros(geo.num_vblocks * E, **i32)
-    s["vb_flags"] = torch.zeros(geo.num_vblocks, **i32)
+    s["vb_flags"] = torch.zeros(geo.num_vblocks + 2, **i32)      # + the fast planner's epoch word and exit counter
     s["count"] = torch.zeros(E, **i32)
     s["tpe_prefix"] = torch.zeros(E, **i32)
     s["remaining"] = torch.zeros(E, **i32)
@@ -169,11 +168,9 @@ def launch_planning(states, topk_list, tpe_list, plans, cu_list):
     for i in range(n):
         p = plans[i]
         st = states[i]
-        if st.plan_fast:
-            st.plan_epoch += 1
         args[i] = PlanArgs(ptr(topk_list[i]), ptr(tpe_list[i]), ptr(p.dst), ptr(cu_list[i]),
                            ptr(p.experts_to_copy), ptr(p.zero_fill_ranges), ptr(p.remote_stats),
-                           st.plan_epoch if st.plan_fast else 0, 0)
+                           1 if st.plan_fast else 0, 0)
     g = states[0].geo
     _native.check(lib.mep_launch_planning(n, _pack(states), args, g.num_sms, g.E, g.R, _native.cur_stream()), "planning")
 
@@ -184,9 +181,9 @@ def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry
     args = (DispatchArgs * n)()
     for i in range(n):
         w = weights_list[i] if weights_list is not None else None
-        half = (states[i].plan_epoch & 1) if states[i].plan_fast else 0     # send_cnt half the planner used
+        fresh_code = 3 if states[i].plan_fast else 1      # which send_cnt half the planner used (3: device epoch)
         args[i] = DispatchArgs(ptr(hidden_list[i]), ptr(w), ptr(plans[i].dst), ptr(plans[i].zero_fill_ranges),
-                               (1 + half) if fresh else 0, 1 if entry_barrier else 0)
+                               fresh_code if fresh else 0, 1 if entry_barrier else 0)
     g = states[0].geo
     _native.check(lib.mep_launch_dispatch(n, _pack(states), args, g.num_sms, g.H, g.epn, _native.cur_stream()), "dispatch")
 

@@ -99,9 +99,22 @@ class MoEBlock:
             ps += self.shared
         return ps
 
+    def fuse_optimizer(self, lr: float | None):
+        """Apply the experts' SGD update inside the backward pass: each projection is updated on a
+        side stream as soon as its gradient is final (``ExpertParallelMoE.on_grad_ready``), beside
+        the GEMMs that are still running.  ``None`` switches back to updating in ``sgd_step``."""
+        self._fused_lr = lr
+        if lr is None:
+            self.moe.on_grad_ready = None
+        else:
+            self.moe.on_grad_ready = lambda n: gg.sgd_step(self.pools.local_weight(n), self.pools.local_grad(n), lr)
+
     def sgd_step(self, lr: float):
-        for n in ("gate", "up", "down"):
-            gg.sgd_step(self.pools.local_weight(n), self.pools.local_grad(n), lr)
+        if self.moe.on_grad_ready is None:
+            for n in ("gate", "up", "down"):
+                gg.sgd_step(self.pools.local_weight(n), self.pools.local_grad(n), lr)
+        else:
+            assert lr == self._fused_lr, "the experts were already updated with another learning rate"
         with torch.no_grad():
             for p in self.parameters():
                 if p.grad is not None:

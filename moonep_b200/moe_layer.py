@@ -2,12 +2,15 @@
 
 Forward  : dispatch -> [prefetch_weight on the comm stream] -> gate/up GEMM with fused
            SwiGLU and route-weight scaling (local experts first, prefetched experts once their
-           weights have landed) -> down GEMM writing straight into the communication shard ->
-           combine (zero copy).
-Backward : re-dispatch of the output grad with the saved plan -> dgrad(down) + wgrad(down) ->
-           SwiGLU backward (also yields the route-weight grads) -> dgrad(gate/up) into the shard
-           -> wgrad(gate), wgrad(up) -> combine with the route-weight-grad channel ->
-           reduce_grad of the replicated experts.
+           weights have landed; the private copy of the dispatched tokens that the backward
+           pass needs is taken on a side stream meanwhile) -> down GEMM writing straight into
+           the communication shard -> combine (zero copy).
+Backward : re-dispatch of the output grad with the saved plan -> dgrad(down) -> SwiGLU backward
+           (also yields the route-weight grads) -> wgrad(down), wgrad(gate) -> [reduce_grad of
+           those two on the comm stream] beside dgrad(gate/up) into the shard -> [combine with
+           the route-weight-grad channel on the comm stream] beside wgrad(up) -> reduce_grad(up).
+           An optional per-projection hook lets the optimizer update a projection as soon as its
+           gradient is final, beside the remaining GEMMs.
 This is the integration the reference leaves to the training framework (README.md:110-156 of
 the reference gives the same operator mapping).  Weights are ``[2*epn, in, out]`` compute views
 of an ``ExpertPools``; weight grads are fp32 ``[2*epn, in, out]`` whose tail is the reduce slots.
@@ -15,6 +18,7 @@ of an ``ExpertPools``; weight grads are fp32 ``[2*epn, in, out]`` whose tail is 
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -36,7 +40,8 @@ class MoEContext:
 
 
 class ExpertParallelMoE:
-    def __init__(self, buffer: Buffer, pools: ExpertPools, overlap_prefetch: bool = True):
+    def __init__(self, buffer: Buffer, pools: ExpertPools, overlap_prefetch: bool = True,
+                 overlap_backward: bool | None = None):
         g = buffer.geo
         self.buf, self.pools, self.geo = buffer, pools, g
         self.H = g.H
@@ -46,7 +51,15 @@ class ExpertParallelMoE:
         assert g.token_padding % 128 == 0, "the grouped GEMM needs token_padding to be a multiple of 128"
         assert pools.epn == g.epn
         self.overlap_prefetch = overlap_prefetch
+        if overlap_backward is None:        # MOONEP_OVERLAP_BACKWARD=0 serialises the backward pass
+            overlap_backward = os.environ.get("MOONEP_OVERLAP_BACKWARD", "1") != "0"
+        self.overlap_backward = overlap_backward
         dev = buffer.hidden_nvsh_buffer_view.device
+        self._side = torch.cuda.Stream(device=dev)
+        self._opt = torch.cuda.Stream(device=dev)
+        self._total_sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self._comm_sms = min(g.num_sms & ~1, self._total_sms - 2)
+        self.on_grad_ready = None       # callable(name) -> None, see backward()
         bf = dict(dtype=torch.bfloat16, device=dev)
         # activations are allocated once; shapes are static (no per-step allocator traffic)
         self._act = torch.zeros(g.NvS, self.Hp, **bf)
@@ -71,12 +84,15 @@ class ExpertParallelMoE:
         ev = None
         if g.R > 1:
             ev = buf.prefetch_weight(plan=plan, async_finish=self.overlap_prefetch, **self.pools.prefetch_kwargs())
-        if need_backward:       # the shard is overwritten below: keep private copies for wgrad
-            self._x.copy_(h_view)
-            self._w.copy_(w_view)
-            x, w = self._x, self._w
-        else:
-            x, w = h_view, w_view
+        x, w = h_view, w_view
+        stashed = None
+        if need_backward:       # the shard is overwritten by the down GEMM: keep private copies for wgrad
+            main = torch.cuda.current_stream()
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                self._x.copy_(h_view)
+                self._w.copy_(w_view)
+                stashed = self._side.record_event()
         gu = self._gu if need_backward else None
         Wg, Wu, Wd = self._W("gate"), self._W("up"), self._W("down")
         if ev is not None:
@@ -85,27 +101,86 @@ class ExpertParallelMoE:
             gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, groups=(epn, 2 * epn))
         else:
             gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w)
+        if stashed is not None:
+            torch.cuda.current_stream().wait_event(stashed)
         gg.down(self._act, Wd, cu, buf.hidden_nvsh_buffer_view)
         out, _, _ = buf.combine(plan=plan, hidden_nvsh=buf.hidden_nvsh_buffer_view, zero_copy=True)
-        ctx = MoEContext(plan, cu, x, w, self._act, self._gu) if need_backward else None
+        ctx = MoEContext(plan, cu, self._x, self._w, self._act, self._gu) if need_backward else None
         return out, ctx
 
+    def _optimizer(self, name: str, *after):
+        """Run the integrator's per-projection optimizer hook on the optimizer stream once the
+        events / streams in ``after`` are done."""
+        if self.on_grad_ready is None:
+            return
+        for a in after:
+            if isinstance(a, torch.cuda.Event):
+                self._opt.wait_event(a)
+            else:
+                self._opt.wait_stream(a)
+        with torch.cuda.stream(self._opt):
+            self.on_grad_ready(name)
+
+    def _beside_comm(self, launch):
+        """Issue one grouped GEMM that shares the GPU with the communication kernel just queued on
+        the comm stream: ``launch(num_ctas, ticket)`` is called twice with one ticket counter --
+        on the current stream for the SMs the communication kernel leaves free, and on the comm
+        stream behind that kernel for the SMs it gives back -- so the two launches split the
+        GEMM's tiles dynamically.  Returns the event that completes the second launch."""
+        tk = gg.Ticket(self._act.device, self._total_sms)
+        launch(self._total_sms - self._comm_sms, tk)
+        comm = self.buf.comm_stream
+        with torch.cuda.stream(comm):
+            launch(self._comm_sms, tk)
+            return comm.record_event()
+
     def backward(self, ctx: MoEContext, grad_out_sh):
+        """Order of work (``overlap_backward``): the weight-grad GEMMs of ``down`` and ``gate`` come
+        first, so that their cross-rank reduction runs on the comm stream beside dgrad(gate/up); the
+        combine of the input grads then runs beside wgrad(up); only the reduction of ``up`` is
+        exposed.  A GEMM that shares the GPU with a communication kernel is split over two launches
+        with a common ticket counter (``_beside_comm``).
+        ``on_grad_ready(name)``, if set, is called on a side stream as soon as the local gradient of
+        projection ``name`` is final and its weights are no longer read (optimizer in backward)."""
         buf, g, epn, Hp = self.buf, self.geo, self.geo.epn, self.Hp
-        acc = self.accumulate_grads
+        acc, ov, multi = self.accumulate_grads, self.overlap_backward, self.geo.R > 1
+        main = torch.cuda.current_stream()
+        pools = self.pools
+        pair = lambda n: (pools.local_grad(n), pools.reduce_view(n))      # noqa: E731
         dy, _, _, _ = buf.dispatch(grad_out_sh, plan=ctx.plan, zero_copy=True)
         Wg, Wu, Wd = self._W("gate"), self._W("up"), self._W("down")
+        shard = buf.hidden_nvsh_buffer_view
         gg.dgrad(dy, Wd, ctx.cu, self._dA)
-        gg.wgrad(ctx.act, dy, ctx.cu, self._dW("down"), accumulate=acc, zero_empty_below=epn)
         dw_view = buf.router_weight_buffer_view
         gg.swiglu_bwd(self._dA, ctx.gu, ctx.w_nvs, self._dgu, dw_view, ctx.cu)
-        gg.dgrad_gate_up(self._dgu, Wg, Wu, ctx.cu, buf.hidden_nvsh_buffer_view)
+        gg.wgrad(ctx.act, dy, ctx.cu, self._dW("down"), accumulate=acc, zero_empty_below=epn)
+        if not multi:
+            self._optimizer("down", main)
         gg.wgrad(ctx.x, self._dgu[:, :Hp], ctx.cu, self._dW("gate"), accumulate=acc, zero_empty_below=epn)
-        gg.wgrad(ctx.x, self._dgu[:, Hp:], ctx.cu, self._dW("up"), accumulate=acc, zero_empty_below=epn)
-        grad_hidden, grad_w, _ = buf.combine(plan=ctx.plan, hidden_nvsh=buf.hidden_nvsh_buffer_view,
-                                             route_weights_nvs=dw_view, zero_copy=True, router_weights_zero_copy=True)
-        if g.R > 1:
-            buf.reduce_grad(plan=ctx.plan, **self.pools.reduce_kwargs())
+        ev_red = None
+        if multi:
+            ev_red = buf.reduce_grad_subset(ctx.plan, [pair("down"), pair("gate")], async_finish=ov)
+            self._optimizer("down", ev_red if ov else main)
+        if ov and multi:
+            ev = self._beside_comm(lambda n, tk: gg.dgrad_gate_up(self._dgu, Wg, Wu, ctx.cu, shard, num_ctas=n, ticket=tk))
+            main.wait_event(ev)
+        else:
+            gg.dgrad_gate_up(self._dgu, Wg, Wu, ctx.cu, shard)
+        self._optimizer("gate", main, *([ev_red] if ev_red is not None else []))
+        grad_hidden, grad_w, ev_comb = buf.combine(plan=ctx.plan, hidden_nvsh=shard, route_weights_nvs=dw_view,
+                                                   async_finish=ov, zero_copy=True, router_weights_zero_copy=True)
+        dW_up, dU = self._dW("up"), self._dgu[:, Hp:]
+        if ov:
+            ev = self._beside_comm(lambda n, tk: gg.wgrad(ctx.x, dU, ctx.cu, dW_up, accumulate=acc, zero_empty_below=epn,
+                                                          num_ctas=n, ticket=tk))
+            main.wait_event(ev)       # also covers the combine, which precedes that launch on the comm stream
+        else:
+            gg.wgrad(ctx.x, dU, ctx.cu, dW_up, accumulate=acc, zero_empty_below=epn)
+        if multi:
+            buf.reduce_grad_subset(ctx.plan, [pair("up")])
+        if self.on_grad_ready is not None:
+            self.on_grad_ready("up")
+            main.wait_stream(self._opt)
         return grad_hidden, grad_w
 
 

@@ -26,7 +26,8 @@ class GemmArgs(C.Structure):
                 ("M_w", C.c_int32), ("b_group_rows", C.c_int32), ("accumulate", C.c_int32),
                 ("g_begin", C.c_int32), ("g_end", C.c_int32), ("zero_empty_below", C.c_int32), ("diag", C.c_int32),
                 ("out", C.c_void_p), ("out2", C.c_void_p), ("row_scale", C.c_void_p), ("ldo", C.c_int64),
-                ("status", C.c_void_p), ("budget_ns", C.c_uint64)]
+                ("status", C.c_void_p), ("budget_ns", C.c_uint64), ("sched", C.c_void_p),
+                ("sched_ctas", C.c_int32)]
 
 
 def _dev_index(device) -> int:
@@ -39,6 +40,41 @@ def _status(device) -> torch.Tensor:
     if key not in _status_cache:
         _status_cache[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
     return _status_cache[key]
+
+
+_SCHED_SLOTS = 64
+_sched_cache: dict = {}
+
+
+class Ticket:
+    """A ticket counter that several launches of ONE grouped GEMM share: the launches (e.g. one on
+    the compute stream beside a communication kernel, a second one behind that kernel on its
+    stream) then split the GEMM's tiles between them dynamically.  ``total_ctas`` is the sum of
+    the launches' CTA counts; every launch must be issued, and the counter is clean again once the
+    last of them has finished."""
+
+    def __init__(self, device, total_ctas: int):
+        self.ptr = _sched(device, True, force=True)
+        self.total_ctas = int(total_ctas)
+
+
+def _sched(device, dynamic: bool, force: bool = False) -> int:
+    """Ticket counter for one launch with the dynamic tile scheduler, or 0 for the static tile
+    order.  ``dynamic`` is the caller's wish (set for GEMMs that run beside a communication kernel,
+    where CTAs start late); ``MOONEP_GEMM_DYNAMIC=1`` / ``=0`` forces it on / off for every launch.
+    Counters are handed out round-robin from a per-device pool so that GEMMs running concurrently
+    on different streams never share one; each kernel leaves its counter at zero."""
+    env = os.environ.get("MOONEP_GEMM_DYNAMIC")
+    if env is not None and not force:
+        dynamic = env == "1"
+    if not dynamic:
+        return 0
+    key = _dev_index(device)
+    ent = _sched_cache.get(key)
+    if ent is None:
+        ent = _sched_cache[key] = [torch.zeros(2 * _SCHED_SLOTS, dtype=torch.int32, device=torch.device("cuda", key)), 0]
+    ent[1] = (ent[1] + 1) % _SCHED_SLOTS
+    return ent[0].data_ptr() + 8 * ent[1]
 
 
 def _num_sms(device) -> int:
@@ -54,11 +90,15 @@ def check_status(device="cuda") -> None:
     v = st.cpu().tolist()
     if v[0] != 0:
         st.zero_()
+        ent = _sched_cache.get(_dev_index(device))
+        if ent is not None:
+            ent[0].zero_()
         raise RuntimeError(f"grouped GEMM aborted: code {v[0]} at site {v[1]}, CTA {v[2]}, tile {v[3]}")
 
 
 def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=None, row_scale=None, ldo=0,
-            accumulate=False, zero_empty_below=0, a_cols=None, b_rows=None, b_cols=None, b_ld=None, groups=None, num_ctas=None):
+            accumulate=False, zero_empty_below=0, a_cols=None, b_rows=None, b_cols=None, b_ld=None, groups=None, num_ctas=None,
+            dynamic=False, ticket=None):
     lib = _native.load()
     assert a.dtype == torch.bfloat16 and b0.dtype == torch.bfloat16
     assert cu.dtype == torch.int32 and cu.is_contiguous()
@@ -76,6 +116,10 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
     args.status = _status(a.device).data_ptr()
     from ..engine import wait_budget_ns
     args.budget_ns = wait_budget_ns()
+    if ticket is not None:
+        args.sched, args.sched_ctas = ticket.ptr, ticket.total_ctas
+    else:
+        args.sched = _sched(a.device, dynamic)
     a_rows = a.shape[0]
     a_ld = a.stride(0)
     a_cols = a.shape[1] if a_cols is None else a_cols
@@ -94,44 +138,44 @@ def _w2d(w):
     return w.shape[0] * w.shape[1], w.shape[2]
 
 
-def gate_up(x, wg, wu, cu, act_out, gu_out=None, row_scale=None, groups=None, num_ctas=None):
+def gate_up(x, wg, wu, cu, act_out, gu_out=None, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None):
     """``act_out[r] = row_scale[r] * silu(x[r] Wg[g]) * (x[r] Wu[g])``; optionally stores the
     pre-activations ``gu_out = [x Wg | x Wu]`` (``[NvS, 2*out]``) for the backward pass."""
     G, K, N = wg.shape
     assert wu.shape == wg.shape and x.shape[1] == K and N % 128 == 0 and K % 64 == 0
     rows, cols = _w2d(wg)
     _launch(GATE_UP, x, wg, wu, cu, N=N, K=K, b_group_rows=K, out=act_out, out2=gu_out, row_scale=row_scale,
-            ldo=act_out.stride(0), b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
+            ldo=act_out.stride(0), b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
 
 
-def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None):
+def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None):
     """``out[r] = row_scale[r] * (act[r] Wd[g])`` with ``Wd [G, inner, hidden]``."""
     G, K, N = wd.shape
     assert act.shape[1] == K and N % 256 == 0 and K % 64 == 0
     rows, cols = _w2d(wd)
     _launch(DOWN, act, wd, None, cu, N=N, K=K, b_group_rows=K, out=out, row_scale=row_scale, ldo=out.stride(0),
-            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
 
 
-def dgrad(dy, w, cu, out, groups=None, num_ctas=None):
+def dgrad(dy, w, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None):
     """``out[r] = dy[r] W[g]^T`` with ``W [G, in, out]`` -> ``out [NvS, in]``."""
     G, N, K = w.shape
     assert dy.shape[1] == K and N % 256 == 0 and K % 64 == 0
     rows, cols = _w2d(w)
     _launch(DGRAD, dy, w, None, cu, N=N, K=K, b_group_rows=N, out=out, ldo=out.stride(0),
-            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
 
 
-def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None):
+def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None):
     """``out[r] = dG[r] Wg[g]^T + dU[r] Wu[g]^T`` with ``dgu = [dG | dU]`` (``[NvS, 2*inner]``)."""
     G, N, Kh = wg.shape
     assert dgu.shape[1] == 2 * Kh and N % 256 == 0 and Kh % 64 == 0
     rows, cols = _w2d(wg)
     _launch(DGRAD_GU, dgu, wg, wu, cu, N=N, K=2 * Kh, b_group_rows=N, out=out, ldo=out.stride(0),
-            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas)
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
 
 
-def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num_ctas=None):
+def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num_ctas=None, dynamic=False, ticket=None):
     """``out[g] (+)= x_g^T dy_g`` in fp32; ``out [G, in, out_dim]``.  ``dy`` may be a column slice
     of a wider matrix (row pitch = ``dy.stride(0)``).  Groups without rows are left untouched,
     except that with ``accumulate=False`` empty groups ``g < zero_empty_below`` are zeroed (local
@@ -153,13 +197,17 @@ def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num
         args.status = _status(x.device).data_ptr()
         from ..engine import wait_budget_ns
         args.budget_ns = wait_budget_ns()
+        if ticket is not None:
+            args.sched, args.sched_ctas = ticket.ptr, ticket.total_ctas
+        else:
+            args.sched = _sched(x.device, dynamic)
         rc = lib.mep_grouped_wgrad_2cta(C.c_void_p(x.data_ptr()), C.c_int64(x.shape[0]), C.c_int64(x.stride(0)),
                                         C.c_void_p(dy.data_ptr()), C.c_int64(dy.stride(0)), C.byref(args),
                                         num_ctas or _num_sms(x.device), _native.cur_stream())
         _native.check(rc, "grouped_wgrad_2cta")
         return
     _launch(WGRAD, x, dy, None, cu, N=N, M_w=M, out=out, accumulate=accumulate, zero_empty_below=zero_empty_below,
-            b_rows=dy.shape[0], b_cols=N, b_ld=dy.stride(0), groups=groups, num_ctas=num_ctas)
+            b_rows=dy.shape[0], b_cols=N, b_ld=dy.stride(0), groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
 
 
 def swiglu_bwd(dA, gu, w, dgu, dw, cu, num_blocks=None):

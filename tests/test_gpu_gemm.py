@@ -28,10 +28,12 @@ def _relerr(a, b):
     return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
 
 
+@pytest.mark.parametrize("tile_order", ["static", "dynamic"])
 @pytest.mark.parametrize("pair_kernels", [False, True], ids=["1cta", "cta_pairs"])
 @pytest.mark.parametrize("rpg", [[128, 0, 256, 128], [384, 128, 0, 0, 128, 256]])
-def test_gate_up_down(rpg, pair_kernels, cuda_device, monkeypatch):
+def test_gate_up_down(rpg, pair_kernels, tile_order, cuda_device, monkeypatch):
     from moonep_b200.ops import grouped_gemm as gg
+    monkeypatch.setenv("MOONEP_GEMM_DYNAMIC", "1" if tile_order == "dynamic" else "0")
     monkeypatch.setenv("MOONEP_GEMM_2CTA", "1" if pair_kernels else "0")
     G, K, N = len(rpg), 256, 256
     cu, tot, rows, x, g = _setup(G, rpg, K, N)
@@ -59,9 +61,11 @@ def test_gate_up_down(rpg, pair_kernels, cuda_device, monkeypatch):
     assert (act[tot:] == 7.0).all() and (y[tot:] == 7.0).all(), "rows beyond cu_seqlens[-1] were written"
 
 
+@pytest.mark.parametrize("tile_order", ["static", "dynamic"])
 @pytest.mark.parametrize("pair_kernels", [False, True], ids=["1cta", "cta_pairs"])
-def test_dgrad_and_wgrad(pair_kernels, cuda_device, monkeypatch):
+def test_dgrad_and_wgrad(pair_kernels, tile_order, cuda_device, monkeypatch):
     from moonep_b200.ops import grouped_gemm as gg
+    monkeypatch.setenv("MOONEP_GEMM_DYNAMIC", "1" if tile_order == "dynamic" else "0")
     monkeypatch.setenv("MOONEP_GEMM_2CTA", "1" if pair_kernels else "0")
     monkeypatch.setenv("MOONEP_WGRAD_2CTA", "1" if pair_kernels else "0")
     rpg = [256, 128, 0, 384]
@@ -125,3 +129,42 @@ def test_sgd(cuda_device):
     gg.sgd_step(p, g, 0.1)
     torch.cuda.synchronize()
     assert torch.equal(p, ref)
+
+
+@pytest.mark.parametrize("pair_kernels", [False, True], ids=["1cta", "cta_pairs"])
+def test_two_launches_share_one_ticket_counter(pair_kernels, cuda_device, monkeypatch):
+    """One GEMM issued as two launches on two streams with a common ticket counter: every tile is
+    computed exactly once, and the counter is clean afterwards (a third, ordinary dynamic launch
+    that happens to get the same counter still computes everything)."""
+    from moonep_b200.ops import grouped_gemm as gg
+    monkeypatch.setenv("MOONEP_WGRAD_2CTA", "1" if pair_kernels else "0")
+    rpg = [512, 0, 256, 1024, 128, 384]
+    G, H, Hp = len(rpg), 512, 512
+    cu, tot, rows, x, g = _setup(G, rpg, H, Hp, seed=3)
+    wd = (torch.randn(G, Hp, H, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    dy = (torch.randn(rows, H, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    dgu = (torch.randn(rows, Hp, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    dA = torch.zeros(rows, Hp, dtype=torch.bfloat16, device="cuda")
+    dW = torch.full((G, H, Hp), 3.0, device="cuda")
+    side = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    for _ in range(3):          # repeated use: the counter must come back to zero every time
+        dA.zero_(); dW.fill_(3.0)
+        side.wait_stream(main)
+        tk1, tk2 = gg.Ticket(dA.device, 24), gg.Ticket(dA.device, 24)
+        gg.dgrad(dy, wd, cu, dA, num_ctas=16, ticket=tk1)
+        gg.wgrad(x, dgu, cu, dW, accumulate=True, num_ctas=16, ticket=tk2)
+        with torch.cuda.stream(side):
+            gg.dgrad(dy, wd, cu, dA, num_ctas=8, ticket=tk1)
+            gg.wgrad(x, dgu, cu, dW, accumulate=True, num_ctas=8, ticket=tk2)
+        main.wait_stream(side)
+        torch.cuda.synchronize()
+        gg.check_status()
+        for gi, a, b in _group_slices(rpg):
+            if a == b:
+                assert (dW[gi] == 3.0).all()
+                continue
+            assert _relerr(dA[a:b], dy[a:b].float() @ wd[gi].float().T) < 1e-2, f"group {gi}: dgrad"
+            assert _relerr(dW[gi], 3.0 + x[a:b].float().T @ dgu[a:b].float()) < 2e-3, f"group {gi}: wgrad (each tile once)"
+    from moonep_b200.ops.grouped_gemm import _sched_cache
+    assert int(_sched_cache[dA.device.index][0].abs().sum()) == 0, "ticket counters must be left at zero"
