@@ -35,9 +35,12 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--no-sweep", action="store_true")
-    ap.add_argument("--optimizer-after-backward", action="store_true",
-                    help="update the experts after the backward pass instead of inside it")
+    ap.add_argument("--optimizer-in-backward", action="store_true",
+                    help="update each projection of the experts inside the backward pass, on a side stream, as soon "
+                         "as its gradient is final (measured slower than updating after the backward pass)")
     ap.add_argument("--maxvio", type=float, default=MAXVIO_MAIN)
+    ap.add_argument("--no-cuda-graph", action="store_true",
+                    help="launch every kernel of every step from Python instead of replaying a captured step")
     return ap.parse_args()
 
 
@@ -75,14 +78,14 @@ def calibrate_skew(blk, x, target, world):
     base = torch.randn(blk.E, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1234)).float()
 
     def mv(scale):
-        blk.router_bias = base * scale
+        blk.router_bias.copy_(base * scale)       # in place: captured steps read this tensor
         with torch.no_grad():
             _, _, tpe = blk.route(x)
         return group_maxvio(tpe, world)
 
     floor = mv(0.0)
     if target <= floor:
-        blk.router_bias = base * 0.0
+        blk.router_bias.zero_()
         return 0.0, floor
     lo, hi, best = 1e-3, 50.0, (0.0, floor)
     for _ in range(40):
@@ -93,7 +96,7 @@ def calibrate_skew(blk, x, target, world):
         if abs(v - target) <= max(0.02 * target, 0.005):
             break
         lo, hi = (mid, hi) if v < target else (lo, mid)
-    blk.router_bias = base * best[0]
+    blk.router_bias.copy_(base * best[0])
     return best
 
 
@@ -149,7 +152,8 @@ def run_ours(args):
     from moonep_b200 import _native
     from moonep_b200.models.moe_block import MoEBlock, CONFIGS
     from moonep_b200.ops import grouped_gemm as gg
-    from moonep_b200.utils import ClockSampler
+    from moonep_b200.utils import ClockSampler, GraphedSteps
+    from benchmarks._loss import mean_square
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -167,17 +171,19 @@ def run_ours(args):
     host_batches = [torch.randn(S, H, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(2)]
     dev_batches = [b.cuda() for b in host_batches]
     lr = 1e-3
-    if not args.optimizer_after_backward:
+    if args.optimizer_in_backward:
         blk.fuse_optimizer(lr)      # each projection's SGD runs beside the remaining backward GEMMs
 
     def step(x):
         x.requires_grad_(True)
         y = blk.forward(x)
-        loss = (y.float() ** 2).mean()
+        loss = mean_square(y)
         loss.backward()
         blk.sgd_step(lr)
         x.grad = None
         return loss.detach()
+
+    graphed = [None]        # GraphedSteps once a step has been captured
 
     def timed_steps(n):
         barrier_sync(world)
@@ -185,10 +191,14 @@ def run_ours(args):
         c0 = lib.mep_launch_count()
         e0.record()
         for i in range(n):
-            step(dev_batches[i % 2].detach())
+            if graphed[0] is not None:
+                graphed[0].replay(i)
+            else:
+                step(dev_batches[i % 2].detach())
         e1.record()
         barrier_sync(world)
-        return max_over_ranks(e0.elapsed_time(e1) / n, world), (lib.mep_launch_count() - c0)
+        launched = graphed[0].launches_per_step * n if graphed[0] is not None else lib.mep_launch_count() - c0
+        return max_over_ranks(e0.elapsed_time(e1) / n, world), launched
 
     scale, realised = calibrate_skew(blk, dev_batches[0], args.maxvio, world)
     sampler = ClockSampler(local).start()      # nvidia-smi needs a moment to come up: start before the warm-up
@@ -197,28 +207,59 @@ def run_ours(args):
     torch.cuda.synchronize()
     blk.buf.check(); gg.check_status()
 
+    # Capture the whole step (both input buffers) as CUDA graphs: one launch per step instead of
+    # ~100.  All ranks must take the same path, so a failure on any rank sends everyone back to
+    # launching from Python.
+    graph_note = "disabled (--no-cuda-graph)"
+    if not args.no_cuda_graph:
+        try:
+            c0 = lib.mep_launch_count()
+            gs = GraphedSteps(lambda x: step(x), dev_batches)
+            gs.launches_per_step = (lib.mep_launch_count() - c0) // len(gs)
+            ok, graph_note = 1, "whole step replayed from a captured CUDA graph"
+        except Exception as e:      # noqa: BLE001
+            gs, ok, graph_note = None, 0, f"capture failed, launched from Python: {type(e).__name__}: {str(e)[:160]}"
+        if world > 1:
+            t = torch.tensor([ok], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            if int(t) == 0 and ok:
+                gs, graph_note = None, "capture failed on another rank, launched from Python"
+        if gs is not None:
+            graphed[0] = gs
+            for i in range(3):
+                gs.replay(i)
+            torch.cuda.synchronize()
+            blk.buf.check(); gg.check_status()
+
     ms, launches = timed_steps(args.steps)
     # end to end through the public API: inputs come from pinned host memory every step and the
     # loss is read back every step
     # (the copy of step i+1's inputs is issued on a side stream before step i runs, as an input
-    # pipeline would; every copy and every loss read-back is inside the timed region)
+    # pipeline would; the loss of step i is copied to pinned host memory asynchronously and read
+    # after step i+1 has been queued, the last one after the loop, so the host keeps the device
+    # fed; every copy and every loss read-back is inside the timed region)
     copy_stream = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    step_done = [None, None]
+    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_val = None
 
     def fetch(i):
+        b = i % 2
         with torch.cuda.stream(copy_stream):
-            x = host_batches[i % 2].to("cuda", non_blocking=True)
+            if graphed[0] is not None:      # the captured steps read fixed device buffers
+                if step_done[b] is not None:
+                    copy_stream.wait_event(step_done[b])
+                x = dev_batches[b]
+                x.detach().copy_(host_batches[b], non_blocking=True)
+            else:
+                x = host_batches[b].to("cuda", non_blocking=True)
             ev = copy_stream.record_event()
         return x, ev
 
-    # the loss of step i is copied to pinned host memory asynchronously and read after step i+1
-    # has been queued (the last one after the loop), so the host keeps the device fed
-    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
-    loss_ev = [None, None]
-    loss_val = None
-
     def read_loss(i):
-        loss_ev[i % 2].synchronize()
-        return float(loss_host[i % 2][0])
+        step_done[i % 2].synchronize()
+        return float((graphed[0].host_losses[i % 2] if graphed[0] is not None else loss_host[i % 2])[0])
 
     barrier_sync(world)
     t0 = time.perf_counter()
@@ -227,10 +268,13 @@ def run_ours(args):
         x, ev = nxt
         if i + 1 < args.steps:
             nxt = fetch(i + 1)
-        torch.cuda.current_stream().wait_event(ev)
-        x.record_stream(torch.cuda.current_stream())
-        loss_host[i % 2].copy_(step(x).reshape(1), non_blocking=True)
-        loss_ev[i % 2] = torch.cuda.current_stream().record_event()
+        main.wait_event(ev)
+        if graphed[0] is not None:
+            graphed[0].replay(i)
+        else:
+            x.record_stream(main)
+            loss_host[i % 2].copy_(step(x).reshape(1), non_blocking=True)
+        step_done[i % 2] = main.record_event()
         if i > 0:
             loss_val = read_loss(i - 1)
     loss_val = read_loss(args.steps - 1)
@@ -288,9 +332,9 @@ def run_ours(args):
                    "global_batch": tokens, "seq_len": S, "parallelism": f"ep{world}", "token_padding": cfg.token_padding,
                    "num_sms": 32, "maxvio_target": args.maxvio, "maxvio": round(realised, 3),
                    "step": "router + dispatch + grouped GEMM fwd/bwd + combine + reduce_grad + SGD"
-                           + ("" if args.optimizer_after_backward else " (each projection's SGD is launched inside the backward "
-                              "pass, on a side stream, once its gradient is final)"),
-                   "l2": "inputs larger than L2 (multi-GB working set per step)"},
+                           + (" (each projection's SGD is launched inside the backward pass, on a side stream, once its "
+                              "gradient is final)" if args.optimizer_in_backward else ""),
+                   "l2": "inputs larger than L2 (multi-GB working set per step)", "launch": graph_note},
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": S * H * 2, "d2h_bytes_per_step": 4},

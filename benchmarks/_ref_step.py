@@ -14,6 +14,8 @@ import time
 import torch
 import torch.distributed as dist
 
+from benchmarks._loss import mean_square
+
 CFG = {"deepseek_v3": dict(H=7168, Hp=2048, K=8, epn=32, S=4096)}
 SWEEP = (0.0, 0.5, 1.0, 2.0, 3.0)
 
@@ -148,7 +150,7 @@ def run(args):
         x.requires_grad_(True)
         w, topk, tpe = route(x)
         y = MoE.apply(x, w, topk, tpe)
-        loss = (y.float() ** 2).mean()
+        loss = mean_square(y)
         loss.backward()
         with torch.no_grad():
             for n in shapes:

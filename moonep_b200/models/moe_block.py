@@ -13,6 +13,7 @@ benchmark ("MoE-layer step vs maxvio") can be run end to end through this packag
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -69,6 +70,8 @@ class MoEBlock:
             self.shared = [(torch.randn(cfg.H, 2 * hs, device=dev, generator=g) * 0.02).to(torch.bfloat16).requires_grad_(True),
                            (torch.randn(hs, cfg.H, device=dev, generator=g) * 0.02).to(torch.bfloat16).requires_grad_(True)]
         self.moe = ExpertParallelMoE(self.buf, self.pools)
+        # sgd_step() joins the last gradient reduction before it updates ``up``
+        self.moe.defer_last_reduction = os.environ.get("MOONEP_DEFER_LAST_REDUCTION", "1") != "0"
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier(group=group)
@@ -111,7 +114,8 @@ class MoEBlock:
 
     def sgd_step(self, lr: float):
         if self.moe.on_grad_ready is None:
-            for n in ("gate", "up", "down"):
+            for n in ("down", "gate", "up"):     # ``up`` last: its cross-rank reduction may still be running
+                self.moe.wait_grads(n)
                 gg.sgd_step(self.pools.local_weight(n), self.pools.local_grad(n), lr)
         else:
             assert lr == self._fused_lr, "the experts were already updated with another learning rate"

@@ -60,6 +60,10 @@ class ExpertParallelMoE:
         self._total_sms = torch.cuda.get_device_properties(dev).multi_processor_count
         self._comm_sms = min(g.num_sms & ~1, self._total_sms - 2)
         self.on_grad_ready = None       # callable(name) -> None, see backward()
+        self.grads_pending = None       # (projection, event) of a reduction still running after backward()
+        # opt-in: backward() may return while the reduction of ``up`` still runs on the comm stream;
+        # the caller then calls wait_grads() before it reads those gradients or uses the Buffer again
+        self.defer_last_reduction = False
         bf = dict(dtype=torch.bfloat16, device=dev)
         # activations are allocated once; shapes are static (no per-step allocator traffic)
         self._act = torch.zeros(g.NvS, self.Hp, **bf)
@@ -79,6 +83,7 @@ class ExpertParallelMoE:
 
     def forward(self, hidden_sh, route_weights_sk, topk_sk, tokens_per_expert, need_backward: bool = True):
         buf, g, epn = self.buf, self.geo, self.geo.epn
+        self.wait_grads()
         h_view, w_view, cu, plan = buf.dispatch(hidden_sh, route_weights_sk, topk_sk, tokens_per_expert,
                                                 zero_copy=True, router_weights_zero_copy=True)
         ev = None
@@ -176,12 +181,27 @@ class ExpertParallelMoE:
             main.wait_event(ev)       # also covers the combine, which precedes that launch on the comm stream
         else:
             gg.wgrad(ctx.x, dU, ctx.cu, dW_up, accumulate=acc, zero_empty_below=epn)
+        self.grads_pending = None
         if multi:
-            buf.reduce_grad_subset(ctx.plan, [pair("up")])
+            # the last reduction has nothing of the backward pass left to hide behind: with
+            # ``defer_last_reduction`` it is left running on the comm stream and ``wait_grads()`` (or
+            # ``wait_grads("up")``) joins it, so an optimizer can update ``down`` and ``gate`` meanwhile
+            ev_up = buf.reduce_grad_subset(ctx.plan, [pair("up")],
+                                           async_finish=ov and self.defer_last_reduction and self.on_grad_ready is None)
+            if ev_up is not None:
+                self.grads_pending = ("up", ev_up)
         if self.on_grad_ready is not None:
             self.on_grad_ready("up")
             main.wait_stream(self._opt)
         return grad_hidden, grad_w
+
+    def wait_grads(self, name: str | None = None) -> None:
+        """Make the current stream wait until the expert weight gradients written by the last
+        ``backward`` are final: all of them (``name=None``) or those of one projection.  Only the
+        reduction of ``up`` can still be in flight after ``backward`` returns."""
+        if self.grads_pending is not None and name in (None, self.grads_pending[0]):
+            torch.cuda.current_stream().wait_event(self.grads_pending[1])
+            self.grads_pending = None
 
 
 class _MoEFn(torch.autograd.Function):

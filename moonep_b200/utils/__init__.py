@@ -1,3 +1,4 @@
 from .clocks import ClockSampler
+from .graphs import GraphedSteps
 
-__all__ = ["ClockSampler"]
+__all__ = ["ClockSampler", "GraphedSteps"]

@@ -49,3 +49,57 @@ def test_smoke_step(cuda_device):
     from moonep_b200.models.moe_block import smoke_step
     loss = smoke_step()
     assert loss == loss
+
+
+def _train(blk, xs, lr, steps, graphed):
+    """``steps`` SGD steps on the inputs ``xs`` (used in turn); returns the losses."""
+    from moonep_b200.utils import GraphedSteps
+
+    def step(x):
+        x.requires_grad_(True)
+        loss = (blk.forward(x).float() ** 2).sum()        # a sum: the updates must be visible in bf16 weights
+        loss.backward()
+        blk.sgd_step(lr)
+        x.grad = None
+        return loss.detach()
+
+    losses = []
+    if graphed:
+        gs = GraphedSteps(step, xs)
+        for i in range(steps):
+            gs.replay(i)
+            torch.cuda.synchronize()
+            losses.append(float(gs.host_losses[i % len(xs)][0]))
+    else:
+        for i in range(steps):
+            losses.append(float(step(xs[i % len(xs)])))
+    torch.cuda.synchronize()
+    blk.buf.check()
+    return losses
+
+
+@pytest.mark.parametrize("optimizer_in_backward", [False, True])
+def test_captured_steps_match_eager_steps(optimizer_in_backward, cuda_device):
+    """A step captured as a CUDA graph and replayed gives the losses and weights of the same steps
+    launched from Python (planner epochs, barrier state and tile counters all live on the device),
+    with the optimizer after or inside the backward pass."""
+    from moonep_b200.models.moe_block import MoEBlock, MoEConfig
+    from moonep_b200.ops import grouped_gemm as gg
+    cfg = MoEConfig("t", H=256, Hp=256, K=2, epn=4, shared_experts=1, S=192)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    xs = [(torch.randn(cfg.S, cfg.H, device="cuda", generator=g) * 0.5).to(torch.bfloat16) for _ in range(2)]
+    out = []
+    for graphed in (False, True):
+        blk = MoEBlock(cfg, num_sms=4, seed=3)
+        if optimizer_in_backward:
+            blk.fuse_optimizer(1e-2)
+        _train(blk, [x.clone() for x in xs], 1e-2, 2, graphed=False)          # warm-up, eager in both runs
+        losses = _train(blk, [x.clone() for x in xs], 1e-2, 5, graphed=graphed)
+        gg.check_status()
+        out.append((losses, [blk.pools.local_weight(n).clone() for n in ("gate", "up", "down")]))
+        blk.destroy()
+    (l0, w0), (l1, w1) = out
+    assert all(abs(a - b) <= 1e-3 * abs(a) + 1e-6 for a, b in zip(l0, l1)), (l0, l1)
+    assert l0[0] != l0[2], "the weights must actually be trained (same input, two steps later)"
+    for a, b in zip(w0, w1):
+        assert torch.equal(a, b)
