@@ -372,8 +372,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) planning_kernel(MepCtxPack P,
 //   * EVERY CTA waits for all peers' epochs itself and then solves the plan redundantly into its
 //     own shared memory (the solve is a few microseconds and fully deterministic), so nothing has
 //     to be exchanged between the CTAs of a rank;
-//   * the count of same-expert entries in earlier blocks is obtained by scanning the top-k prefix
-//     directly instead of exchanging block histograms.
+//   * every CTA publishes the expert histogram of each of its 1024-entry blocks and raises that
+//     block's flag to the launch epoch; the count of same-expert entries in earlier blocks is a
+//     column sum over the earlier blocks' rows (no rescan of the top-k table).
 // send_cnt is double-buffered by epoch parity: this launch accumulates into half (epoch & 1) and
 // clears the other half for the next launch.
 __global__ void __launch_bounds__(kPlanThreads, 1) planning_fast_kernel(MepCtxPack P, PlanArgsPack A) {

@@ -60,10 +60,23 @@ def is_stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile what is out of date and link.  Safe to call from several processes at once (one
+    rank per GPU importing the package): the work is serialised with a file lock, the library is
+    linked under a temporary name and renamed into place, and a process that finds the library
+    fresh once it holds the lock does nothing."""
     if nvcc_path() is None:
         raise RuntimeError("nvcc not found; cannot build libmoonep_b200.so")
     LIBDIR.mkdir(parents=True, exist_ok=True)
     OBJDIR.mkdir(parents=True, exist_ok=True)
+    import fcntl
+    with open(LIBDIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not is_stale():
+            return LIB
+        return _build_locked(force, verbose)
+
+
+def _build_locked(force: bool, verbose: bool) -> Path:
     hdr_t = max(p.stat().st_mtime for p in headers())
     jobs, objs = [], []
     for src in sources():
@@ -75,11 +88,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         for out in ex.map(lambda j: _compile(j[0], j[1], verbose), jobs):
             if verbose and out:
                 print(out, file=sys.stderr)
-    if jobs or not LIB.exists():
-        cmd = [nvcc_path(), *ARCH, "-shared", "--cudart", "shared", "-o", str(LIB), *map(str, objs)]
+    if jobs or not LIB.exists() or is_stale():
+        tmp = LIB.with_suffix(".so.tmp")
+        cmd = [nvcc_path(), *ARCH, "-shared", "--cudart", "shared", "-o", str(tmp), *map(str, objs)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
     return LIB
 
 
