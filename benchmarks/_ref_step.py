@@ -224,6 +224,16 @@ def run(args):
             ev = copy_stream.record_event()
         return x, ev
 
+    # same protocol as the main arm: the loss of step i goes to pinned host memory asynchronously
+    # and is read after step i+1 has been queued (the last one after the loop)
+    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    done = [None, None]
+    lv = None
+
+    def read_loss(i):
+        done[i % 2].synchronize()
+        return float(loss_host[i % 2][0])
+
     sync()
     t0 = time.perf_counter()
     nxt = fetch(0)
@@ -233,7 +243,11 @@ def run(args):
             nxt = fetch(i + 1)
         torch.cuda.current_stream().wait_event(ev)
         x.record_stream(torch.cuda.current_stream())
-        lv = step(x).item()
+        loss_host[i % 2].copy_(step(x).reshape(1).float(), non_blocking=True)
+        done[i % 2] = torch.cuda.current_stream().record_event()
+        if i > 0:
+            lv = read_loss(i - 1)
+    lv = read_loss(args.steps - 1)
     sync()
     e2e_ms = mx((time.perf_counter() - t0) * 1e3 / args.steps)
     sweep = []

@@ -189,6 +189,51 @@ int mep_map_all(int dev, int world, int my_rank, void* local_chunk, const unsign
   return 0;
 }
 
+// Map ONE chunk that another process owns (single-owner tensors): import its shareable handle
+// (fd: consumed; fabric: 64 bytes) and map it read-write at a fresh address. The result is released
+// with mep_unmap_all like any other mapping.
+int mep_map_remote_one(int dev, int kind, size_t bytes, const unsigned char* shareable,
+                       void** mapping_out, unsigned long long* base_out) {
+  const DriverApi* d = driver(); if (!d) return -1;
+  MEP_REQUIRE(bytes > 0 && shareable != nullptr, "map_remote_one: empty chunk");
+  CUmemAllocationProp p = alloc_prop(dev, kind);
+  size_t gran = 0;
+  MEP_CU_CHECK(d->MemGetAllocationGranularity(&gran, &p, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
+  MEP_REQUIRE(bytes % gran == 0, "map_remote_one: %zu bytes is not a multiple of the granularity %zu", bytes, gran);
+  CUmemGenericAllocationHandle h;
+  if (kind == kHandleFabric) {
+    CUmemFabricHandle fh; memcpy(&fh, shareable, sizeof fh);
+    MEP_CU_CHECK(d->MemImportFromShareableHandle(&h, &fh, CU_MEM_HANDLE_TYPE_FABRIC));
+  } else {
+    int fd; memcpy(&fd, shareable, sizeof fd);
+    const CUresult ri = d->MemImportFromShareableHandle(&h, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+    close(fd);
+    MEP_CU_CHECK(ri);
+  }
+  Mapping* m = new Mapping{dev, 1, bytes, 0, std::vector<bool>(1, false)};
+  const char* what = "reserve";
+  CUresult r = d->MemAddressReserve(&m->base, bytes, gran, 0, 0);
+  if (r == CUDA_SUCCESS) {
+    r = d->MemMap(m->base, bytes, 0, h, 0); what = "map";
+    if (r == CUDA_SUCCESS) {
+      m->mapped[0] = true;
+      CUmemAccessDesc acc = {};
+      acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE; acc.location.id = dev; acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+      r = d->MemSetAccess(m->base, bytes, &acc, 1); what = "set_access";
+    }
+  }
+  d->MemRelease(h);          // the mapping keeps the allocation alive
+  if (r != CUDA_SUCCESS) {
+    if (m->mapped[0]) d->MemUnmap(m->base, bytes);
+    if (m->base) d->MemAddressFree(m->base, bytes);
+    delete m;
+    const char* s = nullptr; d->GetErrorString(r, &s);
+    return set_error("map_remote_one: %s failed: %s", what, s ? s : "?");
+  }
+  *mapping_out = m; *base_out = (unsigned long long)m->base;
+  return 0;
+}
+
 // Unmap every chunk and free the range. Caller must have synchronised the device.
 int mep_unmap_all(void* mapping) {
   Mapping* m = static_cast<Mapping*>(mapping);

@@ -35,6 +35,7 @@ from .parallel.symm import SymmetricHeap
 from .plan import MoonEPCommPlan
 
 logger = logging.getLogger(__name__)
+_NVTX = os.environ.get("MOONEP_NVTX", "0") == "1"
 
 PREFETCH_DTYPES = (torch.bfloat16, torch.int8, torch.uint8, torch.float16, torch.float32)
 
@@ -314,19 +315,26 @@ class Buffer(OpsMixin):
                     dedup_ratio=dc[1] / max(1, plan.N), padded_rows=int(zf))
 
     # ---- async plumbing
-    def _run(self, async_finish: bool, tensors, fn):
-        if not async_finish:
-            return fn(), None
-        main = torch.cuda.current_stream()
-        comm = self._comm_stream
-        for t in tensors:
-            if isinstance(t, torch.Tensor) and t.is_cuda:
-                t.record_stream(comm)
-        comm.wait_event(main.record_event())
-        with torch.cuda.stream(comm):
-            out = fn()
-            done = comm.record_event()
-        return out, done
+    def _run(self, async_finish: bool, tensors, fn, label: str = "moonep.op"):
+        nvtx = _NVTX
+        if nvtx:            # MOONEP_NVTX=1: one range per public op (visible in Nsight Systems timelines)
+            torch.cuda.nvtx.range_push(label + (".async" if async_finish else ""))
+        try:
+            if not async_finish:
+                return fn(), None
+            main = torch.cuda.current_stream()
+            comm = self._comm_stream
+            for t in tensors:
+                if isinstance(t, torch.Tensor) and t.is_cuda:
+                    t.record_stream(comm)
+            comm.wait_event(main.record_event())
+            with torch.cuda.stream(comm):
+                out = fn()
+                done = comm.record_event()
+            return out, done
+        finally:
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
 
     # ---- dispatch
     def dispatch(self, hidden_sh: torch.Tensor, route_weights_sk: torch.Tensor | None = None,
@@ -357,7 +365,7 @@ class Buffer(OpsMixin):
         tensors = [hidden_sh, route_weights_sk, topk_experts_sk, tokens_per_expert]
         if plan is not None:
             tensors += list(plan.tensors())
-        (h, w, cu, p), ev = self._run(async_finish, tensors, body)
+        (h, w, cu, p), ev = self._run(async_finish, tensors, body, "moonep.dispatch")
         if async_finish:
             for t in (h, w, cu, *p.tensors()):
                 if isinstance(t, torch.Tensor):
@@ -392,7 +400,7 @@ class Buffer(OpsMixin):
                                      if hasattr(torch, "float8_e8m0fnu") else PREFETCH_DTYPES, "prefetch_weight scales")
             pairs += list(zip(scales, spools))
         tensors = [plan.experts_to_copy] + [t for pr in pairs for t in pr]
-        _, ev = self._run(async_finish, tensors, lambda: self._prefetch_lists([plan], [pairs]))
+        _, ev = self._run(async_finish, tensors, lambda: self._prefetch_lists([plan], [pairs]), "moonep.prefetch_weight")
         return ev
 
     # ---- combine
@@ -410,7 +418,7 @@ class Buffer(OpsMixin):
             return outs[0], (outw[0] if outw is not None else None)
 
         tensors = [hidden_nvsh, route_weights_nvs] + (list(plan.tensors()) if isinstance(plan, MoonEPCommPlan) else [])
-        (o, w), ev = self._run(async_finish, tensors, body)
+        (o, w), ev = self._run(async_finish, tensors, body, "moonep.combine")
         if async_finish:
             for t in (o, w):
                 if isinstance(t, torch.Tensor):
@@ -434,7 +442,7 @@ class Buffer(OpsMixin):
         self._check_weight_pairs(locals_, pools, (torch.float32,), "reduce_grad")
         pairs = list(zip(locals_, pools))
         tensors = [plan.experts_to_copy] + [t for pr in pairs for t in pr]
-        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs]))
+        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs]), "moonep.reduce_grad")
         return ev
 
     def reduce_grad_subset(self, plan: MoonEPCommPlan, grads, async_finish: bool = False):
@@ -449,7 +457,7 @@ class Buffer(OpsMixin):
         assert 1 <= len(pairs) <= 3, "reduce_grad_subset takes one to three (local_grad, reduce_buffer) pairs"
         self._check_weight_pairs([l for l, _ in pairs], [p for _, p in pairs], (torch.float32,), "reduce_grad_subset")
         tensors = [plan.experts_to_copy] + [t for pr in pairs for t in pr]
-        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs]))
+        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs]), "moonep.reduce_grad")
         return ev
 
     # ---- teardown

@@ -39,6 +39,9 @@ class MoEContext:
     gu: torch.Tensor         # pre-activations [NvS, 2H']
 
 
+_DEFERRED: list = []       # layers whose last gradient reduction is still running (see wait_grads)
+
+
 class ExpertParallelMoE:
     def __init__(self, buffer: Buffer, pools: ExpertPools, overlap_prefetch: bool = True,
                  overlap_backward: bool | None = None):
@@ -83,7 +86,7 @@ class ExpertParallelMoE:
 
     def forward(self, hidden_sh, route_weights_sk, topk_sk, tokens_per_expert, need_backward: bool = True):
         buf, g, epn = self.buf, self.geo, self.geo.epn
-        self.wait_grads()
+        self._join_deferred()
         h_view, w_view, cu, plan = buf.dispatch(hidden_sh, route_weights_sk, topk_sk, tokens_per_expert,
                                                 zero_copy=True, router_weights_zero_copy=True)
         ev = None
@@ -149,6 +152,7 @@ class ExpertParallelMoE:
         projection ``name`` is final and its weights are no longer read (optimizer in backward)."""
         buf, g, epn, Hp = self.buf, self.geo, self.geo.epn, self.Hp
         acc, ov, multi = self.accumulate_grads, self.overlap_backward, self.geo.R > 1
+        self._join_deferred()
         main = torch.cuda.current_stream()
         pools = self.pools
         pair = lambda n: (pools.local_grad(n), pools.reduce_view(n))      # noqa: E731
@@ -190,6 +194,7 @@ class ExpertParallelMoE:
                                            async_finish=ov and self.defer_last_reduction and self.on_grad_ready is None)
             if ev_up is not None:
                 self.grads_pending = ("up", ev_up)
+                _DEFERRED.append(self)
         if self.on_grad_ready is not None:
             self.on_grad_ready("up")
             main.wait_stream(self._opt)
@@ -202,6 +207,17 @@ class ExpertParallelMoE:
         if self.grads_pending is not None and name in (None, self.grads_pending[0]):
             torch.cuda.current_stream().wait_event(self.grads_pending[1])
             self.grads_pending = None
+            if self in _DEFERRED:
+                _DEFERRED.remove(self)
+
+    @staticmethod
+    def _join_deferred() -> None:
+        """Before any layer queues new communication kernels, the current stream joins every
+        reduction that some layer left running.  Communication kernels wait for their peers while
+        they hold their SMs, so two of them from different Buffers must never be left to start in
+        different orders on different ranks; joining here keeps one global order."""
+        for layer in list(_DEFERRED):
+            layer.wait_grads()
 
 
 class _MoEFn(torch.autograd.Function):

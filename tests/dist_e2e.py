@@ -211,7 +211,37 @@ def run_scenario(buf, rank, R, dev, S, H, K, epn, pad, E, Hp):
     torch.cuda.synchronize()
     safe_check(buf)
     stage("repeat")
+    symmetric_tensor_factories(rank, R, dev)
     return pools
+
+
+def symmetric_tensor_factories(rank, R, dev):
+    """The three tensor factories (all-rank view, multicast alias, single owner): every rank writes
+    its own part, reads everybody else's and writes into the owner's memory."""
+    from moonep_b200.parallel import create_dist_tensor, create_single_owner_tensor
+    dt = create_dist_tensor((100, 48), torch.float32, multicast=True)
+    chk(dt.local.shape == (100, 48) and dt.all.shape[0] == R * dt.rows, "dist tensor shapes")
+    dt.local.fill_(float(rank + 1))
+    torch.cuda.synchronize()
+    dist.barrier()
+    for r in range(R):
+        chk(bool((dt.of_rank(r) == float(r + 1)).all()), f"dist tensor: chunk of rank {r} seen from rank {rank}")
+    dt.of_rank((rank + 1) % R)[0, :].fill_(-float(rank + 1))        # a store into a peer's chunk
+    torch.cuda.synchronize()
+    dist.barrier()
+    chk(bool((dt.local[0] == -float((rank - 1) % R + 1)).all()), "dist tensor: peer store landed")
+    owner = R - 1
+    so = create_single_owner_tensor((R, 64), torch.int32, owner=owner)
+    chk(bool((so.tensor == 0).all()), "single-owner tensor starts zeroed")
+    dist.barrier()
+    so.tensor[rank].fill_(rank + 7)
+    torch.cuda.synchronize()
+    dist.barrier()
+    want = (torch.arange(R, device=dev, dtype=torch.int32) + 7).unsqueeze(1).expand(R, 64)
+    chk(torch.equal(so.tensor, want), "single-owner tensor: every rank's row visible everywhere")
+    stage("symmetric tensor factories")
+    so.destroy()
+    dt.destroy()
 
 
 if __name__ == "__main__":

@@ -337,3 +337,17 @@ def test_prefetch_and_reduce_beyond_2gib_offsets(cuda_device):
     assert torch.equal(pool[0, 2].view(torch.int16), local[1][2].view(torch.int16))
     assert torch.equal(pool[1, 1].view(torch.int16), local[0][2].view(torch.int16))
     assert not pool[0, 0].any() and not pool[1, 2].any()
+
+
+def test_tensor_factories_single_process(cuda_device):
+    """Without a process group the symmetric tensor factories hand out ordinary device memory
+    with the same interface (the multi-process path runs in tests/dist_e2e.py)."""
+    from moonep_b200.parallel import create_dist_tensor, create_single_owner_tensor
+    dt = create_dist_tensor((10, 6), torch.float32)
+    assert dt.all.shape == (10, 6) and dt.multicast is None and dt.rows == 10
+    dt.local.fill_(2.0)
+    assert bool((dt.of_rank(0) == 2.0).all())
+    so = create_single_owner_tensor((4, 4), torch.int32)
+    assert so.owner == 0 and int(so.tensor.sum()) == 0
+    so.destroy()
+    dt.destroy()
