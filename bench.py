@@ -219,6 +219,8 @@ def run_ours(args):
             ok, graph_note = 1, "whole step replayed from a captured CUDA graph"
         except Exception as e:      # noqa: BLE001
             gs, ok, graph_note = None, 0, f"capture failed, launched from Python: {type(e).__name__}: {str(e)[:160]}"
+            type(blk.moe).forget_deferred()
+            torch.cuda.synchronize()
         if world > 1:
             t = torch.tensor([ok], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MIN)

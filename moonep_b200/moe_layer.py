@@ -211,6 +211,14 @@ class ExpertParallelMoE:
                 _DEFERRED.remove(self)
 
     @staticmethod
+    def forget_deferred() -> None:
+        """Drop the record of reductions left running (their events belong to a CUDA-graph capture
+        that was abandoned, so they can never be waited on); call after a failed capture."""
+        for layer in list(_DEFERRED):
+            layer.grads_pending = None
+        _DEFERRED.clear()
+
+    @staticmethod
     def _join_deferred() -> None:
         """Before any layer queues new communication kernels, the current stream joins every
         reduction that some layer left running.  Communication kernels wait for their peers while
