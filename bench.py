@@ -336,7 +336,9 @@ def run_ours(args):
                    "step": "router + dispatch + grouped GEMM fwd/bwd + combine + reduce_grad + SGD"
                            + (" (each projection's SGD is launched inside the backward pass, on a side stream, once its "
                               "gradient is final)" if args.optimizer_in_backward else ""),
-                   "l2": "inputs larger than L2 (multi-GB working set per step)", "launch": graph_note},
+                   "l2": "inputs larger than L2 (multi-GB working set per step)", "launch": graph_note,
+                   "combine": ("pushed by the down GEMM's epilogue into the source ranks' memory, then a local sum"
+                               if blk.buf.geo.off_push else "pulled from the peers' shards after the down GEMM")},
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": S * H * 2, "d2h_bytes_per_step": 4},

@@ -186,6 +186,53 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, 
   }
 }
 
+// ------------------------------------------------------------------ push-combine: local reduction
+// Counterpart of the combine for the "push" path: the down-projection GEMM's epilogue has already
+// stored every row into its source rank's receive area [S*K, H] (row s*K + k = contribution of
+// the token's k-th expert), so once all ranks have finished (entry barrier) the combine is a purely
+// local sum over k (ascending, fp32) -- no peer reads, no duplicate pre-reduction.
+struct PushReduceArgs {
+  __nv_bfloat16* out;       // [S, H]
+  float* out_weights;       // [S, K] or null: copy of the pushed per-slot values
+  int64_t push_off;         // byte offsets of the receive areas inside this rank's chunk
+  int64_t pushw_off;
+};
+struct PushReduceArgsPack { PushReduceArgs a[MEP_MAX_VRANKS]; };
+
+__global__ void __launch_bounds__(256) push_reduce_kernel(MepCtxPack P, PushReduceArgsPack A) {
+  const MepRankCtx c = *P.ctx[blockIdx.y];
+  const PushReduceArgs& a = A.a[blockIdx.y];
+  const int nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+  const int K = c.K, S = c.S;
+  const size_t row_bytes = (size_t)c.H * 2;
+  const int nvec = (int)(row_bytes >> 4);
+  if (tid == 0) trace_mark(c, MEP_K_COMBINE, 11);
+  if (!cross_rank_barrier(c, nb, 2, MEP_K_COMBINE, 40)) return;
+  if (tid == 0) trace_mark(c, MEP_K_COMBINE, 12);
+  const char* recv = peer_ptr(c, c.rank, (size_t)a.push_off);
+  for (int s = blockIdx.x * nwarp + warp; s < S; s += nb * nwarp) {
+    const char* base = recv + (size_t)s * K * row_bytes;
+    char* orow = (char*)a.out + (size_t)s * row_bytes;
+    for (int v = lane; v < nvec; v += 32) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int k0 = 0; k0 < K; k0 += 8) {        // eight independent 16-byte loads in flight per lane
+        int4 x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (k0 + j < K) x[j] = __ldcg(reinterpret_cast<const int4*>(base + (size_t)(k0 + j) * row_bytes + (size_t)v * 16));
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (k0 + j < K) acc_bf16x8(acc, x[j]);
+      }
+      st_na_v4(orow + (size_t)v * 16, pack_bf16x8(acc));
+    }
+  }
+  if (a.out_weights) {
+    const float* w = (const float*)peer_ptr(c, c.rank, (size_t)a.pushw_off);
+    for (int i = blockIdx.x * blockDim.x + tid; i < S * K; i += nb * blockDim.x) a.out_weights[i] = __ldcg(w + i);
+  }
+}
+
 // ------------------------------------------------------------------ stand-alone rank sync
 __global__ void rank_sync_kernel(MepCtxPack P) {
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
@@ -222,6 +269,14 @@ extern "C" int mep_launch_combine(int nv, const MepRankCtx* const* ctxs, const m
   const size_t smem = (size_t)mep::kCombWarps * mep::kCombSlots * 32 * 16;
   return mep::launch_cooperative(mep::combine_kernel, dim3(num_sms, nv), dim3(mep::kCombThreads), smem,
                                  stream, false, P, A);
+}
+
+extern "C" int mep_launch_push_reduce(int nv, const MepRankCtx* const* ctxs, const mep::PushReduceArgs* args,
+                                      int num_blocks, cudaStream_t stream) {
+  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "push_reduce: nv=%d out of range", nv);
+  MepCtxPack P = {}; mep::PushReduceArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  return mep::launch_cooperative(mep::push_reduce_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, false, P, A);
 }
 
 extern "C" int mep_launch_rank_sync(int nv, const MepRankCtx* const* ctxs, cudaStream_t stream) {

@@ -24,6 +24,9 @@ struct DispatchArgs {
   int32_t fresh;                 // non-zero: publish duplicate-table counts to the peers. 1 / 2: the planner used
                                  // send_cnt half 0 / 1; 3: the half the fast planner's device-side epoch names
   int32_t entry_barrier;         // 1: cross-rank barrier before the first remote write
+  int64_t srcinfo_off;           // 0, or byte offset (inside a rank's chunk) of the provenance table [NvS] int32: the
+                                 // sender writes src_rank * S*K + s*K + k for each of a token's K slots and -1 for
+                                 // padding rows, so that a GEMM epilogue can send a row straight back to its source
 };
 struct DispatchArgsPack { DispatchArgs a[MEP_MAX_VRANKS]; };
 
@@ -93,6 +96,7 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       char* row = hid + (size_t)prow * row_bytes;
       for (int v = lane; v < vec_per_row; v += 32) st_v4(row + (size_t)v * 16, z);
       if (lane == 0 && a.weights) wts[prow] = 0.f;
+      if (lane == 0 && a.srcinfo_off) ((int*)peer_ptr(c, c.rank, (size_t)a.srcinfo_off))[prow] = -1;
     }
   };
 
@@ -164,6 +168,11 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
         const int raw = dval >= 0 ? dval : -dval - 1;
         const int d = raw / NvS, loff = raw - d * NvS;
         ((float*)peer_ptr(c, d, c.off_weights))[loff] = w;
+      }
+      if (lane < K && a.srcinfo_off) {
+        const int raw = dval >= 0 ? dval : -dval - 1;
+        const int d = raw / NvS, loff = raw - d * NvS;
+        ((int*)peer_ptr(c, d, (size_t)a.srcinfo_off))[loff] = c.rank * (S * K) + s * K + lane;
       }
       for (int k = 0; k < K; ++k) {
         const int dv = __shfl_sync(0xffffffffu, dval, k);

@@ -26,6 +26,18 @@ struct GemmArgs {
   uint64_t budget_ns;
   uint32_t* sched;             // [2] zero-initialised ticket counter of the dynamic tile scheduler, or null for
                                // the static strided tile order
+  // DOWN / DGRAD / DGRAD_GU, optional "push" epilogue: row r of the output is not stored to `out` but sent
+  // to the rank it came from: push_info[r] = src_rank * push_rows + index (or < 0 for a padding row) and the
+  // row lands at push_base + src_rank * push_stride + index * N * 2 (row `index` of that rank's [push_rows, N]
+  // bf16 receive area inside the symmetric heap). push_wsrc[r], if given, goes to the float at
+  // push_wbase + src_rank * push_stride + index * 4.
+  const int32_t* push_info;
+  unsigned char* push_base;
+  unsigned char* push_wbase;
+  const float* push_wsrc;
+  uint64_t push_stride;
+  int32_t push_rows;
+  int32_t push_ranks;
   int32_t sched_ctas;          // dynamic order: CTAs over ALL launches that draw from `sched` (several launches of
                                // one GEMM may share a counter); 0 = just this launch
 };

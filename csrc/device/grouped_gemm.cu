@@ -298,6 +298,52 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             bulk_commit();
           }
         }
+      } else if (args.push_info) {
+        // "push" epilogue: every output row goes straight to the rank its token came from (peer
+        // memory, plain 16-byte stores; 8 lanes cover one 128-byte line of a row). The per-row
+        // destinations sit in the second staging buffer of the warp, the first one transposes.
+        const size_t row = (size_t)ti.row0 + r_in_tile;
+        const float sc = (MODE == GEMM_DOWN && args.row_scale) ? args.row_scale[row] : 1.f;
+        const int info = args.push_info[row];
+        unsigned char* dst = nullptr;
+        if (info >= 0) {
+          const int src = info / args.push_rows, idx = info - src * args.push_rows;
+          if (src < args.push_ranks) {
+            dst = args.push_base + (size_t)src * args.push_stride + ((size_t)idx * args.N + ti.n0) * 2;
+            if (args.push_wsrc && ti.n0 == 0)
+              *reinterpret_cast<float*>(args.push_wbase + (size_t)src * args.push_stride + (size_t)idx * 4) = args.push_wsrc[row];
+          } else if (atomicCAS(&args.status[0], 0, MEP_ERR_BOUNDS) == 0) { args.status[1] = 8; args.status[2] = blockIdx.x; args.status[3] = (int)row; }
+        }
+        const uint32_t buf = stg, ptrs = stg + kSlabBytes;
+        __syncwarp();
+        asm volatile("st.shared.b64 [%0], %1;" :: "r"(ptrs + lane * 8), "l"(dst) : "memory");
+        __syncwarp();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[64];
+          tc::tmem_ld32(taddr + c * 64, r);
+          tc::tmem_ld32(taddr + c * 64 + 32, r + 32);
+          tc::tmem_ld_wait();
+          uint32_t o[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * sc, __uint_as_float(r[2 * j + 1]) * sc);
+            o[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            tc::st_shared_v4(buf + lane * 128 + ((j ^ (lane & 7)) << 4), o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3), j = lane & 7;
+            unsigned long long dp;
+            asm volatile("ld.shared.b64 %0, [%1];" : "=l"(dp) : "r"(ptrs + rr * 8) : "memory");
+            const int4 v = tc::ld_shared_v4(buf + rr * 128 + ((j ^ (rr & 7)) << 4));
+            if (dp) st_v4(reinterpret_cast<unsigned char*>(dp) + c * 128 + j * 16, v);
+          }
+          __syncwarp();
+        }
       } else {
         const size_t row = (size_t)ti.row0 + r_in_tile;
         const float sc = (MODE == GEMM_DOWN && args.row_scale) ? args.row_scale[row] : 1.f;

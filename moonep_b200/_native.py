@@ -50,7 +50,11 @@ class PlanArgs(C.Structure):
 
 class DispatchArgs(C.Structure):
     _fields_ = [("hidden", C.c_void_p), ("weights", C.c_void_p), ("dst", C.c_void_p), ("zero_fill", C.c_void_p),
-                ("fresh", C.c_int32), ("entry_barrier", C.c_int32)]
+                ("fresh", C.c_int32), ("entry_barrier", C.c_int32), ("srcinfo_off", C.c_int64)]
+
+
+class PushReduceArgs(C.Structure):
+    _fields_ = [("out", C.c_void_p), ("out_weights", C.c_void_p), ("push_off", C.c_int64), ("pushw_off", C.c_int64)]
 
 
 class DupFinalizeArgs(C.Structure):

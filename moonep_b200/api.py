@@ -181,6 +181,22 @@ class OpsMixin:
         return outs, outw
 
     # ---- prefetch / reduce
+    def _push_reduce_lists(self, want_weights: bool):
+        st, g = self._states, self.geo
+        dev = st[0].hidden_local.device
+        outs = [torch.empty(g.S, g.H, dtype=torch.bfloat16, device=dev) for _ in st]
+        out_ws = [torch.empty(g.S, g.K, dtype=torch.float32, device=dev) for _ in st] if want_weights else None
+        engine.launch_push_reduce(st, outs, out_ws, self._num_sms_dedup)
+        return outs, out_ws
+
+    def _push_target(self, i: int = 0):
+        """``PushTarget`` of rank-state ``i`` for the grouped GEMM's push epilogue."""
+        from .ops.grouped_gemm import PushTarget
+        st, g = self._states[i], self.geo
+        assert g.off_push, "create the Buffer with push_combine=True"
+        heap = st.heap
+        return PushTarget(st.srcinfo_local, heap.base + g.off_push, heap.base + g.off_pushw, heap.chunk_bytes, g.N, g.R)
+
     def _check_weight_pairs(self, locals_, pools, dtypes, what):
         g = self.geo
         for local, pool in zip(locals_, pools):
@@ -210,7 +226,8 @@ class Buffer(OpsMixin):
 
     def __init__(self, S: int, H: int, K: int, E: int, num_ep_ranks: int, num_sms: int | None = None,
                  token_padding: int = 128, group=None, comm_stream_priority: int = -1,
-                 enable_pdl: bool = True, explicitly_destroy: bool = False, multicast: bool | None = None):
+                 enable_pdl: bool = True, explicitly_destroy: bool = False, multicast: bool | None = None,
+                 push_combine: bool = False):
         assert isinstance(comm_stream_priority, int), \
             f"comm_stream_priority must be an int, got {type(comm_stream_priority).__name__}"
         assert isinstance(enable_pdl, bool), f"enable_pdl must be a bool, got {type(enable_pdl).__name__}"
@@ -235,7 +252,7 @@ class Buffer(OpsMixin):
             rank, world = 0, 1
         assert R == world, f"num_ep_ranks ({R}) must equal group world size ({world})"
         self._num_sms_dedup = num_sms_dedup_from_env(max_sms)
-        self.geo = Geometry.make(S, H, K, E, R, token_padding, num_sms)
+        self.geo = Geometry.make(S, H, K, E, R, token_padding, num_sms, push_combine=push_combine)
         device = torch.device("cuda", torch.cuda.current_device())
         if world > 1:
             self._heap = SymmetricHeap.create(self.geo.chunk_bytes, group=group, multicast=multicast)
@@ -424,6 +441,28 @@ class Buffer(OpsMixin):
                 if isinstance(t, torch.Tensor):
                     t.record_stream(torch.cuda.current_stream())
         return o, w, ev
+
+    # ---- push-combine (extension: the reference always pulls)
+    def push_target(self):
+        """Argument for ``ops.grouped_gemm.down(..., push=...)`` / ``dgrad_gate_up(..., push=...)``:
+        with it the GEMM's epilogue stores every output row straight into the receive area of the
+        rank the token came from (peer memory), using the provenance table the last ``dispatch``
+        of this Buffer wrote.  Needs ``Buffer(..., push_combine=True)``."""
+        self._st()
+        return self._push_target(0)
+
+    def combine_pushed(self, want_weights: bool = False, async_finish: bool = False):
+        """Finish a combine whose rows were pushed by a GEMM epilogue: cross-rank barrier, then the
+        local sum over each token's K received rows (ascending k, fp32).  Returns
+        ``(hidden_sh [S, H], per-slot scalars [S, K] | None, event | None)``."""
+        self._st()
+        (o, w), ev = self._run(async_finish, [], lambda: self._push_reduce_lists(want_weights), "moonep.combine_pushed")
+        out, ow = o[0], (w[0] if w is not None else None)
+        if async_finish:
+            for t in (out, ow):
+                if isinstance(t, torch.Tensor):
+                    t.record_stream(torch.cuda.current_stream())
+        return out, ow, ev
 
     # ---- reduce_grad
     def reduce_grad(self, plan: MoonEPCommPlan | None = None, async_finish: bool = False, *,

@@ -15,7 +15,7 @@ from dataclasses import dataclass, field
 import torch
 
 from . import _native
-from ._native import (MepRankCtx, PlanArgs, DispatchArgs, DupFinalizeArgs, DupArgs, CombineArgs,
+from ._native import (MepRankCtx, PlanArgs, DispatchArgs, DupFinalizeArgs, DupArgs, CombineArgs, PushReduceArgs,
                       PrefetchArgs, GradReduceArgs, ptr)
 from .geometry import Geometry
 from .plan import MoonEPCommPlan
@@ -56,6 +56,7 @@ class RankState:
     scratch: dict = field(default_factory=dict)
     hidden_local: torch.Tensor = None     # [NvS, H] bf16 view of this rank's shard
     weights_local: torch.Tensor = None    # [NvS] fp32 view
+    srcinfo_local: torch.Tensor = None    # [NvS] int32 provenance table (push-combine Buffers only)
     status: torch.Tensor = None           # int32[8] device
     plan_fast: bool = False
 
@@ -111,6 +112,7 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     st.plan_fast = bool(_native.load().mep_planning_is_fast(E, R))
     st.hidden_local = heap.view(rank, geo.off_hidden, (geo.NvS, geo.H), torch.bfloat16)
     st.weights_local = heap.view(rank, geo.off_weights, (geo.NvS,), torch.float32)
+    st.srcinfo_local = heap.view(rank, geo.off_srcinfo, (geo.NvS,), torch.int32) if geo.off_srcinfo else None
     return st
 
 
@@ -178,12 +180,13 @@ def launch_planning(states, topk_list, tpe_list, plans, cu_list):
 def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry_barrier: bool):
     lib = _native.load()
     n = len(states)
+    g0 = states[0].geo
     args = (DispatchArgs * n)()
     for i in range(n):
         w = weights_list[i] if weights_list is not None else None
         fresh_code = 3 if states[i].plan_fast else 1      # which send_cnt half the planner used (3: device epoch)
         args[i] = DispatchArgs(ptr(hidden_list[i]), ptr(w), ptr(plans[i].dst), ptr(plans[i].zero_fill_ranges),
-                               fresh_code if fresh else 0, 1 if entry_barrier else 0)
+                               fresh_code if fresh else 0, 1 if entry_barrier else 0, g0.off_srcinfo)
     g = states[0].geo
     _native.check(lib.mep_launch_dispatch(n, _pack(states), args, g.num_sms, g.H, g.epn, _native.cur_stream()), "dispatch")
 
@@ -280,6 +283,19 @@ def launch_grad_reduce(states, etc_list, tensor_pairs_list):
         args[i] = a
     g = states[0].geo
     _native.check(lib.mep_launch_grad_reduce(n, _pack(states), args, g.num_sms, g.R, g.epn, _native.cur_stream()), "grad_reduce")
+
+
+def launch_push_reduce(states, outs, out_ws, num_blocks):
+    """Entry barrier + local sum over k of the rows the GEMM epilogues pushed into each rank's
+    receive area (push-combine)."""
+    lib = _native.load()
+    n = len(states)
+    args = (PushReduceArgs * n)()
+    g = states[0].geo
+    assert g.off_push, "this Buffer was created without the push-combine regions"
+    for i in range(n):
+        args[i] = PushReduceArgs(ptr(outs[i]), ptr(out_ws[i]) if out_ws is not None else None, g.off_push, g.off_pushw)
+    _native.check(lib.mep_launch_push_reduce(n, _pack(states), args, num_blocks, _native.cur_stream()), "push_reduce")
 
 
 def launch_wait_probe(st: RankState, flag: torch.Tensor, expected: int):

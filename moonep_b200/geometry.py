@@ -49,12 +49,15 @@ class Geometry:
     off_dupgroups: int = 0
     off_duploffs: int = 0
     off_ready: int = 0
+    off_srcinfo: int = 0      # push-combine only (0 = not allocated): provenance table [NvS] int32,
+    off_push: int = 0         # receive area [S*K, H] bf16,
+    off_pushw: int = 0        # per-slot scalar receive area [S*K] fp32
     dup_group_cap: int = 0    # staging capacity per source rank (groups)
     dup_loff_cap: int = 0     # staging capacity per source rank (duplicate offsets)
     chunk_bytes: int = 0      # before granularity padding
 
     @staticmethod
-    def make(S, H, K, E, R, token_padding=128, num_sms=32) -> "Geometry":
+    def make(S, H, K, E, R, token_padding=128, num_sms=32, push_combine=False) -> "Geometry":
         for name, v in (("S", S), ("H", H), ("K", K), ("E", E), ("num_ep_ranks", R)):
             if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
                 raise ValueError(f"{name} must be a positive int, got {v!r}")
@@ -93,7 +96,13 @@ class Geometry:
         o_dupgroups = take(R * gcap * 3 * 4)
         o_duploffs = take(R * lcap * 4)
         o_ready = take(4 * (2 * epn + 8))
+        o_srcinfo = o_push = o_pushw = 0
+        if push_combine:
+            # the expert GEMM's epilogue sends every output row back to its source rank
+            o_srcinfo = take(NvS * 4)
+            o_push = take(N * H * 2)
+            o_pushw = take(N * 4)
         chunk = align_up(off, 1024)
         return Geometry(S, H, K, E, R, token_padding, num_sms, epn, N, NvS, vb, nvb,
                         o_hidden, o_weights, o_tpe, o_bar, o_dupcnt, o_dupgroups,
-                        o_duploffs, o_ready, gcap, lcap, chunk)
+                        o_duploffs, o_ready, o_srcinfo, o_push, o_pushw, gcap, lcap, chunk)

@@ -53,7 +53,11 @@ class MoEBlock:
         self.cfg, self.world, self.rank = cfg, world, rank
         dev = torch.device("cuda", torch.cuda.current_device())
         self.E = cfg.epn * world
-        self.buf = Buffer(cfg.S, cfg.H, cfg.K, self.E, world, num_sms=num_sms, token_padding=cfg.token_padding, group=group)
+        # the down GEMM's epilogue sends its rows to their source ranks itself; costs a [S*K, H]
+        # receive area per rank (MOONEP_PUSH_COMBINE=0: plain stores, then the combine pulls)
+        push = os.environ.get("MOONEP_PUSH_COMBINE", "1") != "0"
+        self.buf = Buffer(cfg.S, cfg.H, cfg.K, self.E, world, num_sms=num_sms, token_padding=cfg.token_padding, group=group,
+                          push_combine=push)
         self.pools = ExpertPools(cfg.epn, (cfg.H, cfg.Hp), (cfg.H, cfg.Hp), (cfg.Hp, cfg.H), group=group, with_grads=True)
         g = torch.Generator(device=dev).manual_seed(seed * 7919 + rank)
         for n in ("gate", "up", "down"):

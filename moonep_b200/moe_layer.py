@@ -111,8 +111,14 @@ class ExpertParallelMoE:
             gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w)
         if stashed is not None:
             torch.cuda.current_stream().wait_event(stashed)
-        gg.down(self._act, Wd, cu, buf.hidden_nvsh_buffer_view)
-        out, _, _ = buf.combine(plan=plan, hidden_nvsh=buf.hidden_nvsh_buffer_view, zero_copy=True)
+        if g.off_push:
+            # push-combine: the down GEMM's epilogue sends every row to its source rank while the
+            # GEMM is still running; what is left of the combine is a barrier and a local sum
+            gg.down(self._act, Wd, cu, buf.hidden_nvsh_buffer_view, push=buf.push_target())
+            out, _, _ = buf.combine_pushed()
+        else:
+            gg.down(self._act, Wd, cu, buf.hidden_nvsh_buffer_view)
+            out, _, _ = buf.combine(plan=plan, hidden_nvsh=buf.hidden_nvsh_buffer_view, zero_copy=True)
         ctx = MoEContext(plan, cu, self._x, self._w, self._act, self._gu) if need_backward else None
         return out, ctx
 

@@ -27,7 +27,18 @@ class GemmArgs(C.Structure):
                 ("g_begin", C.c_int32), ("g_end", C.c_int32), ("zero_empty_below", C.c_int32), ("diag", C.c_int32),
                 ("out", C.c_void_p), ("out2", C.c_void_p), ("row_scale", C.c_void_p), ("ldo", C.c_int64),
                 ("status", C.c_void_p), ("budget_ns", C.c_uint64), ("sched", C.c_void_p),
-                ("sched_ctas", C.c_int32)]
+                ("push_info", C.c_void_p), ("push_base", C.c_void_p), ("push_wbase", C.c_void_p),
+                ("push_wsrc", C.c_void_p), ("push_stride", C.c_uint64), ("push_rows", C.c_int32),
+                ("push_ranks", C.c_int32), ("sched_ctas", C.c_int32)]
+
+
+class PushTarget:
+    """Where a "push" epilogue sends its rows (see ``Buffer.push_target``): ``info[r]`` names the
+    source rank and receive row of output row ``r``; ``base`` / ``wbase`` are the addresses of rank
+    0's receive areas, ``stride`` the distance to the next rank's, ``rows`` = S*K."""
+
+    def __init__(self, info, base, wbase, stride, rows, ranks):
+        self.info, self.base, self.wbase, self.stride, self.rows, self.ranks = info, base, wbase, stride, rows, ranks
 
 
 def _dev_index(device) -> int:
@@ -98,7 +109,7 @@ def check_status(device="cuda") -> None:
 
 def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=None, row_scale=None, ldo=0,
             accumulate=False, zero_empty_below=0, a_cols=None, b_rows=None, b_cols=None, b_ld=None, groups=None, num_ctas=None,
-            dynamic=False, ticket=None):
+            dynamic=False, ticket=None, push=None, push_w=None):
     lib = _native.load()
     assert a.dtype == torch.bfloat16 and b0.dtype == torch.bfloat16
     assert cu.dtype == torch.int32 and cu.is_contiguous()
@@ -120,11 +131,18 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
         args.sched, args.sched_ctas = ticket.ptr, ticket.total_ctas
     else:
         args.sched = _sched(a.device, dynamic)
+    if push is not None:
+        assert mode in (DOWN, DGRAD, DGRAD_GU) and push.info.dtype == torch.int32 and push.info.numel() >= a.shape[0]
+        args.push_info, args.push_base, args.push_stride = push.info.data_ptr(), push.base, push.stride
+        args.push_rows, args.push_ranks = push.rows, push.ranks
+        if push_w is not None:
+            assert push_w.dtype == torch.float32 and push_w.numel() >= a.shape[0]
+            args.push_wsrc, args.push_wbase = push_w.data_ptr(), push.wbase
     a_rows = a.shape[0]
     a_ld = a.stride(0)
     a_cols = a.shape[1] if a_cols is None else a_cols
     fn = lib.mep_grouped_gemm
-    if mode != WGRAD and os.environ.get("MOONEP_GEMM_2CTA", "0") == "1":
+    if mode != WGRAD and push is None and os.environ.get("MOONEP_GEMM_2CTA", "0") == "1":
         fn = lib.mep_grouped_gemm_2cta      # CTA-pair kernels (tcgen05 cta_group::2), 256-token tiles
     rc = fn(mode, C.c_void_p(a.data_ptr()), C.c_int64(a_rows), C.c_int64(a_cols), C.c_int64(a_ld),
                               C.c_void_p(b0.data_ptr()), C.c_void_p(_native.ptr(b1)), C.c_int64(b_rows),
@@ -148,13 +166,14 @@ def gate_up(x, wg, wu, cu, act_out, gu_out=None, row_scale=None, groups=None, nu
             ldo=act_out.stride(0), b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
 
 
-def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None):
-    """``out[r] = row_scale[r] * (act[r] Wd[g])`` with ``Wd [G, inner, hidden]``."""
+def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None, push=None):
+    """``out[r] = row_scale[r] * (act[r] Wd[g])`` with ``Wd [G, inner, hidden]``.  With ``push`` (a
+    ``PushTarget``) the rows are not written to ``out`` but sent to the ranks their tokens came from."""
     G, K, N = wd.shape
     assert act.shape[1] == K and N % 256 == 0 and K % 64 == 0
     rows, cols = _w2d(wd)
     _launch(DOWN, act, wd, None, cu, N=N, K=K, b_group_rows=K, out=out, row_scale=row_scale, ldo=out.stride(0),
-            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket, push=push)
 
 
 def dgrad(dy, w, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None):
@@ -166,13 +185,15 @@ def dgrad(dy, w, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None
             b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
 
 
-def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None):
-    """``out[r] = dG[r] Wg[g]^T + dU[r] Wu[g]^T`` with ``dgu = [dG | dU]`` (``[NvS, 2*inner]``)."""
+def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None, push=None, push_w=None):
+    """``out[r] = dG[r] Wg[g]^T + dU[r] Wu[g]^T`` with ``dgu = [dG | dU]`` (``[NvS, 2*inner]``).  With
+    ``push`` the rows (and ``push_w[r]``, e.g. the route-weight grads) go to their source ranks."""
     G, N, Kh = wg.shape
     assert dgu.shape[1] == 2 * Kh and N % 256 == 0 and Kh % 64 == 0
     rows, cols = _w2d(wg)
     _launch(DGRAD_GU, dgu, wg, wu, cu, N=N, K=2 * Kh, b_group_rows=N, out=out, ldo=out.stride(0),
-            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket,
+            push=push, push_w=push_w)
 
 
 def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num_ctas=None, dynamic=False, ticket=None):

@@ -18,9 +18,9 @@ from ..parallel.symm import SymmetricHeap
 
 class LocalCluster(OpsMixin):
     def __init__(self, S, H, K, E, R, num_sms=4, token_padding=128, device="cuda:0", num_sms_dedup=8,
-                 budget_ms: float | None = None):
+                 budget_ms: float | None = None, push_combine: bool = False):
         assert 1 <= R <= MAX_VRANKS, f"LocalCluster hosts at most {MAX_VRANKS} ranks"
-        self.geo = Geometry.make(S, H, K, E, R, token_padding, num_sms)
+        self.geo = Geometry.make(S, H, K, E, R, token_padding, num_sms, push_combine=push_combine)
         self.device = torch.device(device)
         self.heap = SymmetricHeap.local(R, self.geo.chunk_bytes, self.device)
         bn = None if budget_ms is None else int(budget_ms * 1e6)
@@ -37,6 +37,12 @@ class LocalCluster(OpsMixin):
                 router_weights_zero_copy=False):
         return self._combine_lists(plans, hidden_nvsh, weights_nvs, inter_rank_sync=inter_rank_sync,
                                    zero_copy=zero_copy, w_zero_copy=router_weights_zero_copy)
+
+    def push_target(self, rank: int):
+        return self._push_target(rank)
+
+    def combine_pushed(self, want_weights: bool = False):
+        return self._push_reduce_lists(want_weights)
 
     def prefetch(self, plans, pairs_list):
         self._prefetch_lists(plans, pairs_list)

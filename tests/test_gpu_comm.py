@@ -351,3 +351,39 @@ def test_tensor_factories_single_process(cuda_device):
     assert so.owner == 0 and int(so.tensor.sum()) == 0
     so.destroy()
     dt.destroy()
+
+
+@pytest.mark.parametrize("R", [1, 4])
+def test_push_combine_matches_sum_of_rows(R, cuda_device):
+    """Push-combine on emulated ranks: dispatch writes the provenance table, the grouped GEMM
+    (identity weights, so its output rows are the dispatched rows) stores every row into its source
+    rank's receive area, and the local reduction sums each token's K rows.  The K rows of a token
+    are copies of the token, so the exact result is K * token; it must also equal the pull path."""
+    from moonep_b200 import routing
+    from moonep_b200.ops import grouped_gemm as gg
+    from moonep_b200.sim.local_cluster import LocalCluster
+    dev = cuda_device
+    S, H, K, epn, pad = 96, 256, 4, 4, 128
+    E = R * epn
+    cl = LocalCluster(S, H, K, E, R, num_sms=4, token_padding=pad, push_combine=True)
+    g = torch.Generator().manual_seed(11)
+    hidden = [(torch.randn(S, H, generator=g) * 0.5).to(torch.bfloat16).to(dev) for _ in range(R)]
+    topk = [routing.lognormal_topk(S, K, E, R, 1.0, 5, r)[0].to(dev) for r in range(R)]
+    tpe = [torch.bincount(t.flatten().long(), minlength=E).to(torch.int32) for t in topk]
+    wts = [torch.rand(S, K, generator=g).to(dev) for _ in range(R)]
+    eye = torch.eye(H, dtype=torch.bfloat16, device=dev).repeat(2 * epn, 1, 1).contiguous()
+    for rep in range(2):        # twice: the provenance table is rewritten by every dispatch
+        h, w, cus, plans = cl.dispatch(hidden, wts, topk, tpe, zero_copy=True, router_weights_zero_copy=True)
+        sink = torch.empty_like(h[0])
+        for r in range(R):
+            gg.down(h[r], eye, cus[r], sink, push=cl.push_target(r))
+        outs, _ = cl.combine_pushed()
+        torch.cuda.synchronize()
+        cl.check()
+        gg.check_status()
+        pulled, _ = cl.combine(plans, h, None, zero_copy=True)
+        torch.cuda.synchronize()
+        for r in range(R):
+            want = (hidden[r].float() * K).to(torch.bfloat16)
+            assert torch.equal(outs[r], want), f"rank {r}: pushed combine"
+            assert torch.equal(pulled[r], want), f"rank {r}: pulled combine"

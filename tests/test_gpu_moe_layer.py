@@ -6,8 +6,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_moe_layer_matches_dense_reference(cuda_device):
+@pytest.mark.parametrize("push_combine", [False, True], ids=["pull", "push"])
+def test_moe_layer_matches_dense_reference(push_combine, cuda_device, monkeypatch):
     from moonep_b200.models.moe_block import MoEBlock, MoEConfig
+    monkeypatch.setenv("MOONEP_PUSH_COMBINE", "1" if push_combine else "0")
     cfg = MoEConfig("t", H=256, Hp=256, K=2, epn=4, shared_experts=0, S=192)
     blk = MoEBlock(cfg, num_sms=4, seed=3)
     torch.manual_seed(1)
