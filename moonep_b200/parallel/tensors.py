@@ -10,6 +10,7 @@ in use (single process).
 from __future__ import annotations
 
 import ctypes as C
+import math
 import os
 from dataclasses import dataclass
 
@@ -18,7 +19,7 @@ import torch.distributed as dist
 
 from .. import _native
 from ..geometry import align_up
-from .symm import (HANDLE_FABRIC, SymmetricHeap, _all_gather_bytes, exchange_fds, pad_dim0_for_alignment,
+from .symm import (HANDLE_FABRIC, SymmetricHeap, _all_gather_bytes, exchange_fds,
                    resolve_handle_kind, tensor_from_ptr, vmm_granularity)
 
 
@@ -67,12 +68,34 @@ def create_dist_tensor(shape, dtype: torch.dtype, group=None, multicast: bool = 
     if not _multi(group):
         t = torch.zeros(shape, dtype=dtype, device=dev)
         return DistTensor(t, t, None, shape[0], None)
-    rows = pad_dim0_for_alignment(shape, dtype, dev.index)
     es = torch.tensor([], dtype=dtype).element_size()
     row_bytes = es * _numel(shape[1:])
+    payload = shape[0] * row_bytes
+
+    def padded_rows(gran: int) -> int:       # smallest dim 0 >= shape[0] whose chunk is a multiple of gran
+        step = gran // math.gcd(gran, row_bytes)
+        return (shape[0] + step - 1) // step * step
+
+    gran = vmm_granularity(dev.index)
+    rows = padded_rows(gran)
+    if multicast:
+        # a multicast object wants its (often much larger) granularity; a small tensor is not
+        # blown up for it and simply does without the alias
+        mg = C.c_size_t(0)
+        kind = resolve_handle_kind(dev.index, group)
+        lib = _native.load()
+        ok = lib.mep_multicast_granularity(dev.index, dist.get_world_size(group), kind, rows * row_bytes, C.byref(mg)) == 0
+        big = padded_rows(max(gran, mg.value)) if ok and mg.value else 0
+        want = 1 if big and big * row_bytes <= max(4 * payload, 64 << 20) else 0
+        flags = _all_gather_bytes(bytes([want]), group)
+        multicast = all(f == b"\x01" for f in flags)
+        if multicast:
+            rows = big
     heap = SymmetricHeap.create(rows * row_bytes, group=group, multicast=multicast)
-    assert heap.chunk_bytes % row_bytes == 0
-    rows = heap.chunk_bytes // row_bytes          # multicast granularity may have padded further
+    if heap.chunk_bytes % row_bytes:
+        heap.close()
+        raise RuntimeError(f"symmetric chunk of {heap.chunk_bytes} bytes is not a whole number of {row_bytes}-byte rows")
+    rows = heap.chunk_bytes // row_bytes
     whole = heap.whole().view(dtype).view(heap.world * rows, *shape[1:])
     local = whole[heap.rank * rows:heap.rank * rows + shape[0]]
     mc = None

@@ -66,3 +66,17 @@ def test_geometry_limits():
         Geometry.make(8, 60, 2, 4, 2)
     with pytest.raises(AssertionError, match="token_padding"):
         Geometry.make(8, 64, 2, 4, 2, token_padding=0)
+
+
+def test_geometry_push_combine_regions():
+    """The push-combine regions are only laid out on request, follow the regular regions and do
+    not overlap: provenance table [NvS] int32, receive area [S*K, H] bf16, scalars [S*K] fp32."""
+    a = Geometry.make(4096, 7168, 8, 256, 8, 128, 32)
+    b = Geometry.make(4096, 7168, 8, 256, 8, 128, 32, push_combine=True)
+    assert (a.off_srcinfo, a.off_push, a.off_pushw) == (0, 0, 0)
+    assert b.off_srcinfo >= a.chunk_bytes - 1024 and b.off_srcinfo % 1024 == 0
+    assert b.off_push >= b.off_srcinfo + b.NvS * 4 and b.off_push % 1024 == 0
+    assert b.off_pushw >= b.off_push + b.N * b.H * 2
+    assert b.chunk_bytes >= b.off_pushw + b.N * 4
+    for name in ("off_hidden", "off_weights", "off_tpe", "off_bar", "off_dupcnt", "off_dupgroups", "off_duploffs", "off_ready"):
+        assert getattr(a, name) == getattr(b, name)
