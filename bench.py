@@ -167,6 +167,7 @@ def run_ours(args):
     cfg = CONFIGS[args.model]
     blk = MoEBlock(cfg, world, rank, num_sms=32, seed=0)
     S, H = cfg.S, cfg.H
+    path_note = "default"
     gen = torch.Generator().manual_seed(100 + rank)
     host_batches = [torch.randn(S, H, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(2)]
     dev_batches = [b.cuda() for b in host_batches]
@@ -202,10 +203,37 @@ def run_ours(args):
 
     scale, realised = calibrate_skew(blk, dev_batches[0], args.maxvio, world)
     sampler = ClockSampler(local).start()      # nvidia-smi needs a moment to come up: start before the warm-up
-    for _ in range(max(3, args.warmup)):
-        step(dev_batches[0].detach())
-    torch.cuda.synchronize()
-    blk.buf.check(); gg.check_status()
+
+    def warm_up():
+        for _ in range(max(3, args.warmup)):
+            step(dev_batches[0].detach())
+        torch.cuda.synchronize()
+        blk.buf.check(); gg.check_status()
+
+    # Safety net: should a bounded device wait run out during the warm-up on any rank (reported as an
+    # exception, the GPU stays usable), every rank rebuilds the layer on the plain path -- pull
+    # combine, serial backward pass -- and the run says so in its config.
+    try:
+        warm_up()
+        bad = 0
+    except Exception as e:      # noqa: BLE001
+        bad, path_note = 1, f"fallback after {type(e).__name__}: {str(e)[:120]}"
+    if world > 1:
+        t = torch.tensor([bad], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        bad = int(t)
+    if bad:
+        if path_note == "default":
+            path_note = "fallback after a failure on another rank"
+        type(blk.moe).forget_deferred()
+        torch.cuda.synchronize()
+        blk.destroy()
+        os.environ.update(MOONEP_PUSH_COMBINE="0", MOONEP_OVERLAP_BACKWARD="0", MOONEP_DEFER_LAST_REDUCTION="0")
+        blk = MoEBlock(cfg, world, rank, num_sms=32, seed=0)
+        if args.optimizer_in_backward:
+            blk.fuse_optimizer(lr)
+        scale, realised = calibrate_skew(blk, dev_batches[0], args.maxvio, world)
+        warm_up()
 
     # Capture the whole step (both input buffers) as CUDA graphs: one launch per step instead of
     # ~100.  All ranks must take the same path, so a failure on any rank sends everyone back to
@@ -336,7 +364,7 @@ def run_ours(args):
                    "step": "router + dispatch + grouped GEMM fwd/bwd + combine + reduce_grad + SGD"
                            + (" (each projection's SGD is launched inside the backward pass, on a side stream, once its "
                               "gradient is final)" if args.optimizer_in_backward else ""),
-                   "l2": "inputs larger than L2 (multi-GB working set per step)", "launch": graph_note,
+                   "l2": "inputs larger than L2 (multi-GB working set per step)", "launch": graph_note, "path": path_note,
                    "combine": ("pushed by the down GEMM's epilogue into the source ranks' memory, then a local sum"
                                if blk.buf.geo.off_push else "pulled from the peers' shards after the down GEMM")},
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},

@@ -130,6 +130,7 @@ class MoEBlock:
                     p.grad = None
 
     def destroy(self):
+        self.moe.wait_grads()        # nothing of this layer may still be queued on the comm stream
         self.pools.destroy()
         self.buf.destroy()
 
