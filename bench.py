@@ -201,65 +201,90 @@ def run_ours(args):
         launched = graphed[0].launches_per_step * n if graphed[0] is not None else lib.mep_launch_count() - c0
         return max_over_ranks(e0.elapsed_time(e1) / n, world), launched
 
-    scale, realised = calibrate_skew(blk, dev_batches[0], args.maxvio, world)
     sampler = ClockSampler(local).start()      # nvidia-smi needs a moment to come up: start before the warm-up
+    state = {"scale": None, "realised": None, "graph_note": "disabled (--no-cuda-graph)"}
 
-    def warm_up():
-        for _ in range(max(3, args.warmup)):
-            step(dev_batches[0].detach())
-        torch.cuda.synchronize()
-        blk.buf.check(); gg.check_status()
+    def agree_any(flag: int) -> int:
+        if world == 1:
+            return flag
+        t = torch.tensor([flag], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return int(t)
 
-    # Safety net: should a bounded device wait run out during the warm-up on any rank (reported as an
+    def attempt(inject: bool):
+        """Calibrate the routing skew, warm up, capture the step and replay it a few times.
+        Returns None, or the error if a device wait ran out on any rank.  Every rank executes the
+        same sequence of collectives whatever happens on it."""
+        err = None
+        try:
+            if inject:
+                raise RuntimeError("injected host-side failure")
+            state["scale"], state["realised"] = calibrate_skew(blk, dev_batches[0], args.maxvio, world)
+            for _ in range(max(3, args.warmup)):
+                step(dev_batches[0].detach())
+            torch.cuda.synchronize()
+            blk.buf.check(); gg.check_status()
+        except Exception as e:      # noqa: BLE001
+            err = e
+        if agree_any(1 if err is not None else 0):
+            return err if err is not None else RuntimeError("failure on another rank")
+        graphed[0] = None
+        if args.no_cuda_graph:
+            return None
+        # Capture the whole step (both input buffers) as CUDA graphs: one launch per step instead
+        # of ~100.  All ranks must take the same path, so a capture failure on any rank sends
+        # everyone back to launching from Python (not an error).
+        try:
+            c0 = lib.mep_launch_count()
+            gs = GraphedSteps(lambda x: step(x), dev_batches)
+            gs.launches_per_step = (lib.mep_launch_count() - c0) // len(gs)
+            ok, note = 1, "whole step replayed from a captured CUDA graph"
+        except Exception as e:      # noqa: BLE001
+            gs, ok, note = None, 0, f"capture failed, launched from Python: {type(e).__name__}: {str(e)[:160]}"
+            type(blk.moe).forget_deferred()
+            torch.cuda.synchronize()
+        if agree_any(1 - ok) and ok:
+            gs, note = None, "capture failed on another rank, launched from Python"
+        state["graph_note"] = note
+        err = None
+        try:
+            if gs is not None:
+                for i in range(3):
+                    gs.replay(i)
+                torch.cuda.synchronize()
+                blk.buf.check(); gg.check_status()
+        except Exception as e:      # noqa: BLE001
+            err = e
+        if agree_any(1 if err is not None else 0):
+            return err if err is not None else RuntimeError("failure on another rank")
+        graphed[0] = gs
+        return None
+
+    # Safety net: should a bounded device wait run out while preparing on any rank (reported as an
     # exception, the GPU stays usable), every rank rebuilds the layer on the plain path -- pull
     # combine, serial backward pass -- and the run says so in its config.
-    try:
-        warm_up()
-        bad = 0
-    except Exception as e:      # noqa: BLE001
-        bad, path_note = 1, f"fallback after {type(e).__name__}: {str(e)[:120]}"
-    if world > 1:
-        t = torch.tensor([bad], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        bad = int(t)
-    if bad:
-        if path_note == "default":
-            path_note = "fallback after a failure on another rank"
+    # MOONEP_BENCH_INJECT_FAILURE=1 raises a host-side exception in place of the first attempt
+    # (exercises this path without any device fault).
+    for plain in (False, True):
+        err = attempt(inject=not plain and os.environ.get("MOONEP_BENCH_INJECT_FAILURE") == "1")
+        if err is None:
+            break
+        if plain:
+            raise err
+        path_note = f"fallback to the plain path after {type(err).__name__}: {str(err)[:120]}"
+        graphed[0] = None
         type(blk.moe).forget_deferred()
         torch.cuda.synchronize()
+        try:
+            blk.buf.reset()
+        except Exception:      # noqa: BLE001
+            pass
         blk.destroy()
         os.environ.update(MOONEP_PUSH_COMBINE="0", MOONEP_OVERLAP_BACKWARD="0", MOONEP_DEFER_LAST_REDUCTION="0")
         blk = MoEBlock(cfg, world, rank, num_sms=32, seed=0)
         if args.optimizer_in_backward:
             blk.fuse_optimizer(lr)
-        scale, realised = calibrate_skew(blk, dev_batches[0], args.maxvio, world)
-        warm_up()
-
-    # Capture the whole step (both input buffers) as CUDA graphs: one launch per step instead of
-    # ~100.  All ranks must take the same path, so a failure on any rank sends everyone back to
-    # launching from Python.
-    graph_note = "disabled (--no-cuda-graph)"
-    if not args.no_cuda_graph:
-        try:
-            c0 = lib.mep_launch_count()
-            gs = GraphedSteps(lambda x: step(x), dev_batches)
-            gs.launches_per_step = (lib.mep_launch_count() - c0) // len(gs)
-            ok, graph_note = 1, "whole step replayed from a captured CUDA graph"
-        except Exception as e:      # noqa: BLE001
-            gs, ok, graph_note = None, 0, f"capture failed, launched from Python: {type(e).__name__}: {str(e)[:160]}"
-            type(blk.moe).forget_deferred()
-            torch.cuda.synchronize()
-        if world > 1:
-            t = torch.tensor([ok], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MIN)
-            if int(t) == 0 and ok:
-                gs, graph_note = None, "capture failed on another rank, launched from Python"
-        if gs is not None:
-            graphed[0] = gs
-            for i in range(3):
-                gs.replay(i)
-            torch.cuda.synchronize()
-            blk.buf.check(); gg.check_status()
+    scale, realised, graph_note = state["scale"], state["realised"], state["graph_note"]
 
     ms, launches = timed_steps(args.steps)
     # end to end through the public API: inputs come from pinned host memory every step and the
