@@ -50,6 +50,22 @@ def test_dispatch_combine(case, cuda_device):
         assert torch.equal(outw[r].cpu().view(torch.int32), weights[r].view(torch.int32)), "weights must round-trip bit-exactly"
 
 
+from shape_cases import case_params, case_id  # noqa: E402
+
+
+@pytest.mark.parametrize("p", case_params(), ids=case_id)
+def test_shape_list_plan_and_dispatch(p, cuda_device):
+    """Planner outputs (bit-exact against the oracle, duplicate tables as sets), dispatched rows,
+    route weights and zero-filled padding for every shape of the shared list, at every group
+    size the shape allows; both planner kernels are reached (small and large expert counts)."""
+    c, R = p
+    num_sms = 1 if c.S * c.K < 64 else (4 if R > 2 else 6)
+    cl, cp, plans, *_ = run_case(c.S, c.K, c.epn, c.H, R, num_sms, c.pad, c.routing, seed=c.seed, sigma=c.sigma)
+    for r in range(R):
+        assert int(plans[r].remote_stats[0]) == int((cp.experts_to_copy[r] >= 0).sum())
+    cl.heap.close()
+
+
 def test_combine_rounding(cuda_device):
     """randn payloads: duplicates rounded once locally, then one final rounding (<= 1 bf16 ulp)."""
     S, K, epn, H, R = 128, 8, 4, 256, 4

@@ -123,12 +123,17 @@ def test_swiglu_bwd(cuda_device):
 
 def test_sgd(cuda_device):
     from moonep_b200.ops import grouped_gemm as gg
-    p = torch.randn(4096, device="cuda").to(torch.bfloat16)
-    g = torch.randn(4096, device="cuda")
-    ref = (p.float() - 0.1 * g).to(torch.bfloat16)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    p = torch.randn(4096, device="cuda", generator=gen).to(torch.bfloat16)
+    g = torch.randn(4096, device="cuda", generator=gen)
+    ref = (p.float() - 0.1 * g).to(torch.bfloat16).float()
     gg.sgd_step(p, g, 0.1)
     torch.cuda.synchronize()
-    assert torch.equal(p, ref)
+    # the kernel contracts p - lr*g into one fused multiply-add, the fp32 reference rounds twice:
+    # a result may land on the neighbouring bf16 value when it sits on a rounding boundary
+    diff = (p.float() - ref).abs()
+    assert (diff <= ref.abs() * 2.0 ** -7).all(), "more than one bf16 ulp away from the fp32 reference"
+    assert (diff != 0).float().mean() < 0.01
 
 
 @pytest.mark.parametrize("pair_kernels", [False, True], ids=["1cta", "cta_pairs"])

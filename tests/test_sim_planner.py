@@ -100,3 +100,42 @@ def test_planner_properties(R, epn, S, K, pad, seed, hot):
             row = slice(s * K, (s + 1) * K)
             prim = dest[r, row][cp.dst[r, row] >= 0]
             assert len(set(prim.tolist())) == len(prim) == len(set(dest[r, row].tolist()))
+
+
+from shape_cases import case_params, case_id, SHAPE_CASES  # noqa: E402
+
+
+@pytest.mark.parametrize("p", case_params(), ids=case_id)
+def test_shape_list_on_the_oracle(p):
+    """Every shape of the shared list satisfies the planner invariants, fits the buffer geometry
+    and moves tokens consistently through the emulated dispatch / combine."""
+    from gpu_helpers import make_topk
+    from moonep_b200.geometry import Geometry
+    c, R = p
+    E = R * c.epn
+    topk, tpe = make_topk(c.routing, c.S, c.K, E, R, c.seed, c.sigma)
+    cp = plan_cluster(np.stack([t.numpy() for t in topk]), E, c.pad)
+    check_invariants(cp)
+    geo = Geometry.make(c.S, c.H, c.K, E, R, c.pad, 1)
+    assert geo.NvS == cp.NvS
+    for r in range(R):
+        assert torch.equal(torch.from_numpy(np.bincount(topk[r].numpy().ravel(), minlength=E)).int(), tpe[r])
+    if c.S * c.K * R <= 4096:        # identity round trip on the small shapes
+        hidden = [torch.arange(c.S, dtype=torch.float32)[:, None].repeat(1, 4) + 1000 * r for r in range(R)]
+        hn, _ = ops.dispatch(cp, hidden, None)
+        out, _ = ops.combine(cp, [torch.nan_to_num(h) for h in hn], None)
+        for r in range(R):       # combine is a plain sum over a token's K rows, duplicates included
+            assert torch.equal(out[r], hidden[r] * float(c.K))
+
+
+def test_shape_list_reaches_every_planner_regime():
+    """The list must keep covering: E above one thread block, E*R above the fast planner's table
+    limit, padding of 1, padding above every segment, K=1, one token, and all four synthetic
+    routings (a guard against trimming the list)."""
+    names = {c.name for c in SHAPE_CASES}
+    assert any(c.epn > 1024 for c in SHAPE_CASES)
+    assert any(c.epn * c.max_R * c.max_R > 8192 for c in SHAPE_CASES)
+    assert any(c.pad == 1 for c in SHAPE_CASES) and any(c.pad > c.S * c.K for c in SHAPE_CASES)
+    assert any(c.K == 1 for c in SHAPE_CASES) and any(c.S == 1 for c in SHAPE_CASES)
+    assert {"all_local", "all_remote", "single_expert", "duplicate_topk"} <= {c.routing for c in SHAPE_CASES}
+    assert len(names) == len(SHAPE_CASES)
