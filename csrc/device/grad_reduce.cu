@@ -29,9 +29,14 @@ struct GradReduceArgsPack { GradReduceArgs a[MEP_MAX_VRANKS]; };
 
 constexpr int kRedThreads = 384;          // 12 warps
 constexpr int kRedSlots = 32;             // 16-byte vectors per lane in one warp stage
+constexpr int kRedDepth = 4;              // units in flight per warp when an expert has <= 8 replicas
 
 __device__ __forceinline__ void cp_async16(uint32_t saddr, const void* g) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(saddr), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_but() {   // all but the newest N groups are done
+  asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit_wait_all() {
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
@@ -81,10 +86,14 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
   __syncthreads();
   const int nact = s_nact;
 
-  // Each warp owns a 16 KB shared-memory stage. Per pass it fetches P 16-byte vectors per lane from
-  // EVERY replica with asynchronous copies (no registers held while the NVLink reads are in flight),
-  // loads the same vectors of the local grad, waits for its own copies and adds the replicas in list
-  // order. 12 warps x 16 KB keep up to 192 KB per SM in flight.
+  // Each warp owns a 16 KB shared-memory stage of 32 slots (one slot = one 16-byte vector per
+  // lane). A work unit is P vectors per lane of ONE expert matrix: the warp fetches them from EVERY
+  // replica with asynchronous copies (no registers held while the NVLink reads are in flight),
+  // loads the same vectors of the local grad, waits for its own copies and adds the replicas in
+  // list order. With few replicas (the common case: one or two) a unit fills only part of the
+  // stage, so the stage is used as a ring of kRedDepth units and the copies of the next units are
+  // already under way while this one is summed: 12 warps x 16 KB stay in flight per SM, which is
+  // what a 32-CTA launch needs to cover the NVLink round trip at link rate.
   const int lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   const int gw = blockIdx.x * nwarps + warp, gnw = nb * nwarps;
   const uint32_t stage = smem_u32(s_stage) + (uint32_t)warp * (kRedSlots * 32 * 16);
@@ -92,7 +101,8 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
   for (int ai = 0; ai < nact; ++ai) {
     const int le = s_act[ai];
     const int* srcs = s_src + s_off[le]; const int ns = s_off[le + 1] - s_off[le];
-    int P = kRedSlots / ns; if (P > 8) P = 8; if (P < 1) P = 1;
+    const bool ring = ns * kRedDepth <= kRedSlots;               // up to 8 replicas: pipelined path
+    int P = kRedSlots / (ring ? ns * kRedDepth : ns); if (P > 8) P = 8; if (P < 1) P = 1;
     const int npass_src = (ns + kRedSlots - 1) / kRedSlots;     // > 1 only if an expert has more than 32 replicas
     for (int t = 0; t < a.ntensors; ++t) {
       const ReduceTensor& T = a.t[t];
@@ -101,6 +111,52 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
       float* lp = T.local + (int64_t)le * T.expert_elems;
       const int64_t unit_vecs = 32 * (int64_t)P;
       const int64_t nunits = (nvec + unit_vecs - 1) / unit_vecs;
+      if (ring) {
+        const int uslots = ns * P;                                // slots of one unit
+        auto issue = [&](int64_t u, int r) {
+          const int64_t v0 = u * unit_vecs;
+          for (int j = 0; j < ns; ++j) {
+            const int idx = srcs[j], d = idx / epn, b = idx - d * epn;
+            const char* rp = T.pool + (int64_t)d * T.rank_stride + (int64_t)b * ebytes;
+            for (int p = 0; p < P; ++p) {
+              const int64_t v = v0 + (int64_t)p * 32 + lane;
+              if (v < nvec) cp_async16(stage + (uint32_t)((r * uslots + j * P + p) * 32 + lane) * 16, rp + v * 16);
+            }
+          }
+        };
+        // One copy group is committed per ring step, empty or not, so that "all but the newest
+        // kRedDepth-1 groups" always names the unit about to be summed.
+        int64_t ui = gw;
+        for (int k = 0; k < kRedDepth - 1; ++k, ui += gnw) { if (ui < nunits) issue(ui, k); cp_async_commit(); }
+        int r = 0;
+        for (int64_t u = gw; u < nunits; u += gnw, ui += gnw) {
+          int rn = r + kRedDepth - 1; if (rn >= kRedDepth) rn -= kRedDepth;
+          if (ui < nunits) issue(ui, rn);
+          cp_async_commit();
+          const int64_t v0 = u * unit_vecs;
+          float4 acc[8];
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            const int64_t v = v0 + (int64_t)p * 32 + lane;
+            acc[p] = (p < P && v < nvec) ? *reinterpret_cast<const float4*>(lp + v * 4) : make_float4(0, 0, 0, 0);
+          }
+          cp_async_wait_but<kRedDepth - 1>();
+          for (int j = 0; j < ns; ++j)
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+              const int64_t v = v0 + (int64_t)p * 32 + lane;
+              if (p < P && v < nvec)
+                acc[p] = f4add(acc[p], *reinterpret_cast<const int4*>(stage_g + (size_t)((r * uslots + j * P + p) * 32 + lane) * 16));
+            }
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            const int64_t v = v0 + (int64_t)p * 32 + lane;
+            if (p < P && v < nvec) *reinterpret_cast<float4*>(lp + v * 4) = acc[p];
+          }
+          if (++r == kRedDepth) r = 0;
+        }
+        cp_async_wait_but<0>();      // only empty groups can be left; drain them before the stage is reused
+      } else
       for (int64_t u = gw; u < nunits; u += gnw) {
         const int64_t v0 = u * unit_vecs;
         float4 acc[8];
