@@ -82,22 +82,23 @@ def synthetic_plan(etc: torch.Tensor, NvS: int, K: int, N: int, device) -> MoonE
 
 
 def time_launches(fn, warmup: int, iters: int, flush: torch.Tensor | None):
-    """Median device time in microseconds of ``fn`` (CUDA events on the current stream; the
-    optional ``flush`` buffer, larger than L2, is rewritten between timed launches)."""
+    """Median device time in microseconds of ``fn``.  CUDA events on the current stream; the
+    launches are queued behind a short device-side sleep without synchronising in between, so
+    the host's launch cost (Python argument checks, ~0.1 ms) stays off the device timeline; the
+    optional ``flush`` buffer, larger than L2, is rewritten between timed launches."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    ts = []
-    for _ in range(iters):
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    torch.cuda._sleep(400_000 * iters)          # ~0.2 ms per queued launch at 1.9 GHz
+    for a, b in evs:
         if flush is not None:
             flush.add_(1)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
         b.record()
-        torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b) * 1e3)
-    ts.sort()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
     return ts[len(ts) // 2]
 
 
