@@ -32,6 +32,24 @@ def _worker(rank, world, port, mode, q):
                 os.close(fd)
             os.close(rfd); os.close(wfd)
             q.put((rank, "ok" if ok else "bad"))
+        elif mode == "subgroups":
+            # two disjoint EP groups of two ranks inside one job (what ``Buffer(group=...)`` relies
+            # on): each group exchanges among its own members only, addressed by group rank
+            groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+            mine = groups[rank // 2]
+            rfd, wfd = os.pipe()
+            fds = symm.exchange_fds(rfd, mine)
+            os.write(wfd, bytes([65 + rank]) * 2)      # one byte for me, one for my partner
+            dist.barrier()
+            got = os.read(fds[dist.get_rank(mine)], 1)
+            ok = len(fds) == 2 and got == bytes([65 + rank])
+            # the partner's descriptor must be the partner's pipe: it holds the partner's byte
+            other = os.read(fds[1 - dist.get_rank(mine)], 1)
+            ok = ok and other == bytes([65 + (rank ^ 1)])
+            for fd in fds:
+                os.close(fd)
+            os.close(rfd); os.close(wfd)
+            q.put((rank, "ok" if ok else "bad"))
         elif mode == "silent_rank":
             # the last rank skips the send: the others must time out with a clean error
             symm.IPC_TIMEOUT_MS = 500
@@ -86,6 +104,11 @@ def _run(world, mode):
 def test_fd_exchange_between_processes():
     res = _run(3, "ok")
     assert res == {0: "ok", 1: "ok", 2: "ok"}
+
+
+def test_fd_exchange_inside_subgroups():
+    res = _run(4, "subgroups")
+    assert res == {0: "ok", 1: "ok", 2: "ok", 3: "ok"}
 
 
 def test_rank_that_never_sends_times_out_cleanly():
