@@ -21,6 +21,61 @@ from .parallel.symm import SymmetricHeap
 NAMES = ("gate", "up", "down")
 
 
+def pool_layout(epn: int, shapes: dict, dtype, with_grads: bool):
+    """Byte offsets inside one rank's chunk: per projection ``[local epn | slots epn]`` of the
+    payload dtype, then (training) the same in fp32 for the gradients.  Returns
+    ``(weight_offsets, grad_offsets, bytes_per_rank)``."""
+    es = torch.tensor([], dtype=dtype).element_size()
+    off = 0
+    woff, goff = {}, {}
+    for n in NAMES:
+        r, c = shapes[n]
+        woff[n] = off
+        off = align_up(off + 2 * epn * r * c * es, 1024)
+    if with_grads:
+        for n in NAMES:
+            r, c = shapes[n]
+            goff[n] = off
+            off = align_up(off + 2 * epn * r * c * 4, 1024)
+    return woff, goff, off
+
+
+def describe_layout(epn: int, shapes: dict, dtype=torch.bfloat16, with_grads: bool = True, world: int = 8) -> str:
+    """Text diagram of the pools of one rank and of the three views the API takes (the
+    counterpart of the reference's weight_buffer / grad_buffer figures,
+    figure/generate_buffer_figures.py there).  Needs no GPU."""
+    woff, goff, total = pool_layout(epn, shapes, dtype, with_grads)
+    es = torch.tensor([], dtype=dtype).element_size()
+    dn = str(dtype).replace("torch.", "")
+    mib = lambda b: f"{b / 2**20:9.1f} MiB"  # noqa: E731
+    lines = [f"one rank's chunk of the symmetric heap: {mib(total).strip()} "
+             f"(same layout on each of the {world} ranks; rank stride = chunk size)", ""]
+
+    def block(title, offs, esize, tname, local, slots):
+        lines.append(title)
+        for n in NAMES:
+            r, c = shapes[n]
+            half = epn * r * c * esize
+            lines.append(f"  {n:<5} @ {offs[n]:>14,d}  | {local} [{epn}, {r}, {c}] {tname} {mib(half)} "
+                         f"| {slots} [{epn}, {r}, {c}] {tname} {mib(half)} |")
+        lines.append("")
+
+    block("weights", woff, es, dn, "local experts", "prefetch slots")
+    if with_grads:
+        block("gradients", goff, 4, "float32", "local grads  ", "reduce slots  ")
+    r, c = shapes[NAMES[0]]
+    lines += [
+        "views (per projection):",
+        f"  compute  [2*epn={2 * epn}, rows, cols]   local experts followed by this rank's slots -> grouped GEMM operand,",
+        "           indexed by the VM group g of cu_seqlens: g < epn local expert g, g >= epn slot g - epn",
+        f"  prefetch [R={world}, epn={epn}, rows, cols]  every rank's prefetch slots through one mapping -> Buffer.prefetch_weight",
+        f"  reduce   [R={world}, epn={epn}, rows, cols]  every rank's fp32 reduce slots                   -> Buffer.reduce_grad",
+        f"  (slot b of rank d holds expert plan.experts_to_copy[d, b]; e.g. one {NAMES[0]} matrix = "
+        f"{mib(r * c * es).strip()} {dn}, {mib(r * c * 4).strip()} fp32)",
+    ]
+    return "\n".join(lines)
+
+
 class ExpertPools:
     def __init__(self, epn: int, gate_shape, up_shape, down_shape, dtype=torch.bfloat16, group=None,
                  with_grads: bool = False, world: int | None = None, rank: int | None = None,
@@ -37,18 +92,7 @@ class ExpertPools:
             else:
                 world, rank = 1, 0
         self.world, self.rank, self._group = world, rank, group
-        es = torch.tensor([], dtype=dtype).element_size()
-        off = 0
-        self._woff, self._goff = {}, {}
-        for n in NAMES:
-            r, c = self._shapes[n]
-            self._woff[n] = off
-            off = align_up(off + 2 * epn * r * c * es, 1024)
-        if with_grads:
-            for n in NAMES:
-                r, c = self._shapes[n]
-                self._goff[n] = off
-                off = align_up(off + 2 * epn * r * c * 4, 1024)
+        self._woff, self._goff, off = pool_layout(epn, self._shapes, dtype, with_grads)
         self._own_heap = heap is None
         if heap is None:
             if world > 1:
@@ -62,6 +106,10 @@ class ExpertPools:
 
     def shape(self, name):
         return self._shapes[name]
+
+    def describe(self) -> str:
+        """Text diagram of this allocation (see ``describe_layout``)."""
+        return describe_layout(self.epn, self._shapes, self.dtype, self.with_grads, self.world)
 
     def _view(self, off, name, dtype, first, count, rank=None):
         r, c = self._shapes[name]
@@ -116,3 +164,16 @@ class ExpertPools:
                 dist.barrier(group=self._group)
             self.heap.close()
         self.heap = None
+
+
+if __name__ == "__main__":
+    import argparse
+    ap = argparse.ArgumentParser(description="print the expert pool layout of one rank")
+    ap.add_argument("--epn", type=int, default=32)
+    ap.add_argument("--H", type=int, default=7168)
+    ap.add_argument("--Hp", type=int, default=2048)
+    ap.add_argument("--R", type=int, default=8)
+    ap.add_argument("--no-grads", action="store_true")
+    a = ap.parse_args()
+    print(describe_layout(a.epn, {"gate": (a.H, a.Hp), "up": (a.H, a.Hp), "down": (a.Hp, a.H)},
+                          with_grads=not a.no_grads, world=a.R))

@@ -80,3 +80,26 @@ def test_geometry_push_combine_regions():
     assert b.chunk_bytes >= b.off_pushw + b.N * 4
     for name in ("off_hidden", "off_weights", "off_tpe", "off_bar", "off_dupcnt", "off_dupgroups", "off_duploffs", "off_ready"):
         assert getattr(a, name) == getattr(b, name)
+
+
+def test_pool_layout_and_description():
+    """Offsets of the [local | slots] pools: disjoint, 1 KiB aligned, weights before grads; the
+    text diagram names every projection and view."""
+    import torch
+    from moonep_b200.pools import pool_layout, describe_layout, NAMES
+    shapes = {"gate": (256, 96), "up": (256, 96), "down": (96, 256)}
+    epn = 3
+    woff, goff, total = pool_layout(epn, shapes, torch.bfloat16, True)
+    spans = []
+    for n in NAMES:
+        r, c = shapes[n]
+        spans.append((woff[n], woff[n] + 2 * epn * r * c * 2))
+        spans.append((goff[n], goff[n] + 2 * epn * r * c * 4))
+    spans.sort()
+    assert all(a % 1024 == 0 for a, _ in spans)
+    assert all(spans[i][1] <= spans[i + 1][0] for i in range(len(spans) - 1)) and spans[-1][1] <= total
+    assert max(woff.values()) < min(goff.values())
+    assert pool_layout(epn, shapes, torch.int8, False)[1] == {}
+    text = describe_layout(epn, shapes, torch.bfloat16, True, world=4)
+    for word in ("gate", "up", "down", "prefetch", "reduce", "compute", "[R=4, epn=3"):
+        assert word in text

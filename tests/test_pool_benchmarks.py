@@ -51,3 +51,20 @@ def test_pool_benchmark_scripts_run_emulated(script, rate, cuda_device):
     assert [r["case"] for r in rows] == ["slots_3", "ramp", "epn4_full"]
     for r in rows:
         assert r["slots"] > 0 and r["us"] > 0 and r[rate] > 0 and r["emulated"] is True
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [[], ["--no-cudagraph"]], ids=["cudagraph", "eager"])
+def test_comm_benchmark_script_runs(mode, cuda_device, tmp_path):
+    out_csv = tmp_path / "comm.csv"
+    cmd = [sys.executable, os.path.join(ROOT, "benchmarks", "bench_comm.py"), "--S", "256", "--hidden", "256", "512",
+           "--topk", "4", "--epn", "4", "--maxvio", "0", "1", "--num-sms", "4", "--pad", "16", "--iters", "3",
+           "--warmup", "1", "--out", str(out_csv), *mode]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    rows = [json.loads(line) for line in out.stdout.splitlines() if line.startswith("{")]
+    assert len(rows) == 4 and {r["H"] for r in rows} == {256, 512}
+    for r in rows:
+        assert all(r[k + "_us"] > 0 for k in ("dispatch_fwd", "dispatch_bwd", "combine_fwd", "combine_bwd"))
+        assert r["timing"] == ("eager" if mode else "cudagraph")
+    assert out_csv.read_text().count("\n") == 5
