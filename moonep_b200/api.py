@@ -36,6 +36,7 @@ from .plan import MoonEPCommPlan
 
 logger = logging.getLogger(__name__)
 _NVTX = os.environ.get("MOONEP_NVTX", "0") == "1"
+_VERIFY_PLANS = os.environ.get("MOONEP_VERIFY_PLANS", "0") == "1"     # debugging: see Buffer.verify_plan
 
 PREFETCH_DTYPES = (torch.bfloat16, torch.int8, torch.uint8, torch.float16, torch.float32)
 
@@ -331,6 +332,25 @@ class Buffer(OpsMixin):
         return dict(experts_received=rs[0], slots_sent=rs[1], dup_groups=dc[0], dup_rows=dc[1],
                     dedup_ratio=dc[1] / max(1, plan.N), padded_rows=int(zf))
 
+    def verify_plan(self, plan: MoonEPCommPlan) -> None:
+        """Debugging aid, collective and synchronising: every rank fingerprints its view of the
+        plan of one dispatch, the fingerprints are gathered over the process group and compared
+        (identical redundant-expert table everywhere, statistics consistent with it, exactly
+        ``S*K`` rows arriving on every rank).  Raises ``RuntimeError`` on every rank if the
+        replicated planners diverged.  ``MOONEP_VERIFY_PLANS=1`` runs it after every fresh
+        synchronous ``dispatch``."""
+        from .plan import plan_fingerprint, compare_fingerprints
+        self._st()
+        fp = plan_fingerprint(plan, self.rank)
+        if self.geo.R > 1:
+            fps = [None] * self.geo.R
+            dist.all_gather_object(fps, fp, group=self._group)
+        else:
+            fps = [fp]
+        errs = compare_fingerprints(fps)
+        if errs:
+            raise RuntimeError("MoonEP plan check failed: " + "; ".join(errs))
+
     # ---- async plumbing
     def _run(self, async_finish: bool, tensors, fn, label: str = "moonep.op"):
         nvtx = _NVTX
@@ -388,6 +408,8 @@ class Buffer(OpsMixin):
                 if isinstance(t, torch.Tensor):
                     t.record_stream(torch.cuda.current_stream())
             return h, w, cu, p, ev
+        if plan is None and _VERIFY_PLANS and not torch.cuda.is_current_stream_capturing():
+            self.verify_plan(p)
         return h, w, cu, p
 
     # ---- prefetch

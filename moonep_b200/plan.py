@@ -89,3 +89,59 @@ class MoonEPCommPlan:
     def __setstate__(self, state):
         for k, v in state.items():
             object.__setattr__(self, k, v)
+
+
+# ---- cross-rank consistency check (debugging aid)
+#
+# The planner is replicated: every rank solves the same problem from the same exchanged
+# histograms and must arrive at the same tables.  A divergence (a tie broken differently, a
+# stale histogram) would corrupt routing silently, so a plan can be fingerprinted on each rank
+# and the fingerprints compared on the host.
+
+def plan_fingerprint(plan: MoonEPCommPlan, rank: int) -> dict:
+    """Host-side summary of ``plan`` as seen by ``rank`` (synchronises; small)."""
+    import hashlib
+    etc = plan.experts_to_copy.cpu()
+    dst = plan.dst.cpu().long()
+    raw = torch.where(dst >= 0, dst, -dst - 1)
+    dest, loff = raw // plan.NvS, raw % plan.NvS
+    epn = plan.E // plan.R
+    mine = (etc >= rank * epn) & (etc < (rank + 1) * epn)
+    stats = plan.remote_stats.tolist()
+    return {
+        "rank": rank,
+        "etc_sha1": hashlib.sha1(etc.numpy().tobytes()).hexdigest(),
+        "rows_to": torch.bincount(dest.clamp(0, plan.R - 1), minlength=plan.R).tolist(),
+        "dest_in_range": bool(((dest >= 0) & (dest < plan.R)).all()),
+        "max_loff": int(loff.max()) if loff.numel() else -1,
+        "received": int((etc[rank] >= 0).sum()), "received_stat": int(stats[0]),
+        "sent": int(mine.sum()), "sent_stat": int(stats[1]),
+        "N": plan.N, "NvS": plan.NvS,
+    }
+
+
+def compare_fingerprints(fps) -> list[str]:
+    """Problems found in the fingerprints of all ranks of one dispatch (empty list = consistent):
+    identical redundant-expert tables, statistics that match the table, destinations in range,
+    and exactly ``N`` rows arriving on every rank."""
+    fps = sorted(fps, key=lambda f: f["rank"])
+    errs = []
+    if len({f["etc_sha1"] for f in fps}) != 1:
+        errs.append("experts_to_copy differs between ranks: " + ", ".join(f"{f['rank']}:{f['etc_sha1'][:8]}" for f in fps))
+    for f in fps:
+        if not f["dest_in_range"]:
+            errs.append(f"rank {f['rank']}: a destination rank is out of range")
+        if f["max_loff"] >= f["NvS"]:
+            errs.append(f"rank {f['rank']}: slot offset {f['max_loff']} beyond NvS={f['NvS']}")
+        if f["received"] != f["received_stat"] or f["sent"] != f["sent_stat"]:
+            errs.append(f"rank {f['rank']}: remote_stats ({f['received_stat']}, {f['sent_stat']}) disagree with the "
+                        f"slot table ({f['received']}, {f['sent']})")
+    R = len(fps)
+    if all(len(f["rows_to"]) == R for f in fps):
+        for d in range(R):
+            got = sum(f["rows_to"][d] for f in fps)
+            if got != fps[d]["N"]:
+                errs.append(f"rank {d} receives {got} rows, expected exactly {fps[d]['N']}")
+    else:
+        errs.append("fingerprints come from groups of different sizes")
+    return errs

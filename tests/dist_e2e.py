@@ -97,6 +97,7 @@ def run_scenario(buf, rank, R, dev, S, H, K, epn, pad, E, Hp):
 
     # ---- fresh dispatch, sync
     h1, w1, cu1, plan1 = buf.dispatch(hidden, weights, topk, tpe)
+    buf.verify_plan(plan1)            # replicated planners agree; every rank receives S*K rows
     torch.cuda.synchronize()
     safe_check(buf)
     chk(torch.equal(plan1.dst.cpu().long(), torch.from_numpy(cp.dst[rank])), "dst")

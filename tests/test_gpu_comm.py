@@ -187,6 +187,7 @@ def test_public_buffer_r1(cuda_device):
     topk = torch.randint(0, E, (S, K), dtype=torch.int32, device="cuda", generator=g)
     tpe = torch.bincount(topk.flatten(), minlength=E).to(torch.int32)
     h1, w1, cu1, plan1 = buf.dispatch(hidden, w, topk, tpe)
+    buf.verify_plan(plan1)            # replicated planners agree; every rank receives S*K rows
     assert isinstance(plan1, MoonEPCommPlan) and tuple(h1.shape) == (buf.NvS, H)
     h2, w2, cu2, plan2, ev = buf.dispatch(hidden, w, topk, tpe, async_finish=True)
     ev.wait(torch.cuda.current_stream())

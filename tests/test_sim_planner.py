@@ -139,3 +139,46 @@ def test_shape_list_reaches_every_planner_regime():
     assert any(c.K == 1 for c in SHAPE_CASES) and any(c.S == 1 for c in SHAPE_CASES)
     assert {"all_local", "all_remote", "single_expert", "duplicate_topk"} <= {c.routing for c in SHAPE_CASES}
     assert len(names) == len(SHAPE_CASES)
+
+
+def _plans_from_oracle(cp):
+    """MoonEPCommPlan objects (CPU tensors) for every rank of an oracle plan."""
+    from moonep_b200 import MoonEPCommPlan
+    R, epn, NvS = cp.R, cp.E // cp.R, cp.NvS
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.int32).contiguous()  # noqa: E731
+    z = lambda *s: torch.zeros(*s, dtype=torch.int32)  # noqa: E731
+    return [MoonEPCommPlan(dst=i32(cp.dst[r]), experts_to_copy=i32(cp.experts_to_copy),
+                           zero_fill_ranges=i32(cp.zero_fill_ranges[r]), remote_stats=i32(cp.remote_stats[r]),
+                           N=cp.dst.shape[1], R=R, E=cp.E, NvS=NvS, K=cp.K,
+                           dup_groups=z(NvS, 3), dup_loffs=z(NvS), dup_counts=z(2)) for r in range(R)]
+
+
+def test_plan_fingerprints_agree_and_catch_divergence():
+    """The cross-rank plan check accepts the oracle's plans and names each kind of divergence."""
+    from moonep_b200.plan import plan_fingerprint, compare_fingerprints
+    R, S, K, epn = 4, 64, 4, 4
+    topk = np.stack([routing.lognormal_topk(S, K, R * epn, R, 2.0, 7, r)[0].numpy() for r in range(R)])
+    cp = plan_cluster(topk, R * epn, 16)
+    assert (cp.experts_to_copy >= 0).any()
+    plans = _plans_from_oracle(cp)
+    fps = [plan_fingerprint(p, r) for r, p in enumerate(plans)]
+    assert compare_fingerprints(fps) == []
+    # a rank whose slot table differs
+    bad = plans[2].clone()
+    bad.experts_to_copy[0, -1] = 1
+    errs = compare_fingerprints(fps[:2] + [plan_fingerprint(bad, 2)] + fps[3:])
+    assert any("experts_to_copy differs" in e for e in errs)
+    # a rank that routes one row to another destination: two ranks no longer receive S*K rows
+    bad = plans[1].clone()
+    raw = int(bad.dst[0]) if int(bad.dst[0]) >= 0 else -int(bad.dst[0]) - 1
+    bad.dst[0] = ((raw // cp.NvS + 1) % R) * cp.NvS + raw % cp.NvS
+    errs = compare_fingerprints([fps[0], plan_fingerprint(bad, 1)] + fps[2:])
+    assert sum("receives" in e for e in errs) == 2
+    # statistics that do not match the table
+    bad = plans[0].clone()
+    bad.remote_stats[0] += 1
+    assert any("remote_stats" in e for e in compare_fingerprints([plan_fingerprint(bad, 0)] + fps[1:]))
+    # plans survive pickling (debug dumps)
+    import pickle
+    again = pickle.loads(pickle.dumps(plans[0]))
+    assert torch.equal(again.dst, plans[0].dst) and again.NvS == plans[0].NvS
