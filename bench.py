@@ -400,10 +400,30 @@ def run_ours(args):
         "published_config": published,
     }
     if rank == 0:
-        print(json.dumps(out), flush=True)
+        _emit(json.dumps(out))
     blk.destroy()
     if world > 1:
         dist.destroy_process_group()
+
+
+_RESULT_FD = None
+
+
+def _emit(line: str) -> None:
+    """Write the result line to the process's original stdout."""
+    if _RESULT_FD is None:
+        print(line, flush=True)
+    else:
+        os.write(_RESULT_FD, (line + "\n").encode())
+
+
+def _reserve_stdout() -> None:
+    """Libraries write banners to stdout (NCCL prints its version there): point fd 1 at stderr for
+    the rest of the run and keep the original stdout for the one JSON line."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
 
 
 def main():
@@ -411,6 +431,7 @@ def main():
     if args.impl == "reference":
         from benchmarks.bench_reference import run_reference
         return run_reference(args)
+    _reserve_stdout()
     run_ours(args)
 
 

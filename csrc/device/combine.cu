@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(256) dup_reduce_kernel(MepCtxPack P, DupArgsPa
     const unsigned rows = __ballot_sync(0xffffffffu, myrow != nullptr);
     reduce_rows_auto<false>(myrow, rows, __popc(rows), base + (size_t)p * row_bytes, nvec, lane);
   }
+  pdl_trigger();                               // the combine may be scheduled while this grid drains
 }
 
 // ------------------------------------------------------------------ combine
@@ -131,6 +132,7 @@ __device__ __forceinline__ void cp_async_commit_wait_all() {
 // A lane only ever reads back what it copied itself, so no cross-lane synchronisation is needed.
 // With 14 warps per CTA up to 224 KB per SM are in flight, which is what hides NVLink latency.
 __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, CombineArgsPack A) {
+  pdl_wait();                                // rows of this shard were pre-reduced by the kernel before
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const CombineArgs& a = A.a[blockIdx.y];
   extern __shared__ __align__(128) unsigned char smem[];
@@ -261,14 +263,13 @@ extern "C" int mep_launch_dup_reduce(int nv, const MepRankCtx* const* ctxs, cons
 }
 
 extern "C" int mep_launch_combine(int nv, const MepRankCtx* const* ctxs, const mep::CombineArgs* args,
-                                  int num_sms, int H, cudaStream_t stream) {
+                                  int num_sms, int pdl, cudaStream_t stream) {
   MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "combine: nv=%d out of range", nv);
-  (void)H;
   MepCtxPack P = {}; mep::CombineArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
   const size_t smem = (size_t)mep::kCombWarps * mep::kCombSlots * 32 * 16;
   return mep::launch_cooperative(mep::combine_kernel, dim3(num_sms, nv), dim3(mep::kCombThreads), smem,
-                                 stream, false, P, A);
+                                 stream, pdl != 0, P, A);
 }
 
 extern "C" int mep_launch_push_reduce(int nv, const MepRankCtx* const* ctxs, const mep::PushReduceArgs* args,

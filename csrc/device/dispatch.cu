@@ -192,6 +192,7 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   if (lane == 0 && warp == kSendWarps) trace_mark(c, MEP_K_DISPATCH, 4);
   cross_rank_barrier(c, nb, 1, MEP_K_DISPATCH, 30);
   if (tid == 0) trace_mark(c, MEP_K_DISPATCH, 5);
+  pdl_trigger();                               // the duplicate expansion may be scheduled while this grid drains
 }
 
 // ---------------------------------------------------------------------------------------
@@ -234,6 +235,7 @@ struct DupArgs { __nv_bfloat16* buf; const int32_t* dup_groups; const int32_t* d
 struct DupArgsPack { DupArgs a[MEP_MAX_VRANKS]; };
 
 __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPack A) {
+  pdl_wait();                                // the plan tables and the rows come from the kernel before
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const DupArgs& a = A.a[blockIdx.y];
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
@@ -273,6 +275,7 @@ struct DupFreshArgs { __nv_bfloat16* buf; int32_t* dup_groups; int32_t* dup_loff
 struct DupFreshArgsPack { DupFreshArgs a[MEP_MAX_VRANKS]; };
 
 __global__ void __launch_bounds__(256) dup_expand_fresh_kernel(MepCtxPack P, DupFreshArgsPack A) {
+  pdl_wait();                                // the plan tables and the rows come from the kernel before
   const MepRankCtx c = *P.ctx[blockIdx.y];
   const DupFreshArgs& a = A.a[blockIdx.y];
   __shared__ int s_goff[MEP_MAX_RANKS + 1], s_loff[MEP_MAX_RANKS + 1];
@@ -363,15 +366,15 @@ extern "C" int mep_launch_dup_finalize(int nv, const MepRankCtx* const* ctxs, co
 }
 
 extern "C" int mep_launch_dup_expand(int nv, const MepRankCtx* const* ctxs, const mep::DupArgs* args,
-                                     int num_blocks, cudaStream_t stream) {
+                                     int num_blocks, int pdl, cudaStream_t stream) {
   MepCtxPack P = {}; mep::DupArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  return mep::launch_plain(mep::dup_expand_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A);
+  return mep::launch_plain_pdl(mep::dup_expand_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, pdl != 0, P, A);
 }
 
 extern "C" int mep_launch_dup_expand_fresh(int nv, const MepRankCtx* const* ctxs, const mep::DupFreshArgs* args,
-                                           int num_blocks, cudaStream_t stream) {
+                                           int num_blocks, int pdl, cudaStream_t stream) {
   MepCtxPack P = {}; mep::DupFreshArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  return mep::launch_plain(mep::dup_expand_fresh_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A);
+  return mep::launch_plain_pdl(mep::dup_expand_fresh_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, pdl != 0, P, A);
 }

@@ -62,6 +62,15 @@ __device__ __forceinline__ void st_na_v4(void* p, int4 v) {
   asm volatile("st.global.L1::no_allocate.v4.s32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Counterpart of the reference's pdl_wait_predecessor / pdl_trigger_dependents
+// (moonep/_common.py:393-406). pdl_wait: returns once every kernel this launch depends on has
+// completed and its writes are visible (a no-op for a launch without the attribute).
+// pdl_trigger: this CTA has nothing left that a dependent launch must wait for before being
+// SCHEDULED; the dependent still waits in pdl_wait for this grid to finish.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- NVSwitch multicast
 // One store, delivered by the switch to the same offset of every rank's chunk.
 __device__ __forceinline__ void multimem_st_v4(void* mc_addr, int4 v) {

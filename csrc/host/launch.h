@@ -60,4 +60,23 @@ int launch_plain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
   return 0;
 }
 
+// launch_plain with an optional programmatic dependency on the previous kernel of the stream:
+// the grid may be scheduled while that kernel drains; the kernel itself must execute
+// griddepcontrol.wait (pdl_wait) before it touches anything its predecessor wrote.
+template <class... KArgs, class... Args>
+int launch_plain_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                     cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = pdl ? attr : nullptr; cfg.numAttrs = pdl ? 1 : 0;
+  if (smem > 16 * 1024)
+    MEP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  MEP_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
 }  // namespace mep

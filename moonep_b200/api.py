@@ -127,10 +127,11 @@ class OpsMixin:
         # planning's barrier already orders this op after every rank's previous one
         engine.launch_dispatch(st, hidden, weights, plans, fresh=fresh,
                                entry_barrier=(not fresh) and inter_rank_sync)
+        pdl = bool(getattr(self, "enable_pdl", False))      # the expansion is scheduled while dispatch drains
         if fresh:
-            engine.launch_dup_expand_fresh(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4)
+            engine.launch_dup_expand_fresh(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4, pdl)
         else:
-            engine.launch_dup_expand(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4)
+            engine.launch_dup_expand(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4, pdl)
         out_h, out_w = [], []
         for i in range(n):
             if zero_copy:
@@ -178,7 +179,7 @@ class OpsMixin:
         engine.launch_dup_reduce(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4)
         outs = [torch.empty(g.S, g.H, dtype=torch.bfloat16, device=s.device) for s in st]
         outw = [torch.empty(g.S, g.K, dtype=torch.float32, device=s.device) for s in st] if have_w else None
-        engine.launch_combine(st, plans, outs, outw, entry_barrier=True)
+        engine.launch_combine(st, plans, outs, outw, entry_barrier=True, pdl=bool(getattr(self, "enable_pdl", False)))
         return outs, outw
 
     # ---- prefetch / reduce

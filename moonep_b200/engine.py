@@ -200,11 +200,12 @@ def launch_dup_finalize(states, plans):
     _native.check(lib.mep_launch_dup_finalize(n, _pack(states), args, _native.cur_stream()), "dup_finalize")
 
 
-def launch_dup_expand_fresh(states, bufs, plans, num_blocks: int):
-    """Fresh dispatch: compact the staged duplicate groups into the plan and expand them, one launch."""
+def launch_dup_expand_fresh(states, bufs, plans, num_blocks: int, pdl: bool = False):
+    """Fresh dispatch: compact the staged duplicate groups into the plan and expand them, one launch.
+    ``pdl``: programmatic dependent launch behind the kernel queued just before on this stream."""
     lib = _native.load()
     _native.check(lib.mep_launch_dup_expand_fresh(len(states), _pack(states), _dup_args(states, bufs, plans),
-                                                  num_blocks, _native.cur_stream()), "dup_expand_fresh")
+                                                  num_blocks, 1 if pdl else 0, _native.cur_stream()), "dup_expand_fresh")
 
 
 def _dup_args(states, bufs, plans):
@@ -215,10 +216,10 @@ def _dup_args(states, bufs, plans):
     return args
 
 
-def launch_dup_expand(states, bufs, plans, num_blocks: int):
+def launch_dup_expand(states, bufs, plans, num_blocks: int, pdl: bool = False):
     lib = _native.load()
     _native.check(lib.mep_launch_dup_expand(len(states), _pack(states), _dup_args(states, bufs, plans),
-                                            num_blocks, _native.cur_stream()), "dup_expand")
+                                            num_blocks, 1 if pdl else 0, _native.cur_stream()), "dup_expand")
 
 
 def launch_dup_reduce(states, bufs, plans, num_blocks: int):
@@ -227,14 +228,14 @@ def launch_dup_reduce(states, bufs, plans, num_blocks: int):
                                             num_blocks, _native.cur_stream()), "dup_reduce")
 
 
-def launch_combine(states, plans, outs, out_weights, entry_barrier: bool = True):
+def launch_combine(states, plans, outs, out_weights, entry_barrier: bool = True, pdl: bool = False):
     lib = _native.load()
     n = len(states)
     args = (CombineArgs * n)()
     for i in range(n):
         ow = out_weights[i] if out_weights is not None else None
         args[i] = CombineArgs(ptr(plans[i].dst), ptr(outs[i]), ptr(ow), 1 if entry_barrier else 0)
-    _native.check(lib.mep_launch_combine(n, _pack(states), args, states[0].geo.num_sms, states[0].geo.H, _native.cur_stream()), "combine")
+    _native.check(lib.mep_launch_combine(n, _pack(states), args, states[0].geo.num_sms, 1 if pdl else 0, _native.cur_stream()), "combine")
 
 
 def launch_rank_sync(states):

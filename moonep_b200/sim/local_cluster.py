@@ -18,7 +18,7 @@ from ..parallel.symm import SymmetricHeap
 
 class LocalCluster(OpsMixin):
     def __init__(self, S, H, K, E, R, num_sms=4, token_padding=128, device="cuda:0", num_sms_dedup=8,
-                 budget_ms: float | None = None, push_combine: bool = False):
+                 budget_ms: float | None = None, push_combine: bool = False, enable_pdl: bool = True):
         assert 1 <= R <= MAX_VRANKS, f"LocalCluster hosts at most {MAX_VRANKS} ranks"
         self.geo = Geometry.make(S, H, K, E, R, token_padding, num_sms, push_combine=push_combine)
         self.device = torch.device(device)
@@ -27,6 +27,7 @@ class LocalCluster(OpsMixin):
         self._states = [engine.make_rank_state(self.geo, r, self.heap, self.device, bn) for r in range(R)]
         self._num_sms_dedup = num_sms_dedup
         self.R = R
+        self.enable_pdl = enable_pdl
 
     def dispatch(self, hidden, weights=None, topk=None, tpe=None, plans=None, *, inter_rank_sync=True,
                  zero_copy=False, router_weights_zero_copy=False):

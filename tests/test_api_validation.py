@@ -103,3 +103,17 @@ def test_pool_layout_and_description():
     text = describe_layout(epn, shapes, torch.bfloat16, True, world=4)
     for word in ("gate", "up", "down", "prefetch", "reduce", "compute", "[R=4, epn=3"):
         assert word in text
+
+
+def test_bench_keeps_stdout_for_the_result_line():
+    """bench.py prints exactly one line on stdout even if a library writes banners there."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import os, sys; sys.path.insert(0, %r); import bench; bench._reserve_stdout(); "
+            "print('banner from python'); os.write(1, b'banner from C\\n'); bench._emit('{\"ok\": 1}')" % root)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout == '{"ok": 1}\n'
+    assert "banner from python" in r.stderr and "banner from C" in r.stderr
