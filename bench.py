@@ -280,7 +280,8 @@ def run_ours(args):
         except Exception:      # noqa: BLE001
             pass
         blk.destroy()
-        os.environ.update(MOONEP_PUSH_COMBINE="0", MOONEP_OVERLAP_BACKWARD="0", MOONEP_DEFER_LAST_REDUCTION="0")
+        os.environ.update(MOONEP_PUSH_COMBINE="0", MOONEP_OVERLAP_BACKWARD="0", MOONEP_DEFER_LAST_REDUCTION="0",
+                          MOONEP_PDL="0")
         blk = MoEBlock(cfg, world, rank, num_sms=32, seed=0)
         if args.optimizer_in_backward:
             blk.fuse_optimizer(lr)

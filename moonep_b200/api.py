@@ -235,7 +235,7 @@ class Buffer(OpsMixin):
         assert isinstance(enable_pdl, bool), f"enable_pdl must be a bool, got {type(enable_pdl).__name__}"
         self.explicitly_destroy = explicitly_destroy
         self.comm_stream_priority = comm_stream_priority
-        self.enable_pdl = enable_pdl
+        self.enable_pdl = enable_pdl and os.environ.get("MOONEP_PDL", "1") != "0"   # MOONEP_PDL=0: plain launches
         self._destroyed = False
         self._states = []
         self._heap = None
