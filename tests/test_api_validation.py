@@ -117,3 +117,24 @@ def test_bench_keeps_stdout_for_the_result_line():
     assert r.returncode == 0, r.stderr
     assert r.stdout == '{"ok": 1}\n'
     assert "banner from python" in r.stderr and "banner from C" in r.stderr
+
+
+def test_grad_reduce_ring_geometry():
+    """Index arithmetic of grad_reduce's per-warp stage, restated on the host: with up to eight
+    replicas a unit takes ns*P of the 32 slots and the ring holds four units that never overlap;
+    beyond that one unit uses the stage alone (constants mirror csrc/device/grad_reduce.cu)."""
+    SLOTS, DEPTH = 32, 4
+    for ns in range(1, 200):
+        ring = ns * DEPTH <= SLOTS
+        P = max(1, min(8, SLOTS // (ns * DEPTH if ring else ns)))
+        if ring:
+            spans = [(r * ns * P, (r + 1) * ns * P) for r in range(DEPTH)]
+            assert spans[-1][1] <= SLOTS
+            assert all(spans[i][1] <= spans[i + 1][0] for i in range(DEPTH - 1))
+            # slot of (unit r, replica j, vector p) is unique
+            idx = {(r * ns * P + j * P + p) for r in range(DEPTH) for j in range(ns) for p in range(P)}
+            assert len(idx) == DEPTH * ns * P
+        else:
+            per_pass = min(ns, SLOTS)
+            assert per_pass * P <= SLOTS
+    assert [max(1, min(8, SLOTS // (ns * DEPTH))) for ns in (1, 2, 3, 4, 8)] == [8, 4, 2, 2, 1]
