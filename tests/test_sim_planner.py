@@ -182,3 +182,22 @@ def test_plan_fingerprints_agree_and_catch_divergence():
     import pickle
     again = pickle.loads(pickle.dumps(plans[0]))
     assert torch.equal(again.dst, plans[0].dst) and again.NvS == plans[0].NvS
+
+
+def test_workload_report_counts():
+    """The offline workload report: counters agree with the plan they are computed from."""
+    from moonep_b200.sim.report import report, workload
+    R, S, K, E, H, Hp = 4, 128, 4, 16, 256, 128
+    rep = report(R, S, K, E, H, Hp, 2.0, token_padding=16)
+    assert rep["redundant_slots"] == sum(rep["slots_sent_per_owner"]) and rep["max_slots_sent"] >= 1
+    assert 1.0 <= rep["distinct_dest_ranks_per_token"] <= min(K, R)
+    assert rep["NvS"] == -(-(S * K + 15 * 2 * (E // R)) // 16) * 16      # capacity rule, rounded up to the padding
+    # all-local routing: nothing crosses a link, K-1 of every K rows are duplicates
+    topk = np.stack([routing.pattern_topk("all_local", S, K, E, R, r)[0].numpy() for r in range(R)])
+    w = workload(plan_cluster(topk, E, 16), H, Hp)
+    assert w["dispatch_egress_MB_max"] == 0 and w["dispatch_us_at_link"] == 0
+    assert w["duplicate_rows_pct"] == 75.0 and w["redundant_slots"] == 0 and w["tokens_off_home_pct"] == 0
+    # all-remote routing: every token sends exactly one row to its neighbour
+    topk = np.stack([routing.pattern_topk("all_remote", S, K, E, R, r)[0].numpy() for r in range(R)])
+    w = workload(plan_cluster(topk, E, 16), H, Hp)
+    assert w["dispatch_egress_MB_max"] == round(S * H * 2 / 1e6, 1)
