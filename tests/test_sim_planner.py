@@ -201,3 +201,21 @@ def test_workload_report_counts():
     topk = np.stack([routing.pattern_topk("all_remote", S, K, E, R, r)[0].numpy() for r in range(R)])
     w = workload(plan_cluster(topk, E, 16), H, Hp)
     assert w["dispatch_egress_MB_max"] == round(S * H * 2 / 1e6, 1)
+
+
+@pytest.mark.parametrize("target", [0.5, 1.0, 2.0, 3.0])
+def test_skew_solver_hits_the_requested_maxvio(target):
+    """The routing generator's skew scale is solved so that the realised group-wide
+    maxvio = max_e(T_e) / mean_e(T_e) - 1 lands on the target; below the sampling-noise floor
+    it reports the floor instead."""
+    R, S, K, E = 8, 512, 8, 64
+    scale, realised = routing.solve_scale_for_maxvio(target, S, K, E, R, seed=0)
+    assert scale > 0 and abs(realised - target) <= max(0.05 * target, 0.02)
+    tot = sum(routing.softmax_topk(S, K, E, scale, 0, r)[2].long() for r in range(R))
+    assert abs(routing.maxvio(tot) - realised) < 1e-9
+    floor_scale, floor = routing.solve_scale_for_maxvio(0.01, S, K, E, R, seed=0)
+    assert floor_scale == 0.0 and 0.0 < floor < 0.5
+    # weights are a normalised top-k distribution and topk ids are distinct per token
+    topk, w, tpe = routing.softmax_topk(S, K, E, scale, 0, 3)
+    assert torch.allclose(w.sum(dim=1), torch.ones(S), atol=1e-5) and int(tpe.sum()) == S * K
+    assert all(len(set(row.tolist())) == K for row in topk[:32])
