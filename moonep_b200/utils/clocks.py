@@ -44,7 +44,7 @@ class ClockSampler:
             self._proc.wait(timeout=5)
         except Exception:
             self._proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         try:
             for line in open(self._path):
                 f = [x.strip() for x in line.split(",")]
@@ -54,6 +54,10 @@ class ClockSampler:
                     sm.append(float(f[1])); mx.append(float(f[2]))
                 except ValueError:
                     continue
+                try:
+                    pw.append(float(f[3]))
+                except ValueError:
+                    pw.append(None)
                 for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                     if v.lower().startswith("active"):
                         reasons.add(name)
@@ -63,7 +67,19 @@ class ClockSampler:
             except OSError:
                 pass
         if sm:
-            # "under load" = the upper half of the samples (idle samples before/after are dropped)
-            hot = sorted(sm)[len(sm) // 2:]
-            out.update(sm_mhz=statistics.median(hot), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(under_load(sm, pw)), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm))
         return out
+
+
+def under_load(sm, power):
+    """SM clock samples taken while the GPU was busy.  Busy = power draw of at least 60 % of the
+    highest draw seen (a power-capped GPU clocks DOWN under load, so the clock itself cannot tell
+    busy from idle); without usable power readings, the upper half of the clock samples."""
+    known = [p for p in power if p is not None]
+    if len(known) == len(sm) and known and max(known) > 0:
+        cut = 0.6 * max(known)
+        hot = [c for c, p in zip(sm, power) if p >= cut]
+        if hot:
+            return hot
+    return sorted(sm)[len(sm) // 2:]

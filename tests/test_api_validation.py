@@ -1,5 +1,7 @@
 """Host-only checks of argument validation (no GPU): num_sms is validated before any CUDA
 or process-group access, like the reference (tests/test_api_validation.py:8-86)."""
+import os
+
 import pytest
 
 from moonep_b200.api import validate_num_sms, num_sms_dedup_from_env
@@ -138,3 +140,31 @@ def test_grad_reduce_ring_geometry():
             per_pass = min(ns, SLOTS)
             assert per_pass * P <= SLOTS
     assert [max(1, min(8, SLOTS // (ns * DEPTH))) for ns in (1, 2, 3, 4, 8)] == [8, 4, 2, 2, 1]
+
+
+def test_clock_sampler_with_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """The sampler reads clocks and throttle reasons from nvidia-smi's CSV stream; "under load"
+    is decided by power draw, because a power-capped GPU clocks down when it is busy."""
+    import stat
+    import time
+    from moonep_b200.utils.clocks import ClockSampler, under_load
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text(
+        "#!/bin/bash\n"
+        "echo '0, 1965, 1965, 180.5, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active'\n"
+        "for i in 1 2 3 4 5 6; do\n"
+        "  echo '0, 1410, 1965, 995.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active'\n"
+        "done\n"
+        "echo '0, 1965, 1965, 210.0, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active'\n"
+        "sleep 30\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{tmp_path}:{os.environ['PATH']}")
+    s = ClockSampler(0, 20).start()
+    time.sleep(0.3)
+    out = s.stop()
+    assert out["samples"] == 8 and out["sm_max_mhz"] == 1965.0
+    assert out["sm_mhz"] == 1410.0, "the busy samples are the power-capped ones, not the idle 1965 MHz ones"
+    assert out["reasons"] == ["sw_power_cap"]
+    # no usable power reading: fall back to the upper half of the clock samples
+    assert under_load([300.0, 300.0, 1900.0, 1950.0], [None] * 4) == [1900.0, 1950.0]
+    assert under_load([1965.0, 1400.0, 1420.0], [100.0, 990.0, 1000.0]) == [1400.0, 1420.0]
