@@ -291,3 +291,6 @@ extern "C" int mep_launch_wait_probe(const MepRankCtx* ctx, const uint32_t* flag
   MepCtxPack P = {}; P.ctx[0] = ctx;
   return mep::launch_plain(mep::wait_probe_kernel, dim3(1, 1), dim3(32), 0, stream, P, flag, expected);
 }
+
+MEP_EXPORT_SIZEOF(CombineArgs, mep::CombineArgs)
+MEP_EXPORT_SIZEOF(PushReduceArgs, mep::PushReduceArgs)

@@ -378,3 +378,8 @@ extern "C" int mep_launch_dup_expand_fresh(int nv, const MepRankCtx* const* ctxs
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
   return mep::launch_plain_pdl(mep::dup_expand_fresh_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, pdl != 0, P, A);
 }
+
+MEP_EXPORT_SIZEOF(DispatchArgs, mep::DispatchArgs)
+MEP_EXPORT_SIZEOF(DupFinalizeArgs, mep::DupFinalizeArgs)
+MEP_EXPORT_SIZEOF(DupArgs, mep::DupArgs)
+MEP_EXPORT_SIZEOF(DupFreshArgs, mep::DupFreshArgs)

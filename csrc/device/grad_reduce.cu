@@ -232,3 +232,5 @@ extern "C" int mep_launch_grad_reduce(int nv, const MepRankCtx* const* ctxs, con
   return mep::launch_cooperative(mep::grad_reduce_kernel, dim3(num_sms, nv), dim3(mep::kRedThreads), smem,
                                  stream, false, P, A);
 }
+
+MEP_EXPORT_SIZEOF(GradReduceArgs, mep::GradReduceArgs)

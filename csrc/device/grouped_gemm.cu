@@ -468,3 +468,5 @@ extern "C" int mep_grouped_gemm(int mode, const void* a, int64_t a_rows, int64_t
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;
 }
+
+MEP_EXPORT_SIZEOF(GemmArgs, mep::GemmArgs)

@@ -513,3 +513,5 @@ extern "C" int mep_launch_planning(int nv, const MepRankCtx* const* ctxs, const 
 extern "C" int mep_planning_is_fast(int E, int R) {
   return (E <= mep::kFastMaxE && (long long)E * R <= mep::kFastMaxER) ? 1 : 0;
 }
+
+MEP_EXPORT_SIZEOF(PlanArgs, mep::PlanArgs)

@@ -95,3 +95,5 @@ extern "C" int mep_launch_prefetch(int nv, const MepRankCtx* const* ctxs, const 
   return mep::launch_cooperative(mep::prefetch_kernel, dim3(num_sms, nv), dim3(mep::kCopyThreads), smem,
                                  stream, false, P, A);
 }
+
+MEP_EXPORT_SIZEOF(PrefetchArgs, mep::PrefetchArgs)

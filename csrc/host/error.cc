@@ -18,3 +18,6 @@ extern "C" long long mep_launch_count() { return mep::g_launches.load(); }
 
 extern "C" const char* mep_last_error() { return mep::last_error().c_str(); }
 extern "C" int mep_abi_version() { return 1; }
+
+MEP_EXPORT_SIZEOF(MepRankCtx, MepRankCtx)
+MEP_EXPORT_SIZEOF(MepStatus, MepStatus)

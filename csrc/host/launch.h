@@ -9,6 +9,10 @@
 #include <string>
 #include "../mep_types.h"
 
+// Exports sizeof(type) as mep_sizeof_<name>() so that the Python side can check its ctypes
+// mirror of an argument struct against the compiled layout.
+#define MEP_EXPORT_SIZEOF(name, type) extern "C" int mep_sizeof_##name() { return (int)sizeof(type); }
+
 namespace mep {
 
 std::string& last_error();

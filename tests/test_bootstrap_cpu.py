@@ -155,3 +155,23 @@ def test_native_library_loads_without_gpu():
     lib = _native.load()
     assert lib.mep_abi_version() >= 1
     assert isinstance(lib.mep_launch_count(), int)
+
+
+def test_ctypes_mirrors_match_the_compiled_struct_sizes():
+    """Every argument struct that Python fills through ctypes has the size the compiler gave its
+    C++ definition (the library exports sizeof for each); a field added on one side only shows up
+    here instead of as a corrupted kernel argument."""
+    import ctypes as C
+    from moonep_b200 import _native
+    from moonep_b200.ops.grouped_gemm import GemmArgs
+    lib = _native.load()
+    mirrors = {
+        "MepRankCtx": _native.MepRankCtx, "MepStatus": _native.MepStatus, "PlanArgs": _native.PlanArgs,
+        "DispatchArgs": _native.DispatchArgs, "DupFinalizeArgs": _native.DupFinalizeArgs,
+        "DupArgs": _native.DupArgs, "DupFreshArgs": _native.DupArgs, "CombineArgs": _native.CombineArgs,
+        "PushReduceArgs": _native.PushReduceArgs, "PrefetchArgs": _native.PrefetchArgs,
+        "GradReduceArgs": _native.GradReduceArgs, "GemmArgs": GemmArgs,
+    }
+    for name, cls in mirrors.items():
+        native = getattr(lib, f"mep_sizeof_{name}")()
+        assert C.sizeof(cls) == native, f"{name}: ctypes {C.sizeof(cls)} bytes, compiled {native} bytes"
