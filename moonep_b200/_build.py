@@ -3,6 +3,10 @@
 ``python -m moonep_b200._build`` compiles every source under ``csrc/`` into
 ``moonep_b200/_lib/libmoonep_b200.so``.  Objects are cached by source mtime; files are
 compiled in parallel.  nvcc cross-compiles without a GPU.
+
+Counterpart of the reference's ``setup.py`` (setup.py:24-77 there: one ``CUDAExtension`` of
+host-only code with torch's default architectures); here every kernel is device code built for
+``sm_100a`` explicitly and the result stays in the source tree.
 """
 
 from __future__ import annotations

@@ -3,6 +3,10 @@
 The structs mirror ``csrc/mep_types.h`` and the per-kernel argument structs field by
 field.  Every native function returns 0 on success; on failure ``check`` raises
 ``MoonEPNativeError`` with the library's thread-local message.
+
+Takes the place of the reference's pybind11 module ``moonep._C`` (csrc/bindings.cu:13-53), which
+exposes only the symmetric-memory calls; here the same library also carries every kernel
+launcher, and it loads without a CUDA driver (the driver API is resolved at first use).
 """
 
 from __future__ import annotations

@@ -5,6 +5,10 @@ Conventions: ``x`` is the dispatched token matrix ``[NvS, in]`` in VM-group orde
 ``cu_seqlens[G]`` holds each group's padded end row (multiples of 128); weights are
 ``[G, in, out]`` bf16 (G = 2*epn: local experts then prefetch slots).  All functions launch
 on the current stream and fail loudly if the native library is missing.
+
+The reference ships no GEMM: it hands ``hidden_nvsh``, ``cu_seqlens`` and the ``[2*epn, H, H']``
+compute view to the integrating framework's grouped GEMM (README.md:45, 54 of the reference;
+moonep/dispatch.py:454 names DeepGEMM as the consumer).  This module is that consumer.
 """
 
 from __future__ import annotations
