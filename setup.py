@@ -1,6 +1,6 @@
 """Packaging of moonep_b200.
 
-``pip install --no-build-isolation .`` (or ``-e .``) compiles the native library for sm_100a with
+``pip install --no-build-isolation .`` compiles the native library for sm_100a with
 nvcc and ships it inside the package (``moonep_b200/_lib/libmoonep_b200.so``).  The library is
 plain ``extern "C"`` code loaded with ctypes, so there is no Python extension module to link
 against a particular torch build; torch is only a run-time dependency.  Counterpart of the
