@@ -91,13 +91,17 @@ __global__ void __launch_bounds__(256) dup_reduce_kernel(MepCtxPack P, DupArgsPa
   char* base = (char*)a.buf;
   for (int g = gw; g < ng; g += nw) {
     const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
-    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
+    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) {
+      if (c.checked && lane == 0) report(c, MEP_ERR_BOUNDS, MEP_K_DUP_REDUCE, 1, g, (uint32_t)p, (uint32_t)n);
+      continue;
+    }
     // lane 0 holds the primary row, lanes 1..n the duplicates in table order
     const char* myrow = nullptr;
     if (lane == 0) myrow = base + (size_t)p * row_bytes;
     else if (lane <= n) {
       const int q = a.dup_loffs[st + lane - 1];
       if ((unsigned)q < (unsigned)c.NvS) myrow = base + (size_t)q * row_bytes;
+      else if (c.checked) report(c, MEP_ERR_BOUNDS, MEP_K_DUP_REDUCE, 2, g, (uint32_t)q, (uint32_t)c.NvS);
     }
     const unsigned rows = __ballot_sync(0xffffffffu, myrow != nullptr);
     reduce_rows_auto<false>(myrow, rows, __popc(rows), base + (size_t)p * row_bytes, nvec, lane);
@@ -155,15 +159,25 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, 
     if (lane < K) {
       const int raw = dval >= 0 ? dval : -dval - 1;
       const int d = raw / NvS, loff = raw - d * NvS;
-      if (a.out_weights)
-        a.out_weights[(size_t)s * K + lane] = __ldcg((const float*)peer_ptr(c, d, c.off_weights) + loff);
-      if (dval >= 0) myrow = peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes;
+      if (d >= c.R) {         // corrupt or foreign plan: report, form no address from the entry
+        report(c, MEP_ERR_BOUNDS, MEP_K_COMBINE, 20, s, (uint32_t)raw, (uint32_t)(c.R * NvS));
+        if (a.out_weights) a.out_weights[(size_t)s * K + lane] = 0.f;
+      } else {
+        if (a.out_weights)
+          a.out_weights[(size_t)s * K + lane] = __ldcg((const float*)peer_ptr(c, d, c.off_weights) + loff);
+        if (dval >= 0) myrow = peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes;
+      }
     }
     const unsigned prim = __ballot_sync(0xffffffffu, myrow != nullptr);
     const int np = __popc(prim);
+    char* orow = (char*)a.out + (size_t)s * row_bytes;
+    if (np == 0) {            // no valid primary row (only possible with a corrupt plan): the token's output is zero
+      if (lane == 0) report(c, MEP_ERR_BOUNDS, MEP_K_COMBINE, 21, s, 0u, (uint32_t)K);
+      for (int v = lane; v < nvec; v += 32) st_na_v4(orow + (size_t)v * 16, make_int4(0, 0, 0, 0));
+      continue;
+    }
     int per = kCombSlots / np;                       // vectors per lane and row in one pass
     if (per > vpl) per = vpl;
-    char* orow = (char*)a.out + (size_t)s * row_bytes;
     for (int j0 = 0; j0 < vpl; j0 += per) {
       const int nj = vpl - j0 < per ? vpl - j0 : per;
       unsigned rest = prim;

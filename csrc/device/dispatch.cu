@@ -93,6 +93,10 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       int lo = 0, hi = ngroups - 1;                 // last g with s_zpre[g] <= rr
       while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (s_zpre[mid] <= (int)rr) lo = mid; else hi = mid - 1; }
       const int prow = s_zstart[lo] + ((int)rr - s_zpre[lo]);
+      if ((unsigned)prow >= (unsigned)NvS) {      // a corrupt zero_fill_ranges table must not reach memory
+        if (lane == 0) report(c, MEP_ERR_BOUNDS, MEP_K_DISPATCH, 40, lo, (uint32_t)prow, (uint32_t)NvS);
+        continue;
+      }
       char* row = hid + (size_t)prow * row_bytes;
       for (int v = lane; v < vec_per_row; v += 32) st_v4(row + (size_t)v * 16, z);
       if (lane == 0 && a.weights) wts[prow] = 0.f;
@@ -163,13 +167,23 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
+      // a plan entry that names a rank outside the group (corrupt or foreign plan) is reported and
+      // dropped before any address is formed from it
+      bool entry_ok = lane < K;
+      if (entry_ok) {
+        const int raw = dval >= 0 ? dval : -dval - 1;
+        if (raw / NvS >= c.R) {
+          report(c, MEP_ERR_BOUNDS, MEP_K_DISPATCH, 41, s, (uint32_t)raw, (uint32_t)(c.R * NvS));
+          entry_ok = false; dval = -1;          // negative: the send loop below skips it as well
+        }
+      }
       // route weights: every entry (primary or duplicate) owns a slot on its destination
-      if (lane < K && a.weights) {
+      if (entry_ok && a.weights) {
         const int raw = dval >= 0 ? dval : -dval - 1;
         const int d = raw / NvS, loff = raw - d * NvS;
         ((float*)peer_ptr(c, d, c.off_weights))[loff] = w;
       }
-      if (lane < K && a.srcinfo_off) {
+      if (entry_ok && a.srcinfo_off) {
         const int raw = dval >= 0 ? dval : -dval - 1;
         const int d = raw / NvS, loff = raw - d * NvS;
         ((int*)peer_ptr(c, d, (size_t)a.srcinfo_off))[loff] = c.rank * (S * K) + s * K + lane;
@@ -246,11 +260,17 @@ __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPa
   char* base = (char*)a.buf;
   for (int g = gw; g < ng; g += nw) {
     const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
-    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
+    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) {
+      if (c.checked && lane == 0) report(c, MEP_ERR_BOUNDS, MEP_K_EXPAND, 1, g, (uint32_t)p, (uint32_t)n);
+      continue;
+    }
     const char* src = base + (size_t)p * row_bytes;
     // duplicate offsets of this group live in lanes 0..n-1
     int myq = -1;
-    if (lane < n) { myq = a.dup_loffs[st + lane]; if ((unsigned)myq >= (unsigned)c.NvS) myq = -1; }
+    if (lane < n) {
+      myq = a.dup_loffs[st + lane];
+      if ((unsigned)myq >= (unsigned)c.NvS) { if (c.checked) report(c, MEP_ERR_BOUNDS, MEP_K_EXPAND, 2, g, (uint32_t)myq, (uint32_t)c.NvS); myq = -1; }
+    }
     for (int v0 = 0; v0 < nvec; v0 += 128) {          // 4 x 16-byte loads in flight per lane
       int4 x[4];
 #pragma unroll

@@ -16,8 +16,7 @@ struct GemmArgs {
   int32_t accumulate;          // WGRAD: 1 -> out += acc, 0 -> out = acc
   int32_t g_begin, g_end;      // only groups in [g_begin, g_end) are computed
   int32_t zero_empty_below;    // WGRAD without accumulate: empty groups g < this get zeros
-  int32_t diag;                // diagnostics only (results invalid): 1 = MMA does not wait for operands and no
-                               // TMA loads are issued, 2 = epilogue discards the accumulators
+  int32_t reserved0;
   void* out;                   // bf16 [rows, ldo]; WGRAD: fp32 [G, M_w, N]
   void* out2;                  // GATE_UP: optional bf16 [rows, 2N] pre-activations (gate | up)
   const float* row_scale;      // GATE_UP / DOWN: optional per-row factor [rows]

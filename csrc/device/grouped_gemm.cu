@@ -135,7 +135,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tq::Strided seq{(int)blockIdx.x, (int)gridDim.x, ntiles};
       for (int t; !s_abort && (t = dyn ? sched.next(args.budget_ns) : seq.next()) != -1;) {
         if (t == -2) { fail(5, sched.n); break; }
-        if (args.diag & 1) continue;
         get_tile(t, gcur, ti);
         for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
@@ -194,7 +193,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         bool ok = true;
         for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
-          if (!(args.diag & 1) && !mbar_wait_bounded(&full_bar[s], ph, args.budget_ns)) { fail(3, t); ok = false; break; }
+          if (!mbar_wait_bounded(&full_bar[s], ph, args.budget_ns)) { fail(3, t); ok = false; break; }
           tc::fence_after_sync();
           const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kABytes;
 #pragma unroll
@@ -203,7 +202,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             const uint64_t bd = B_MN ? tc::smem_desc(sb + k * 2048, kAtomBytes, 1024) : tc::smem_desc(sb + k * 32, 16, 1024);
             tc::mma_bf16(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
           }
-          if (!(args.diag & 1)) tc::mma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
+          tc::mma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
         }
         if (!ok) break;
         tc::mma_commit(&tfull_bar[acc]);      // accumulator complete
@@ -244,9 +243,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (!ok) { if (lane == 0) fail(4, t); break; }
       tc::fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * kBN;
-      if (args.diag & 2) {
-        // diagnostics: hand the accumulator back untouched
-      } else if (MODE == GEMM_GATE_UP) {
+      if (MODE == GEMM_GATE_UP) {
         const size_t row = (size_t)ti.row0 + r_in_tile;
         __nv_bfloat16* orow = (__nv_bfloat16*)args.out + row * args.ldo + ti.n0;
         __nv_bfloat16* grow = args.out2 ? (__nv_bfloat16*)args.out2 + row * (size_t)(2 * args.N) + ti.n0 : nullptr;

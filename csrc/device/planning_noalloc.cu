@@ -58,6 +58,12 @@ extern "C" int mep_plan_single_rank_noalloc(const int32_t* topk, const int32_t* 
               "noalloc: null input or output pointer");
   const long long nvs_ll = up((size_t)N + (size_t)(token_padding - 1) * 2 * E, token_padding);
   MEP_REQUIRE(nvs_ll < (1ll << 24), "noalloc: padded slot count %lld exceeds 2^24", nvs_ll);
+  // The rank context below is copied from this stack frame with an asynchronous copy: a stream
+  // capture would record the frame's address and replay the copy after the frame is gone.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  MEP_CUDA_CHECK(cudaStreamIsCapturing(stream, &cap));
+  MEP_REQUIRE(cap == cudaStreamCaptureStatusNone, "noalloc: the stream is being captured; this entry point only runs on a "
+              "stream that executes its work directly");
 
   unsigned char* base = nullptr;
   if (scratch_base(&base)) return -1;

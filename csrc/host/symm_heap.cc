@@ -142,8 +142,12 @@ int mep_chunk_release(void* chunk) {
 }
 
 // Map all ranks' chunks contiguously. `shareables` is world x 64 bytes (fd ints or fabric
-// handles; entry `my_rank` is ignored and the local chunk's own handle is used). Imported
-// fds are closed here. On failure everything mapped so far is undone.
+// handles; entry `my_rank` is not imported: the local chunk's own handle is used). With fd
+// handles this call CONSUMES every descriptor of the table, on success and on failure alike:
+// peers' descriptors are closed once imported, entry `my_rank` (the copy of the caller's own
+// descriptor that came back through the exchange; negative = none) is closed unused, and after a
+// failed import the descriptors of the ranks not reached yet are closed too. On failure
+// everything mapped so far is undone.
 int mep_map_all(int dev, int world, int my_rank, void* local_chunk, const unsigned char* shareables,
                 void** mapping_out, unsigned long long* base_out) {
   const DriverApi* d = driver(); if (!d) return -1;
@@ -160,9 +164,14 @@ int mep_map_all(int dev, int world, int my_rank, void* local_chunk, const unsign
   CUmemAccessDesc acc = {};
   acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE; acc.location.id = dev; acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
   const char* what = "";
+  int consumed = 0;      // fd handles: table entries [0, consumed) have been closed
   for (int i = 0; i < world && r == CUDA_SUCCESS; ++i) {
     CUmemGenericAllocationHandle h; bool imported = false;
-    if (i == my_rank) { h = lc->handle; }
+    if (i == my_rank) {
+      h = lc->handle;
+      if (lc->kind != kHandleFabric) { int fd; memcpy(&fd, shareables + 64 * i, sizeof fd); if (fd >= 0) close(fd); }
+      consumed = i + 1;
+    }
     else if (lc->kind == kHandleFabric) {
       CUmemFabricHandle fh; memcpy(&fh, shareables + 64 * i, sizeof fh);
       r = d->MemImportFromShareableHandle(&h, &fh, CU_MEM_HANDLE_TYPE_FABRIC); what = "import(fabric)"; imported = r == CUDA_SUCCESS;
@@ -171,6 +180,7 @@ int mep_map_all(int dev, int world, int my_rank, void* local_chunk, const unsign
       r = d->MemImportFromShareableHandle(&h, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
       what = "import(fd)"; imported = r == CUDA_SUCCESS;
       close(fd);
+      consumed = i + 1;
     }
     if (r != CUDA_SUCCESS) break;
     r = d->MemMap(m->base + (size_t)i * cb, cb, 0, h, 0); what = "map";
@@ -179,6 +189,8 @@ int mep_map_all(int dev, int world, int my_rank, void* local_chunk, const unsign
   }
   if (r == CUDA_SUCCESS) { r = d->MemSetAccess(m->base, cb * world, &acc, 1); what = "set_access"; }
   if (r != CUDA_SUCCESS) {
+    if (lc->kind != kHandleFabric)
+      for (int i = consumed; i < world; ++i) { int fd; memcpy(&fd, shareables + 64 * i, sizeof fd); if (fd >= 0) close(fd); }
     for (int i = 0; i < world; ++i) if (m->mapped[i]) d->MemUnmap(m->base + (size_t)i * cb, cb);
     d->MemAddressFree(m->base, cb * world);
     delete m;

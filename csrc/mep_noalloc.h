@@ -41,8 +41,11 @@ extern "C" {
 //  * Calls nothing that allocates: no cudaMalloc/cudaFree, no library allocator. The launch is
 //    asynchronous on `stream`; outputs are valid once the stream reaches that point.
 //  * The FIRST call on each device resolves the device address of the work space (one
-//    cudaGetSymbolAddress with that device current). Make that first call outside of any
-//    stream capture.
+//    cudaGetSymbolAddress with that device current).
+//  * A call on a stream that is being captured is rejected (returns -1, nothing is recorded):
+//    the rank context travels to the device in an asynchronous copy from the caller's stack,
+//    which a captured graph would replay from a dead frame. Call it on a stream that executes
+//    its work directly.
 //  * All calls on a device share the one work space, which keeps the previous call's contents;
 //    the entry point clears the words that must start at zero itself. Two calls whose kernels
 //    can overlap on the GPU (different streams, no ordering) race on it: serialise them.

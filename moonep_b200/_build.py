@@ -44,8 +44,6 @@ def nvcc_path() -> str | None:
 
 def _compile(src: Path, obj: Path, verbose: bool):
     cmd = [nvcc_path(), *ARCH, *COMMON, "-c", str(src), "-o", str(obj)]
-    if os.environ.get("MOONEP_CHECKED") == "1":
-        cmd.insert(1, "-DMOONEP_CHECKED=1")
     if os.environ.get("MOONEP_POLL_SLEEP_NS"):
         cmd.insert(1, "-DMEP_POLL_SLEEP_NS=" + str(int(os.environ["MOONEP_POLL_SLEEP_NS"])))
     if verbose:

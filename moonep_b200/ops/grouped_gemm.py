@@ -28,7 +28,7 @@ _sm_cache: dict = {}
 class GemmArgs(C.Structure):
     _fields_ = [("cu_seqlens", C.c_void_p), ("G", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
                 ("M_w", C.c_int32), ("b_group_rows", C.c_int32), ("accumulate", C.c_int32),
-                ("g_begin", C.c_int32), ("g_end", C.c_int32), ("zero_empty_below", C.c_int32), ("diag", C.c_int32),
+                ("g_begin", C.c_int32), ("g_end", C.c_int32), ("zero_empty_below", C.c_int32), ("reserved0", C.c_int32),
                 ("out", C.c_void_p), ("out2", C.c_void_p), ("row_scale", C.c_void_p), ("ldo", C.c_int64),
                 ("status", C.c_void_p), ("budget_ns", C.c_uint64), ("sched", C.c_void_p),
                 ("push_info", C.c_void_p), ("push_base", C.c_void_p), ("push_wbase", C.c_void_p),
@@ -125,7 +125,6 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
     args.b_group_rows, args.accumulate = b_group_rows, 1 if accumulate else 0
     args.g_begin, args.g_end = g0, g1
     args.zero_empty_below = zero_empty_below
-    args.diag = int(os.environ.get("MOONEP_GEMM_DIAG", "0"))
     args.out, args.out2 = out.data_ptr(), _native.ptr(out2)
     args.row_scale, args.ldo = _native.ptr(row_scale), ldo
     args.status = _status(a.device).data_ptr()

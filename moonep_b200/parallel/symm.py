@@ -173,6 +173,8 @@ class SymmetricHeap:
         my_fd = -1
         try:
             table = (C.c_ubyte * (64 * h.world))()
+            # fd handles: mep_map_all consumes (closes) every descriptor of the table, including the copy
+            # of this rank's own descriptor that the exchange delivered back in entry [rank]
             if kind == HANDLE_FABRIC:
                 blobs = _all_gather_bytes(bytes(share), group)
                 for i, b in enumerate(blobs):

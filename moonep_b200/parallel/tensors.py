@@ -166,7 +166,7 @@ def create_single_owner_tensor(shape, dtype: torch.dtype, owner: int = 0, group=
             C.memmove(recv, int(fds[owner]).to_bytes(4, "little", signed=True), 4)
     try:
         if rank == owner:
-            table = (C.c_ubyte * 64)()
+            table = (C.c_ubyte * 64)(0xFF, 0xFF, 0xFF, 0xFF)      # fd -1: the own entry carries no descriptor
             _native.check(lib.mep_map_all(dev.index, 1, 0, chunk, table, C.byref(mapping), C.byref(base)), "map own chunk")
         else:
             _native.check(lib.mep_map_remote_one(dev.index, kind, nbytes, recv, C.byref(mapping), C.byref(base)),

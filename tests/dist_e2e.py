@@ -59,6 +59,15 @@ def main():
     S, H, K, epn, pad = 256, 1024, 4, 8, 32
     E = R * epn
     Hp = 128
+    # descriptor accounting: creating and destroying a Buffer (handle exchange over unix sockets,
+    # imports, mappings) must leave no file descriptor open
+    warm = Buffer(S, H, K, E, R, num_sms=16, token_padding=pad)     # first use opens library-internal files
+    warm.destroy()
+    fds_before = len(os.listdir("/proc/self/fd"))
+    probe = Buffer(S, H, K, E, R, num_sms=16, token_padding=pad)
+    probe.destroy()
+    fds_after = len(os.listdir("/proc/self/fd"))
+    chk(fds_after == fds_before, f"Buffer create + destroy leaked {fds_after - fds_before} file descriptors")
     buf = Buffer(S, H, K, E, R, num_sms=16, token_padding=pad)
     if rank == 0:
         print(f"[dist_e2e] multicast alias {'active' if buf._heap.mc_base else 'off'}", flush=True)

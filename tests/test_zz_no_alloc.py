@@ -27,7 +27,7 @@ def _regular_plan(S, K, E, pad, topk, tpe):
     return plan, cu
 
 
-def _noalloc_plan(lib, S, K, E, pad, topk, tpe):
+def _noalloc_plan(lib, S, K, E, pad, topk, tpe, check_free=False):
     i32 = dict(dtype=torch.int32, device="cuda")
     dst = torch.full((S * K,), 123456, **i32)
     cu = torch.full((2 * E,), 123456, **i32)
@@ -35,6 +35,8 @@ def _noalloc_plan(lib, S, K, E, pad, topk, tpe):
     etc = torch.full((E,), 123456, **i32)
     stats = torch.full((2,), 123456, **i32)
     before = torch.cuda.memory_allocated()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = lib.mep_plan_single_rank_noalloc(
         C.c_void_p(topk.data_ptr()), C.c_void_p(tpe.data_ptr()), S, K, E, pad,
         C.c_void_p(dst.data_ptr()), C.c_void_p(cu.data_ptr()), C.c_void_p(zfr.data_ptr()),
@@ -43,6 +45,11 @@ def _noalloc_plan(lib, S, K, E, pad, topk, tpe):
     assert rc == 0, lib.mep_last_error().decode()
     assert torch.cuda.memory_allocated() == before
     torch.cuda.synchronize()
+    # the driver's own count of free device memory sees raw cudaMalloc calls as well, which torch's
+    # counter does not; only checked once the kernel's code is resident (the first call of a process
+    # loads it, which takes device memory)
+    if check_free:
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
     return dst, cu, zfr, etc, stats
 
 
@@ -56,7 +63,7 @@ def test_noalloc_planner_matches_regular(first, second, cuda_device):
         topk = torch.randint(0, E, (S, K), dtype=torch.int32, device="cuda", generator=g)
         tpe = torch.zeros(E, dtype=torch.int32, device="cuda")
         tpe.scatter_add_(0, topk.reshape(-1).long(), torch.ones(S * K, dtype=torch.int32, device="cuda"))
-        dst, cu, zfr, etc, stats = _noalloc_plan(lib, S, K, E, pad, topk.reshape(-1).contiguous(), tpe)
+        dst, cu, zfr, etc, stats = _noalloc_plan(lib, S, K, E, pad, topk.reshape(-1).contiguous(), tpe, check_free=call > 0)
         plan, cu_ref = _regular_plan(S, K, E, pad, topk.reshape(-1).contiguous(), tpe)
         assert torch.equal(dst, plan.dst), f"call {call}: dst differs"
         assert torch.equal(cu, cu_ref), f"call {call}: cu_seqlens differs"
@@ -75,3 +82,28 @@ def test_noalloc_rejects_oversize(cuda_device):
     assert b"exceeds the built-in work space" in lib.mep_last_error()
     assert lib.mep_plan_single_rank_noalloc(p, p, 8, 1, 2048, 1, p, p, p, p, p, None) == -1
     assert b"max 1024 experts" in lib.mep_last_error()
+
+
+def test_noalloc_rejects_a_capturing_stream(cuda_device):
+    """Under stream capture the copy of the rank context would be replayed from a dead stack frame, so
+    the entry point refuses: nothing is recorded and the capture stays valid."""
+    from moonep_b200 import _native
+    lib = _native.load()
+    lib.mep_plan_single_rank_noalloc.restype = C.c_int
+    S, K, E, pad = 64, 2, 8, 16
+    topk = torch.randint(0, E, (S * K,), dtype=torch.int32, device="cuda")
+    tpe = torch.bincount(topk.long(), minlength=E).to(torch.int32)
+    outs = [torch.zeros(n, dtype=torch.int32, device="cuda") for n in (S * K, 2 * E, 4 * E, E, 2)]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        graph.capture_begin()
+        try:
+            rc = lib.mep_plan_single_rank_noalloc(C.c_void_p(topk.data_ptr()), C.c_void_p(tpe.data_ptr()), S, K, E, pad,
+                                                  *[C.c_void_p(o.data_ptr()) for o in outs], C.c_void_p(side.cuda_stream))
+            msg = lib.mep_last_error()
+        finally:
+            graph.capture_end()
+    assert rc == -1 and b"being captured" in msg
+    torch.cuda.synchronize()
