@@ -281,7 +281,7 @@ def run_ours(args):
             pass
         blk.destroy()
         os.environ.update(MOONEP_PUSH_COMBINE="0", MOONEP_OVERLAP_BACKWARD="0", MOONEP_DEFER_LAST_REDUCTION="0",
-                          MOONEP_PDL="0")
+                          MOONEP_PDL="0", MOONEP_READY_FLAGS="0")
         blk = MoEBlock(cfg, world, rank, num_sms=32, seed=0)
         if args.optimizer_in_backward:
             blk.fuse_optimizer(lr)

@@ -150,6 +150,8 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, 
   if (a.entry_barrier) { if (!cross_rank_barrier(c, nb, 2, MEP_K_COMBINE, 10)) return; }
   if (tid == 0) trace_mark(c, MEP_K_COMBINE, 2);
 
+  if (tid == 0 && blockIdx.x == 0) count(c, MEP_CNT_COMBINES, 1);
+  int pulled = 0;
   const uint32_t stage = smem_u32(smem) + (uint32_t)warp * (kCombSlots * 32 * 16);
   const unsigned char* stage_g = smem + (size_t)warp * (kCombSlots * 32 * 16);
   for (int s = blockIdx.x * kCombWarps + warp; s < S; s += nb * kCombWarps) {
@@ -176,30 +178,52 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, 
       for (int v = lane; v < nvec; v += 32) st_na_v4(orow + (size_t)v * 16, make_int4(0, 0, 0, 0));
       continue;
     }
-    int per = kCombSlots / np;                       // vectors per lane and row in one pass
+    pulled += np;
+    // One pass moves `per` 16-byte vectors per lane from EVERY row of the token into the warp's stage,
+    // then sums them. With up to kCombSlots / 2 rows the stage is split in two halves and pass p + 1
+    // is already in flight while pass p is summed, so the warp always has copies outstanding.
+    const bool pipelined = np <= kCombSlots / 2;
+    int per = (pipelined ? kCombSlots / 2 : kCombSlots) / np;
     if (per > vpl) per = vpl;
-    for (int j0 = 0; j0 < vpl; j0 += per) {
-      const int nj = vpl - j0 < per ? vpl - j0 : per;
+    const int npass = (vpl + per - 1) / per;
+    auto issue = [&](int p) {
+      const int j0 = p * per, nj = vpl - j0 < per ? vpl - j0 : per;
+      const uint32_t base = stage + (pipelined ? (uint32_t)(p & 1) * (kCombSlots / 2 * 32 * 16) : 0u);
       unsigned rest = prim;
       for (int r = 0; r < np; ++r) {
         const int src = __ffs(rest) - 1; rest &= rest - 1;
         const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)myrow, src);
         for (int j = 0; j < nj; ++j) {
           const int v = (j0 + j) * 32 + lane;
-          if (v < nvec) cp_async16(stage + (uint32_t)((r * per + j) * 32 + lane) * 16, rp + (size_t)v * 16);
+          if (v < nvec) cp_async16(base + (uint32_t)((r * per + j) * 32 + lane) * 16, rp + (size_t)v * 16);
         }
       }
-      cp_async_commit_wait_all();
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto consume = [&](int p) {
+      const int j0 = p * per, nj = vpl - j0 < per ? vpl - j0 : per;
+      const unsigned char* base = stage_g + (pipelined ? (size_t)(p & 1) * (kCombSlots / 2 * 32 * 16) : 0);
       for (int j = 0; j < nj; ++j) {
         const int v = (j0 + j) * 32 + lane;
         if (v >= nvec) continue;
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int r = 0; r < np; ++r)
-          acc_bf16x8(acc, *reinterpret_cast<const int4*>(stage_g + (size_t)((r * per + j) * 32 + lane) * 16));
+          acc_bf16x8(acc, *reinterpret_cast<const int4*>(base + (size_t)((r * per + j) * 32 + lane) * 16));
         st_na_v4(orow + (size_t)v * 16, pack_bf16x8(acc));
+      }
+    };
+    if (!pipelined) {
+      for (int p = 0; p < npass; ++p) { issue(p); asm volatile("cp.async.wait_group 0;" ::: "memory"); consume(p); }
+    } else {
+      issue(0);
+      for (int p = 0; p < npass; ++p) {
+        if (p + 1 < npass) { issue(p + 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        consume(p);
       }
     }
   }
+  if (lane == 0 && pulled) count(c, MEP_CNT_ROWS_PULLED, (unsigned long long)pulled);
 }
 
 // ------------------------------------------------------------------ push-combine: local reduction

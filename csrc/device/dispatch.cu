@@ -12,28 +12,10 @@
 //  * a spare warp per CTA clears the padding rows of the local shard meanwhile.
 // Exit: one cross-rank barrier publishes all remote writes.
 #include "prims.cuh"
+#include "dispatch_args.h"
 #include "../host/launch.h"
 
 namespace mep {
-
-struct DispatchArgs {
-  const __nv_bfloat16* hidden;   // [S, H] local tokens
-  const float* weights;          // [S, K] or null
-  const int32_t* dst;            // [N] plan
-  const int32_t* zero_fill;      // [2epn, 2] plan
-  int32_t fresh;                 // non-zero: publish duplicate-table counts to the peers. 1 / 2: the planner used
-                                 // send_cnt half 0 / 1; 3: the half the fast planner's device-side epoch names
-  int32_t entry_barrier;         // 1: cross-rank barrier before the first remote write
-  int64_t srcinfo_off;           // 0, or byte offset (inside a rank's chunk) of the provenance table [NvS] int32: the
-                                 // sender writes src_rank * S*K + s*K + k for each of a token's K slots and -1 for
-                                 // padding rows, so that a GEMM epilogue can send a row straight back to its source
-};
-struct DispatchArgsPack { DispatchArgs a[MEP_MAX_VRANKS]; };
-
-constexpr int kSendWarps = 6;                 // sender warps per CTA
-constexpr int kDispThreads = (kSendWarps + 1) * 32;   // + one zero-fill warp
-constexpr int kMaxStages = 8;
-constexpr int kMetaTokens = 32;   // tokens per warp whose plan entries / weights are staged at once
 
 template <int N> __device__ __forceinline__ void wait_read_le() { bulk_wait_read<N>(); }
 __device__ __forceinline__ void wait_read_dyn(int n) {
@@ -53,11 +35,13 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   __shared__ __align__(8) uint64_t s_bar[kSendWarps * kMaxStages];
   __shared__ int s_err;
   __shared__ int s_znext, s_ztotal;
+  __shared__ int s_peer[MEP_MAX_RANKS];     // rows this CTA sent to each rank (counters only)
   const int nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = c.K, S = c.S, NvS = c.NvS;
   const uint32_t row_bytes = (uint32_t)c.H * 2u;
 
   if (tid == 0) s_err = 0;
+  if (tid < MEP_MAX_RANKS) s_peer[tid] = 0;
   if (tid < kSendWarps * kMaxStages) mbar_init(&s_bar[tid], 1);
   fence_mbar_init();
   // padding-row table of the local shard: s_zstart[g] = first padding row of group g,
@@ -193,6 +177,7 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
         if (dv >= 0 && lane == 0) {
           const int d = dv / NvS, loff = dv - d * NvS;
           bulk_s2g(peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes, ring + (size_t)st * row_bytes, row_bytes);
+          if (c.counters) atomicAdd(&s_peer[d], 1);
         }
       }
       if (lane == 0) bulk_commit();
@@ -205,6 +190,14 @@ dispatch_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   }
   if (lane == 0 && warp == kSendWarps) trace_mark(c, MEP_K_DISPATCH, 4);
   cross_rank_barrier(c, nb, 1, MEP_K_DISPATCH, 30);
+  if (c.counters) {
+    if (tid < c.R && s_peer[tid]) {
+      if (tid < 48) count(c, MEP_CNT_PEER_ROWS + tid, (unsigned long long)s_peer[tid]);
+      count(c, MEP_CNT_ROWS_SENT, (unsigned long long)s_peer[tid]);
+      if (tid != c.rank) count(c, MEP_CNT_ROWS_REMOTE, (unsigned long long)s_peer[tid]);
+    }
+    if (tid == 0 && blockIdx.x == 0) count(c, MEP_CNT_DISPATCHES, 1);
+  }
   if (tid == 0) trace_mark(c, MEP_K_DISPATCH, 5);
   pdl_trigger();                               // the duplicate expansion may be scheduled while this grid drains
 }

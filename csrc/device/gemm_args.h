@@ -35,6 +35,13 @@ struct GemmArgs {
   unsigned char* push_wbase;
   const float* push_wsrc;
   uint64_t push_stride;
+  // GATE_UP / DGRAD, optional: the rows of `a` are produced by a flagged dispatch that is still running.
+  // tile_done[t] holds the flag epoch at which rows [128 t, 128 t + 128) became complete; the TMA producer waits
+  // (bounded) for tile_done[t] >= *tile_epoch before it loads rows of tile t. The launch must leave the dispatch
+  // kernel's SMs free (num_ctas <= SMs - its CTAs), since that kernel has to be resident meanwhile.
+  const uint32_t* tile_done;
+  const uint32_t* tile_epoch;
+  int32_t* status_host;        // optional host-mapped copy of status[0]
   int32_t push_rows;
   int32_t push_ranks;
   int32_t sched_ctas;          // dynamic order: CTAs over ALL launches that draw from `sched` (several launches of

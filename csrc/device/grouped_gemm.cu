@@ -44,6 +44,17 @@ template <int MODE> struct GemmCfg {
   static constexpr size_t kSmem = (size_t)kRing * (16384 + 32768) + (size_t)kEpiWarps * 2 * 4096 + 1024;
 };
 constexpr int kMaxGroups = 192;
+
+// Bounded poll of a tile flag (see GemmArgs.tile_done): true once *flag has reached `epoch`.
+__device__ __forceinline__ bool wait_flag_bounded(const uint32_t* flag, uint32_t epoch, uint64_t budget_ns) {
+  if ((int32_t)(ld_acquire_gpu(flag) - epoch) >= 0) return true;
+  const long long t0 = clock64(), lim = budget_cycles(budget_ns);
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) { __nanosleep(100); if ((int32_t)(ld_acquire_gpu(flag) - epoch) >= 0) return true; }
+    if (clock64() - t0 > lim) return false;
+  }
+}
 constexpr int kSlabBytes = 32 * 128;             // epilogue staging: 32 rows x 128 B per warp and buffer
 constexpr int kTmemCols = 512;
 
@@ -102,7 +113,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const bool dyn = args.sched != nullptr;
 
   auto fail = [&](int site, int tile) {
-    if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = site; args.status[2] = blockIdx.x; args.status[3] = tile; }
+    const int code = site == 9 ? MEP_ERR_FLAG_TIMEOUT : MEP_ERR_MBAR_TIMEOUT;
+    if (atomicCAS(&args.status[0], 0, code) == 0) {
+      args.status[1] = site; args.status[2] = blockIdx.x; args.status[3] = tile;
+      if (args.status_host) { *(volatile int32_t*)args.status_host = code; __threadfence_system(); }
+    }
     s_abort = 1;
   };
 
@@ -133,9 +148,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int it = 0, gcur = 0; TileInfo ti;
       tq::Scheduler<false> sched; if (dyn) sched.setup(&s_ring, args.sched, ntiles);
       tq::Strided seq{(int)blockIdx.x, (int)gridDim.x, ntiles};
+      const uint32_t flag_ep = args.tile_done ? *(volatile const uint32_t*)args.tile_epoch : 0u;
+      int flag_tile = -1;                  // last row tile whose flag was seen complete
       for (int t; !s_abort && (t = dyn ? sched.next(args.budget_ns) : seq.next()) != -1;) {
         if (t == -2) { fail(5, sched.n); break; }
         get_tile(t, gcur, ti);
+        if (!A_MN && args.tile_done && ti.kblocks > 0 && (ti.row0 >> 7) != flag_tile) {
+          // rows of this tile come from a dispatch that may still be running: wait until they have all
+          // landed and the duplicates are expanded, then order the TMA engine's reads behind that
+          const uint32_t* f = args.tile_done + (ti.row0 >> 7);
+          if (!wait_flag_bounded(f, flag_ep, args.budget_ns)) { fail(9, t); break; }
+          fence_proxy_async();
+          flag_tile = ti.row0 >> 7;
+        }
         for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;
           if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, args.budget_ns)) { fail(1, t); break; }
@@ -247,7 +272,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         const size_t row = (size_t)ti.row0 + r_in_tile;
         __nv_bfloat16* orow = (__nv_bfloat16*)args.out + row * args.ldo + ti.n0;
         __nv_bfloat16* grow = args.out2 ? (__nv_bfloat16*)args.out2 + row * (size_t)(2 * args.N) + ti.n0 : nullptr;
-        const float sc = args.row_scale ? args.row_scale[row] : 1.f;
+        const float sc = args.row_scale ? __ldcg(args.row_scale + row) : 1.f;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t gr[32], ur[32];
@@ -300,7 +325,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         // memory, plain 16-byte stores; 8 lanes cover one 128-byte line of a row). The per-row
         // destinations sit in the second staging buffer of the warp, the first one transposes.
         const size_t row = (size_t)ti.row0 + r_in_tile;
-        const float sc = (MODE == GEMM_DOWN && args.row_scale) ? args.row_scale[row] : 1.f;
+        const float sc = (MODE == GEMM_DOWN && args.row_scale) ? __ldcg(args.row_scale + row) : 1.f;
         const int info = args.push_info[row];
         unsigned char* dst = nullptr;
         if (info >= 0) {
@@ -309,7 +334,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             dst = args.push_base + (size_t)src * args.push_stride + ((size_t)idx * args.N + ti.n0) * 2;
             if (args.push_wsrc && ti.n0 == 0)
               *reinterpret_cast<float*>(args.push_wbase + (size_t)src * args.push_stride + (size_t)idx * 4) = args.push_wsrc[row];
-          } else if (atomicCAS(&args.status[0], 0, MEP_ERR_BOUNDS) == 0) { args.status[1] = 8; args.status[2] = blockIdx.x; args.status[3] = (int)row; }
+          } else if (atomicCAS(&args.status[0], 0, MEP_ERR_BOUNDS) == 0) {
+            args.status[1] = 8; args.status[2] = blockIdx.x; args.status[3] = (int)row;
+            if (args.status_host) { *(volatile int32_t*)args.status_host = MEP_ERR_BOUNDS; __threadfence_system(); }
+          }
         }
         const uint32_t buf = stg, ptrs = stg + kSlabBytes;
         __syncwarp();
@@ -343,7 +371,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       } else {
         const size_t row = (size_t)ti.row0 + r_in_tile;
-        const float sc = (MODE == GEMM_DOWN && args.row_scale) ? args.row_scale[row] : 1.f;
+        const float sc = (MODE == GEMM_DOWN && args.row_scale) ? __ldcg(args.row_scale + row) : 1.f;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c, ++chunk_no) {       // 64 output columns (128 B of bf16) per chunk
           const uint32_t buf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;

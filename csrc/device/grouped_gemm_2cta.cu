@@ -104,7 +104,10 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const bool dyn = args.sched != nullptr;
 
   auto fail = [&](int site, int tile) {
-    if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = 100 + site; args.status[2] = blockIdx.x; args.status[3] = tile; }
+    if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) {
+      args.status[1] = 100 + site; args.status[2] = blockIdx.x; args.status[3] = tile;
+      if (args.status_host) { *(volatile int32_t*)args.status_host = MEP_ERR_MBAR_TIMEOUT; __threadfence_system(); }
+    }
     s_abort = 1;
   };
   auto get_tile = [&](int t, Tile& ti) {
@@ -330,7 +333,10 @@ tok_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   const bool dyn = args.sched != nullptr;
 
   auto fail = [&](int site, int tile) {
-    if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) { args.status[1] = 200 + site; args.status[2] = blockIdx.x; args.status[3] = tile; }
+    if (atomicCAS(&args.status[0], 0, MEP_ERR_MBAR_TIMEOUT) == 0) {
+      args.status[1] = 200 + site; args.status[2] = blockIdx.x; args.status[3] = tile;
+      if (args.status_host) { *(volatile int32_t*)args.status_host = MEP_ERR_MBAR_TIMEOUT; __threadfence_system(); }
+    }
     s_abort = 1;
   };
   auto get_tile = [&](int t, int& gcur, TTile& ti) {

@@ -30,6 +30,14 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
   uint32_t v; asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
 }
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+// 16-byte load served by L2 (never by this SM's L1): for data another agent wrote during this kernel
+__device__ __forceinline__ int4 ld_cg_v4(const void* p) {
+  int4 v; asm volatile("ld.global.cg.v4.s32 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory"); return v;
+}
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
@@ -93,7 +101,11 @@ __device__ __forceinline__ void report(const MepRankCtx& c, int code, int kernel
     s->kernel = kernel; s->site = site; s->rank = c.rank; s->peer = peer;
     s->observed = observed; s->expected = expected;
     __threadfence();
+    if (c.status_host) { *(volatile int32_t*)c.status_host = code; __threadfence_system(); }
   }
+}
+__device__ __forceinline__ void count(const MepRankCtx& c, int slot, unsigned long long v) {
+  if (c.counters) atomicAdd(c.counters + slot, v);
 }
 __device__ __forceinline__ bool aborted(const MepRankCtx& c) {
   return *(volatile int32_t*)&c.status->code != 0;
@@ -197,7 +209,11 @@ __device__ __forceinline__ bool cross_rank_arrive_wait(const MepRankCtx& c, int 
 __device__ __forceinline__ bool cross_rank_barrier(const MepRankCtx& c, int nblocks, int row, int kernel, int site) {
   if (!grid_sync(c, nblocks, kernel, site, true)) return false;
   if (blockIdx.x == 0) {
-    if (c.R > 1) cross_rank_arrive_wait(c, row, kernel, site + 1);
+    if (c.R > 1) {
+      const uint64_t t0 = (c.counters && threadIdx.x == 0) ? globaltimer_ns() : 0;
+      cross_rank_arrive_wait(c, row, kernel, site + 1);
+      if (c.counters && threadIdx.x == 0) { count(c, MEP_CNT_BARRIER_WAIT_NS, globaltimer_ns() - t0); count(c, MEP_CNT_BARRIERS, 1); }
+    }
   }
   if (!grid_sync(c, nblocks, kernel, site + 2, false)) return false;
   return !aborted(c);

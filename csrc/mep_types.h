@@ -7,6 +7,23 @@
 #define MEP_MAX_VRANKS 8    // ranks one launch may host on a single GPU (emulation)
 #define MEP_MAX_TOPK 32
 #define MEP_BAR_ROWS 4      // independent cross-rank flag rows per Buffer
+#define MEP_FLAG_ROWS 128   // rows per ready-flag tile (= the grouped GEMM's M tile)
+
+// Slots of the optional per-Buffer counter block (MepRankCtx.counters, unsigned 64-bit each):
+// accumulated by the kernels with relaxed atomics, read by Buffer.stats().
+enum MepCounter {
+  MEP_CNT_DISPATCHES = 0,       // dispatch launches
+  MEP_CNT_ROWS_SENT = 1,        // token rows stored to any rank's shard
+  MEP_CNT_ROWS_REMOTE = 2,      // ... of which to another rank
+  MEP_CNT_PAD_ROWS = 3,         // padding rows cleared
+  MEP_CNT_BARRIER_WAIT_NS = 4,  // time CTA 0 spent waiting in cross-rank barriers
+  MEP_CNT_BARRIERS = 5,         // cross-rank barriers executed
+  MEP_CNT_COMBINES = 6,         // combine launches
+  MEP_CNT_ROWS_PULLED = 7,      // rows read by combine (local and remote)
+  MEP_CNT_DUP_ROWS = 8,         // duplicate rows expanded by a flagged dispatch
+  MEP_CNT_PEER_ROWS = 16,       // [16 + d]: rows sent to rank d (first 48 ranks)
+  MEP_CNT_SLOTS = 64,
+};
 
 // Error codes written to MepStatus.code by device code; 0 means "no error".
 enum MepError {
@@ -72,6 +89,24 @@ typedef struct MepRankCtx {
   char* mc_base;
   // fast planner: flag per 1024-entry block, set to the launch epoch once its histogram is published
   uint32_t* vb_flags;
+  // host-visible copy of status.code (pinned host memory mapped into the device, or null): the
+  // first failure is written to both, so the host can test for a failure without synchronising
+  int32_t* status_host;
+  // tile-ready flags (dispatch -> consumer GEMM), see dispatch_flagged_kernel. A tile is
+  // MEP_FLAG_ROWS consecutive slots of a rank's shard.
+  //   heap, off_ready:  uint32 [ntiles] arrivals; every flagged dispatch adds exactly one arrival per
+  //                     slot of the tile (row landed / duplicate registered / padding cleared / unused)
+  //   heap, off_rowsrc: int32 [NvS] slot a row's payload comes from (itself, the row it duplicates,
+  //                     or -1 for a padding row)
+  int64_t off_rowsrc;
+  uint32_t* tile_done;     // local [ntiles]: flag epoch at which the tile became complete (all rows
+                           // landed, duplicates expanded); consumers wait for tile_done[t] >= epoch
+  uint32_t* flag_epoch;    // local: [0] flagged dispatches issued so far (advanced by flag_epoch_bump in
+                           // stream order before the dispatch and its consumers), [1] expander ticket
+  int32_t ntiles;          // ceil(NvS / MEP_FLAG_ROWS)
+  int32_t reserved1;
+  // per-op counters (null = off), see MepCounters
+  unsigned long long* counters;
 } MepRankCtx;
 
 typedef struct MepCtxPack { const MepRankCtx* ctx[MEP_MAX_VRANKS]; } MepCtxPack;

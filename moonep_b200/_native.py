@@ -44,7 +44,14 @@ class MepRankCtx(C.Structure):
         + [(n, C.c_void_p) for n in ("grid_bar", "epoch", "hist", "count", "tpe_prefix", "remaining", "alloc",
                                      "alloc_cumsum", "expert_off", "etc_all", "stats_all", "send_cnt", "status")]
         + [("wait_budget_ns", C.c_uint64), ("trace", C.c_void_p), ("trace_cap", C.c_int64), ("mc_base", C.c_void_p), ("vb_flags", C.c_void_p)]
+        + [("status_host", C.c_void_p), ("off_rowsrc", C.c_int64), ("tile_done", C.c_void_p), ("flag_epoch", C.c_void_p),
+           ("ntiles", C.c_int32), ("reserved1", C.c_int32), ("counters", C.c_void_p)]
     )
+
+COUNTER_SLOTS = 64
+COUNTER_NAMES = {0: "dispatches", 1: "rows_sent", 2: "rows_sent_remote", 3: "padding_rows_cleared", 4: "barrier_wait_ns",
+                 5: "barriers", 6: "combines", 7: "rows_pulled", 8: "duplicate_rows_expanded"}
+COUNTER_PEER_BASE = 16
 
 
 class PlanArgs(C.Structure):
@@ -54,7 +61,12 @@ class PlanArgs(C.Structure):
 
 class DispatchArgs(C.Structure):
     _fields_ = [("hidden", C.c_void_p), ("weights", C.c_void_p), ("dst", C.c_void_p), ("zero_fill", C.c_void_p),
-                ("fresh", C.c_int32), ("entry_barrier", C.c_int32), ("srcinfo_off", C.c_int64)]
+                ("fresh", C.c_int32), ("entry_barrier", C.c_int32), ("srcinfo_off", C.c_int64),
+                ("send_list", C.c_void_p), ("send_meta", C.c_void_p)]
+
+
+class SendOrderArgs(C.Structure):
+    _fields_ = [("dst", C.c_void_p), ("cu_seqlens", C.c_void_p), ("send_list", C.c_void_p), ("send_meta", C.c_void_p)]
 
 
 class PushReduceArgs(C.Structure):

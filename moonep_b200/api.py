@@ -85,6 +85,16 @@ def validate_rank_strided_pool(pool: torch.Tensor) -> int:
     return rank_stride
 
 
+class TileReady:
+    """Handle on the ready flags of one flagged dispatch, handed to the grouped GEMM that consumes
+    the dispatched rows (``ops.grouped_gemm.gate_up(..., ready=...)`` / ``dgrad(..., ready=...)``).
+    The GEMM then waits tile by tile (128 rows) instead of for the whole dispatch.  ``free_sms`` is
+    the number of SMs such a GEMM may occupy while the dispatch kernel is still running."""
+
+    def __init__(self, done_ptr: int, epoch_ptr: int, free_sms: int):
+        self.done_ptr, self.epoch_ptr, self.free_sms = done_ptr, epoch_ptr, free_sms
+
+
 class OpsMixin:
     """The collective operations, written over lists of per-rank arguments.  ``self._states``
     holds the ranks this process hosts (one for ``Buffer``)."""
@@ -92,6 +102,67 @@ class OpsMixin:
     _states: list
     geo: Geometry
     _num_sms_dedup: int
+
+    # ---- dispatch with ready flags
+    def _dispatch_ready_lists(self, hidden, weights, topk, tpe, plans, comm_stream, *, inter_rank_sync):
+        """Planning and the send list on the current stream, then the flagged dispatch kernel on
+        ``comm_stream``.  Returns ``(hidden views, weight views, cu_seqlens, plans, event)``; the
+        event completes with the dispatch kernel (all rows landed, duplicates expanded)."""
+        st, g, n = self._states, self.geo, len(self._states)
+        fresh = plans is None
+        for i in range(n):
+            h = hidden[i]
+            assert h.dtype == torch.bfloat16 and h.is_contiguous() and tuple(h.shape) == (g.S, g.H), \
+                f"hidden_sh must be a contiguous [S={g.S}, H={g.H}] bf16 tensor"
+            if weights is not None:
+                w = weights[i]
+                assert w.dtype == torch.float32 and w.is_contiguous() and w.numel() == g.N, \
+                    "route_weights_sk must be a contiguous [S, K] fp32 tensor"
+        cus = [None] * n
+        if fresh:
+            plans, cus = [], []
+            for i in range(n):
+                t, c = topk[i].reshape(-1), tpe[i]
+                assert t.dtype == torch.int32 and t.numel() == g.N and t.is_contiguous(), \
+                    "topk_experts_sk must be a contiguous [S, K] int32 tensor"
+                assert c.dtype == torch.int32 and c.numel() == g.E and c.is_contiguous(), \
+                    "tokens_per_expert must be a contiguous [E] int32 tensor"
+                p, cu = engine.allocate_plan(st[i], with_send_list=True)
+                plans.append(p)
+                cus.append(cu)
+            engine.launch_planning(st, [t.reshape(-1) for t in topk], tpe, plans, cus)
+            engine.launch_send_order(st, plans, cus)
+        else:
+            for p in plans:
+                assert isinstance(p, MoonEPCommPlan), "plan must be a MoonEPCommPlan"
+                assert (p.N, p.R, p.E, p.NvS, p.K) == (g.N, g.R, g.E, g.NvS, g.K), "plan belongs to another Buffer geometry"
+                assert p.send_list is not None, "dispatch_ready needs a plan made by dispatch_ready (it carries the send list)"
+        engine.launch_flag_epoch_bump(st)
+        main = torch.cuda.current_stream()
+        if comm_stream is None or comm_stream == main:
+            engine.launch_dispatch(st, hidden, weights, plans, fresh=fresh, entry_barrier=(not fresh) and inter_rank_sync, flagged=True)
+            if fresh:
+                engine.launch_dup_finalize(st, plans)
+            ev = None
+        else:
+            for t in (*hidden, *(weights or ())):
+                t.record_stream(comm_stream)
+            comm_stream.wait_event(main.record_event())
+            with torch.cuda.stream(comm_stream):
+                engine.launch_dispatch(st, hidden, weights, plans, fresh=fresh,
+                                       entry_barrier=(not fresh) and inter_rank_sync, flagged=True)
+                if fresh:
+                    engine.launch_dup_finalize(st, plans)
+                ev = comm_stream.record_event()
+        out_h = [s.hidden_local for s in st]
+        out_w = [s.weights_local if weights is not None else None for s in st]
+        return out_h, out_w, cus, plans, ev
+
+    def _tile_ready(self, i: int = 0) -> TileReady:
+        st = self._states[i]
+        total = torch.cuda.get_device_properties(st.device).multi_processor_count
+        return TileReady(st.scratch["tile_done"].data_ptr(), st.scratch["flag_epoch"].data_ptr(),
+                         total - len(self._states) * self.geo.num_sms)
 
     # ---- dispatch
     def _dispatch_lists(self, hidden, weights, topk, tpe, plans, *, inter_rank_sync, zero_copy, w_zero_copy):
@@ -279,8 +350,15 @@ class Buffer(OpsMixin):
         return self._destroyed
 
     def _st(self) -> engine.RankState:
+        """Entry check of every public op: the Buffer is alive and no kernel of it has given up a
+        wait.  The failure flag is host memory that the kernels write (no synchronisation here), so
+        a rank whose peers were late learns of it at its next call instead of computing on with
+        unsynchronised data."""
         assert not self._destroyed, "MoonEP Buffer has been destroyed"
-        return self._states[0]
+        st = self._states[0]
+        if engine.failed(st):
+            self.check()
+        return st
 
     @property
     def NvS(self) -> int:
@@ -304,23 +382,30 @@ class Buffer(OpsMixin):
     # ---- health
     def check(self) -> None:
         """Synchronise and raise ``MoonEPTimeout`` if any kernel of this Buffer gave up a wait."""
-        s = engine.read_status(self._st())
+        assert not self._destroyed, "MoonEP Buffer has been destroyed"
+        s = engine.read_status(self._states[0])
         if s is not None:
             raise MoonEPTimeout(s)
 
+    def healthy(self) -> bool:
+        """False once a kernel of this Buffer has recorded a failure.  Does not synchronise: safe to
+        call between launches and between replays of a captured graph (``check()`` gives the details)."""
+        return self._destroyed or not engine.failed(self._states[0])
+
     def reset(self) -> None:
         """Collective: clear barrier words, epochs and the error status after a failed op."""
-        st = self._st()
+        assert not self._destroyed, "MoonEP Buffer has been destroyed"
+        st = self._states[0]
         torch.cuda.synchronize()
         if self.geo.R > 1:
             dist.barrier(group=self._group)
         g = self.geo
         self._heap.view(st.rank, g.off_bar, (4 * 128,), torch.int32).zero_()
-        st.scratch["grid_bar"].zero_()
-        st.scratch["epoch"].zero_()
-        st.scratch["send_cnt"].zero_()
-        st.scratch["vb_flags"].zero_()
+        self._heap.view(st.rank, g.off_ready, (g.ntiles,), torch.int32).zero_()
+        for name in ("grid_bar", "epoch", "send_cnt", "vb_flags", "tile_done", "flag_epoch"):
+            st.scratch[name].zero_()
         st.status.zero_()
+        st.status_host.zero_()
         torch.cuda.synchronize()
         if self.geo.R > 1:
             dist.barrier(group=self._group)
@@ -332,6 +417,14 @@ class Buffer(OpsMixin):
         zf = plan.zero_fill_ranges[:, 1].sum().item()
         return dict(experts_received=rs[0], slots_sent=rs[1], dup_groups=dc[0], dup_rows=dc[1],
                     dedup_ratio=dc[1] / max(1, plan.N), padded_rows=int(zf))
+
+    def counters(self, reset: bool = False) -> dict:
+        """Device-side counters of this Buffer's kernels since creation or the last reset
+        (synchronises): dispatch / combine launches, rows sent in total, to other ranks and per
+        destination rank, padding rows cleared, rows pulled by combine, duplicate rows expanded by
+        flagged dispatches, cross-rank barriers executed and the time spent waiting in them.
+        ``MOONEP_COUNTERS=0`` at construction switches the accounting off (empty dict)."""
+        return engine.read_counters(self._st(), reset)
 
     def verify_plan(self, plan: MoonEPCommPlan) -> None:
         """Debugging aid, collective and synchronising: every rank fingerprints its view of the
@@ -412,6 +505,36 @@ class Buffer(OpsMixin):
         if plan is None and _VERIFY_PLANS and not torch.cuda.is_current_stream_capturing():
             self.verify_plan(p)
         return h, w, cu, p
+
+    def dispatch_ready(self, hidden_sh: torch.Tensor, route_weights_sk: torch.Tensor | None = None,
+                       topk_experts_sk: torch.Tensor | None = None, tokens_per_expert: torch.Tensor | None = None,
+                       plan: MoonEPCommPlan | None = None, *, inter_rank_sync: bool = True):
+        """``dispatch`` for a consumer that starts before the all-to-all has finished (extension; the
+        reference's dispatch ends with a full barrier, moonep/dispatch.py:687-692).
+
+        Planning runs on the current stream, the dispatch kernel on the communication stream.
+        Rows are sent in the order of their destination slots, every 128-row tile of the shard gets
+        a ready flag, and duplicate rows are expanded by the same kernel as their tile completes.
+        Returns ``(hidden_nvsh, route_weights_nvs | None, cu_seqlens | None, plan, ready, event)``:
+        the two views are zero-copy and fill up while the kernel runs; ``ready`` (``TileReady``) goes
+        to ``ops.grouped_gemm.gate_up`` / ``dgrad`` launched on the current stream with at most
+        ``ready.free_sms`` CTAs; anything else that reads the views must wait for ``event``.
+        A saved ``plan`` must come from ``dispatch_ready`` (it carries the send list)."""
+        self._st()
+        if plan is None:
+            assert topk_experts_sk is not None and tokens_per_expert is not None, \
+                "dispatch needs topk_experts_sk and tokens_per_expert unless a plan is reused"
+        if _NVTX:
+            torch.cuda.nvtx.range_push("moonep.dispatch_ready")
+        try:
+            oh, ow, cus, plans, ev = self._dispatch_ready_lists(
+                [hidden_sh], None if route_weights_sk is None else [route_weights_sk],
+                None if plan is not None else [topk_experts_sk], None if plan is not None else [tokens_per_expert],
+                None if plan is None else [plan], self._comm_stream, inter_rank_sync=inter_rank_sync)
+        finally:
+            if _NVTX:
+                torch.cuda.nvtx.range_pop()
+        return oh[0], ow[0], cus[0], plans[0], self._tile_ready(0), ev
 
     # ---- prefetch
     def prefetch_weight(self, plan: MoonEPCommPlan | None = None, async_finish: bool = False, *,

@@ -16,7 +16,7 @@ import torch
 
 from . import _native
 from ._native import (MepRankCtx, PlanArgs, DispatchArgs, DupFinalizeArgs, DupArgs, CombineArgs, PushReduceArgs,
-                      PrefetchArgs, GradReduceArgs, ptr)
+                      PrefetchArgs, GradReduceArgs, SendOrderArgs, ptr)
 from .geometry import Geometry
 from .plan import MoonEPCommPlan
 
@@ -58,6 +58,7 @@ class RankState:
     weights_local: torch.Tensor = None    # [NvS] fp32 view
     srcinfo_local: torch.Tensor = None    # [NvS] int32 provenance table (push-combine Buffers only)
     status: torch.Tensor = None           # int32[8] device
+    status_host: torch.Tensor = None      # int32[1] pinned host memory the kernels mirror status[0] into
     plan_fast: bool = False
 
     @property
@@ -84,7 +85,14 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     s["etc_all"] = torch.zeros(R * epn, **i32)
     s["stats_all"] = torch.zeros(R * 2, **i32)
     s["send_cnt"] = torch.zeros(2 * R, dtype=torch.int64, device=dev)     # two halves, see planning_fast_kernel
+    s["tile_done"] = torch.zeros(geo.ntiles, **i32)           # ready flags: epoch at which a tile became complete
+    s["flag_epoch"] = torch.zeros(4, **i32)                   # [0] flagged dispatches issued, [1] expander ticket
+    if os.environ.get("MOONEP_COUNTERS", "1") != "0":
+        s["counters"] = torch.zeros(_native.COUNTER_SLOTS, dtype=torch.int64, device=dev)
     st.status = torch.zeros(8, **i32)
+    # first failure code, mirrored by the kernels into host memory the device can write: the host
+    # tests it without synchronising (see Buffer._st)
+    st.status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     c = MepRankCtx()
     c.rank, c.R, c.S, c.H, c.K, c.E, c.epn, c.N, c.NvS = rank, R, geo.S, geo.H, geo.K, E, epn, geo.N, geo.NvS
@@ -93,13 +101,16 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     c.checked = 1 if os.environ.get("MOONEP_CHECKED") == "1" else 0
     c.heap_base, c.chunk_stride = heap.base, heap.chunk_bytes
     for name in ("off_hidden", "off_weights", "off_tpe", "off_bar", "off_dupcnt", "off_dupgroups",
-                 "off_duploffs", "off_ready"):
+                 "off_duploffs", "off_ready", "off_rowsrc"):
         setattr(c, name, getattr(geo, name))
     c.dup_group_cap, c.dup_loff_cap = geo.dup_group_cap, geo.dup_loff_cap
     for name in ("grid_bar", "epoch", "hist", "count", "tpe_prefix", "remaining", "alloc", "alloc_cumsum",
-                 "expert_off", "etc_all", "stats_all", "send_cnt", "vb_flags"):
+                 "expert_off", "etc_all", "stats_all", "send_cnt", "vb_flags", "tile_done", "flag_epoch"):
         setattr(c, name, s[name].data_ptr())
+    c.ntiles = geo.ntiles
+    c.counters = s["counters"].data_ptr() if "counters" in s else None
     c.status = st.status.data_ptr()
+    c.status_host = st.status_host.data_ptr()
     c.wait_budget_ns = wait_budget_ns() if budget_ns is None else budget_ns
     c.mc_base = getattr(heap, "mc_base", 0) or None
     if os.environ.get("MOONEP_TRACE") == "1":
@@ -114,6 +125,25 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     st.weights_local = heap.view(rank, geo.off_weights, (geo.NvS,), torch.float32)
     st.srcinfo_local = heap.view(rank, geo.off_srcinfo, (geo.NvS,), torch.int32) if geo.off_srcinfo else None
     return st
+
+
+def failed(st: RankState) -> bool:
+    """True once any kernel of this rank has recorded a failure. A plain read of host memory: no
+    synchronisation, usable between launches and during CUDA-graph replays."""
+    return int(st.status_host[0]) != 0
+
+
+def read_counters(st: RankState, reset: bool = False) -> dict:
+    """Per-op device counters accumulated since the Buffer was created or last reset (synchronises)."""
+    t = st.scratch.get("counters")
+    if t is None:
+        return {}
+    v = t.cpu().tolist()
+    out = {name: int(v[i]) for i, name in _native.COUNTER_NAMES.items()}
+    out["rows_sent_to"] = [int(x) for x in v[_native.COUNTER_PEER_BASE:_native.COUNTER_PEER_BASE + min(st.geo.R, 48)]]
+    if reset:
+        t.zero_()
+    return out
 
 
 def read_status(st: RankState) -> dict | None:
@@ -145,10 +175,11 @@ def _pack(states):
     return _native.ctx_array([s.ctx_ptr for s in states])
 
 
-def allocate_plan(st: RankState):
+def allocate_plan(st: RankState, with_send_list: bool = False):
     """Plan-owned tensors plus cu_seqlens for one rank (reference: planning.py:1168-1215)."""
     g = st.geo
     i32 = dict(dtype=torch.int32, device=st.device)
+    extra = dict(send_list=torch.empty(g.N, **i32), send_meta=torch.zeros(4, **i32)) if with_send_list else {}
     plan = MoonEPCommPlan(
         dst=torch.empty(g.N, **i32),
         experts_to_copy=torch.empty(g.R, g.epn, **i32),
@@ -158,6 +189,7 @@ def allocate_plan(st: RankState):
         dup_groups=torch.empty(g.NvS, 3, **i32),
         dup_loffs=torch.empty(g.NvS, **i32),
         dup_counts=torch.zeros(2, **i32),
+        **extra,
     )
     cu = torch.empty(2 * g.epn, **i32)
     return plan, cu
@@ -177,7 +209,7 @@ def launch_planning(states, topk_list, tpe_list, plans, cu_list):
     _native.check(lib.mep_launch_planning(n, _pack(states), args, g.num_sms, g.E, g.R, _native.cur_stream()), "planning")
 
 
-def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry_barrier: bool):
+def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry_barrier: bool, flagged: bool = False):
     lib = _native.load()
     n = len(states)
     g0 = states[0].geo
@@ -186,9 +218,34 @@ def launch_dispatch(states, hidden_list, weights_list, plans, fresh: bool, entry
         w = weights_list[i] if weights_list is not None else None
         fresh_code = 3 if states[i].plan_fast else 1      # which send_cnt half the planner used (3: device epoch)
         args[i] = DispatchArgs(ptr(hidden_list[i]), ptr(w), ptr(plans[i].dst), ptr(plans[i].zero_fill_ranges),
-                               fresh_code if fresh else 0, 1 if entry_barrier else 0, g0.off_srcinfo)
+                               fresh_code if fresh else 0, 1 if entry_barrier else 0, g0.off_srcinfo,
+                               ptr(plans[i].send_list), ptr(plans[i].send_meta))
     g = states[0].geo
-    _native.check(lib.mep_launch_dispatch(n, _pack(states), args, g.num_sms, g.H, g.epn, _native.cur_stream()), "dispatch")
+    fn = lib.mep_launch_dispatch_flagged if flagged else lib.mep_launch_dispatch
+    _native.check(fn(n, _pack(states), args, g.num_sms, g.H, g.epn, _native.cur_stream()), "dispatch")
+
+
+def launch_send_order(states, plans, cu_list):
+    """Build each plan's send list (``plan.send_list`` / ``plan.send_meta``) from ``plan.dst``."""
+    lib = _native.load()
+    n = len(states)
+    args = (SendOrderArgs * n)()
+    for i in range(n):
+        args[i] = SendOrderArgs(ptr(plans[i].dst), ptr(cu_list[i]), ptr(plans[i].send_list), ptr(plans[i].send_meta))
+    g = states[0].geo
+    _native.check(lib.mep_launch_send_order(n, _pack(states), args, g.NvS, g.R, _native.cur_stream()), "send_order")
+
+
+def launch_flag_epoch_bump(states):
+    """A flagged dispatch is about to be issued: advance the flag epoch on the current stream, ahead
+    of the dispatch kernel and of every consumer of its tile flags."""
+    lib = _native.load()
+    _native.check(lib.mep_launch_flag_epoch_bump(len(states), _pack(states), _native.cur_stream()), "flag_epoch_bump")
+
+
+def launch_tile_wait_probe(st: RankState, tile: int):
+    lib = _native.load()
+    _native.check(lib.mep_launch_tile_wait_probe(C.c_void_p(st.ctx_ptr), tile, _native.cur_stream()), "tile_wait_probe")
 
 
 def launch_dup_finalize(states, plans):

@@ -17,6 +17,7 @@ MAX_TOPK = 32            # per-token duplicate bitmask width
 MAX_NVS = (1 << 24) - 1  # slot offsets fit 24 bits
 MAX_VRANKS = 8           # ranks one process may host in single-GPU emulation
 VBLOCK = 1024            # planning kernel block size (entries ranked per CTA pass)
+FLAG_ROWS = 128          # rows per ready-flag tile (the grouped GEMM's M tile)
 
 
 def align_up(x: int, a: int) -> int:
@@ -48,7 +49,9 @@ class Geometry:
     off_dupcnt: int = 0
     off_dupgroups: int = 0
     off_duploffs: int = 0
-    off_ready: int = 0
+    off_ready: int = 0        # uint32 [ntiles] arrival counters of the ready-flag tiles
+    off_rowsrc: int = 0       # int32 [NvS] slot a row's payload comes from (flagged dispatch)
+    ntiles: int = 0           # ceil(NvS / FLAG_ROWS)
     off_srcinfo: int = 0      # push-combine only (0 = not allocated): provenance table [NvS] int32,
     off_push: int = 0         # receive area [S*K, H] bf16,
     off_pushw: int = 0        # per-slot scalar receive area [S*K] fp32
@@ -95,7 +98,9 @@ class Geometry:
         o_dupcnt = take(R * 2 * 4)
         o_dupgroups = take(R * gcap * 3 * 4)
         o_duploffs = take(R * lcap * 4)
-        o_ready = take(4 * (2 * epn + 8))
+        ntiles = (NvS + FLAG_ROWS - 1) // FLAG_ROWS
+        o_ready = take(4 * ntiles)
+        o_rowsrc = take(4 * NvS)
         o_srcinfo = o_push = o_pushw = 0
         if push_combine:
             # the expert GEMM's epilogue sends every output row back to its source rank
@@ -105,4 +110,4 @@ class Geometry:
         chunk = align_up(off, 1024)
         return Geometry(S, H, K, E, R, token_padding, num_sms, epn, N, NvS, vb, nvb,
                         o_hidden, o_weights, o_tpe, o_bar, o_dupcnt, o_dupgroups,
-                        o_duploffs, o_ready, o_srcinfo, o_push, o_pushw, gcap, lcap, chunk)
+                        o_duploffs, o_ready, o_rowsrc, ntiles, o_srcinfo, o_push, o_pushw, gcap, lcap, chunk)

@@ -5,7 +5,13 @@ Forward  : dispatch -> [prefetch_weight on the comm stream] -> gate/up GEMM with
            weights have landed; the private copy of the dispatched tokens that the backward
            pass needs is taken on a side stream meanwhile) -> down GEMM writing straight into
            the communication shard -> combine (zero copy).
-Backward : re-dispatch of the output grad with the saved plan -> dgrad(down) -> SwiGLU backward
+           With ``ready_flags`` (default) the dispatch kernel runs on the comm stream and publishes
+           a flag per 128-row tile; the gate/up GEMM of the local experts starts at once on the SMs
+           that kernel leaves free and takes each tile as it completes, and a second launch of the
+           same GEMM (same ticket counter) joins on the comm stream once dispatch and prefetch have
+           given their SMs back.
+Backward : re-dispatch of the output grad with the saved plan (flagged in the same way, feeding
+           dgrad(down)) -> dgrad(down) -> SwiGLU backward
            (also yields the route-weight grads) -> wgrad(down), wgrad(gate) -> [reduce_grad of
            those two on the comm stream] beside dgrad(gate/up) into the shard -> [combine with
            the route-weight-grad channel on the comm stream] beside wgrad(up) -> reduce_grad(up).
@@ -44,7 +50,7 @@ _DEFERRED: list = []       # layers whose last gradient reduction is still runni
 
 class ExpertParallelMoE:
     def __init__(self, buffer: Buffer, pools: ExpertPools, overlap_prefetch: bool = True,
-                 overlap_backward: bool | None = None):
+                 overlap_backward: bool | None = None, ready_flags: bool | None = None):
         g = buffer.geo
         self.buf, self.pools, self.geo = buffer, pools, g
         self.H = g.H
@@ -57,6 +63,9 @@ class ExpertParallelMoE:
         if overlap_backward is None:        # MOONEP_OVERLAP_BACKWARD=0 serialises the backward pass
             overlap_backward = os.environ.get("MOONEP_OVERLAP_BACKWARD", "1") != "0"
         self.overlap_backward = overlap_backward
+        if ready_flags is None:             # MOONEP_READY_FLAGS=0: the GEMMs wait for the whole dispatch
+            ready_flags = os.environ.get("MOONEP_READY_FLAGS", "1") != "0"
+        self.ready_flags = ready_flags
         dev = buffer.hidden_nvsh_buffer_view.device
         self._side = torch.cuda.Stream(device=dev)
         self._opt = torch.cuda.Stream(device=dev)
@@ -87,6 +96,8 @@ class ExpertParallelMoE:
     def forward(self, hidden_sh, route_weights_sk, topk_sk, tokens_per_expert, need_backward: bool = True):
         buf, g, epn = self.buf, self.geo, self.geo.epn
         self._join_deferred()
+        if self.ready_flags:
+            return self._forward_flagged(hidden_sh, route_weights_sk, topk_sk, tokens_per_expert, need_backward)
         h_view, w_view, cu, plan = buf.dispatch(hidden_sh, route_weights_sk, topk_sk, tokens_per_expert,
                                                 zero_copy=True, router_weights_zero_copy=True)
         ev = None
@@ -109,6 +120,41 @@ class ExpertParallelMoE:
             gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, groups=(epn, 2 * epn))
         else:
             gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w)
+        return self._forward_tail(plan, cu, stashed, need_backward)
+
+    def _forward_flagged(self, hidden_sh, route_weights_sk, topk_sk, tokens_per_expert, need_backward):
+        """Forward pass with tile-ready flags: see the module docstring."""
+        buf, g, epn = self.buf, self.geo, self.geo.epn
+        main, comm = torch.cuda.current_stream(), buf.comm_stream
+        x, w, cu, plan, ready, ev_disp = buf.dispatch_ready(hidden_sh, route_weights_sk, topk_sk, tokens_per_expert)
+        if g.R > 1:     # queued on the comm stream behind the dispatch kernel
+            buf.prefetch_weight(plan=plan, async_finish=True, **self.pools.prefetch_kwargs())
+        stashed = None
+        if need_backward:       # private copies for wgrad, taken as soon as the dispatch kernel has finished
+            self._side.wait_event(ev_disp)
+            with torch.cuda.stream(self._side):
+                self._x.copy_(x)
+                self._w.copy_(w)
+                stashed = self._side.record_event()
+        gu = self._gu if need_backward else None
+        Wg, Wu = self._W("gate"), self._W("up")
+        # local experts: one GEMM, two launches on one ticket counter -- now, on the SMs the dispatch
+        # kernel leaves free, and behind dispatch (+ prefetch) on the comm stream for the rest
+        tk = gg.Ticket(self._act.device, self._total_sms)
+        free = min(ready.free_sms, self._total_sms - self._comm_sms)
+        gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, groups=(0, epn), num_ctas=free, ticket=tk, ready=ready)
+        with torch.cuda.stream(comm):
+            gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, groups=(0, epn), num_ctas=self._total_sms - free, ticket=tk,
+                       ready=ready)
+            joined = comm.record_event()
+        main.wait_event(joined)             # also: dispatch finished, prefetched weights have landed
+        if g.R > 1:
+            gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, groups=(epn, 2 * epn))
+        return self._forward_tail(plan, cu, stashed, need_backward)
+
+    def _forward_tail(self, plan, cu, stashed, need_backward):
+        buf, g = self.buf, self.geo
+        Wd = self._W("down")
         if stashed is not None:
             torch.cuda.current_stream().wait_event(stashed)
         if g.off_push:
@@ -162,10 +208,21 @@ class ExpertParallelMoE:
         main = torch.cuda.current_stream()
         pools = self.pools
         pair = lambda n: (pools.local_grad(n), pools.reduce_view(n))      # noqa: E731
-        dy, _, _, _ = buf.dispatch(grad_out_sh, plan=ctx.plan, zero_copy=True)
         Wg, Wu, Wd = self._W("gate"), self._W("up"), self._W("down")
         shard = buf.hidden_nvsh_buffer_view
-        gg.dgrad(dy, Wd, ctx.cu, self._dA)
+        if self.ready_flags and ctx.plan.send_list is not None:
+            # dgrad(down) starts on the tiles of the re-dispatched output grad as they complete
+            dy, _, _, _, ready, _ = buf.dispatch_ready(grad_out_sh, plan=ctx.plan)
+            tk = gg.Ticket(self._act.device, self._total_sms)
+            free = min(ready.free_sms, self._total_sms - self._comm_sms)
+            gg.dgrad(dy, Wd, ctx.cu, self._dA, num_ctas=free, ticket=tk, ready=ready)
+            with torch.cuda.stream(buf.comm_stream):
+                gg.dgrad(dy, Wd, ctx.cu, self._dA, num_ctas=self._total_sms - free, ticket=tk, ready=ready)
+                joined = buf.comm_stream.record_event()
+            main.wait_event(joined)
+        else:
+            dy, _, _, _ = buf.dispatch(grad_out_sh, plan=ctx.plan, zero_copy=True)
+            gg.dgrad(dy, Wd, ctx.cu, self._dA)
         dw_view = buf.router_weight_buffer_view
         gg.swiglu_bwd(self._dA, ctx.gu, ctx.w_nvs, self._dgu, dw_view, ctx.cu)
         gg.wgrad(ctx.act, dy, ctx.cu, self._dW("down"), accumulate=acc, zero_empty_below=epn)

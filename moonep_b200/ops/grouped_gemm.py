@@ -32,8 +32,9 @@ class GemmArgs(C.Structure):
                 ("out", C.c_void_p), ("out2", C.c_void_p), ("row_scale", C.c_void_p), ("ldo", C.c_int64),
                 ("status", C.c_void_p), ("budget_ns", C.c_uint64), ("sched", C.c_void_p),
                 ("push_info", C.c_void_p), ("push_base", C.c_void_p), ("push_wbase", C.c_void_p),
-                ("push_wsrc", C.c_void_p), ("push_stride", C.c_uint64), ("push_rows", C.c_int32),
-                ("push_ranks", C.c_int32), ("sched_ctas", C.c_int32)]
+                ("push_wsrc", C.c_void_p), ("push_stride", C.c_uint64),
+                ("tile_done", C.c_void_p), ("tile_epoch", C.c_void_p), ("status_host", C.c_void_p),
+                ("push_rows", C.c_int32), ("push_ranks", C.c_int32), ("sched_ctas", C.c_int32)]
 
 
 class PushTarget:
@@ -55,6 +56,24 @@ def _status(device) -> torch.Tensor:
     if key not in _status_cache:
         _status_cache[key] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
     return _status_cache[key]
+
+
+_status_host_cache: dict = {}
+
+
+def _status_host(device) -> torch.Tensor:
+    """Pinned host word the GEMM kernels mirror their failure code into (see ``failed``)."""
+    key = _dev_index(device)
+    if key not in _status_host_cache:
+        _status_host_cache[key] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _status_host_cache[key]
+
+
+def failed(device="cuda") -> bool:
+    """True once a grouped GEMM on ``device`` has given up a wait.  Reads host memory only (no
+    synchronisation); ``check_status`` gives the details and clears the state."""
+    t = _status_host_cache.get(_dev_index(device))
+    return t is not None and int(t[0]) != 0
 
 
 _SCHED_SLOTS = 64
@@ -105,6 +124,7 @@ def check_status(device="cuda") -> None:
     v = st.cpu().tolist()
     if v[0] != 0:
         st.zero_()
+        _status_host(device).zero_()
         ent = _sched_cache.get(_dev_index(device))
         if ent is not None:
             ent[0].zero_()
@@ -113,7 +133,7 @@ def check_status(device="cuda") -> None:
 
 def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=None, row_scale=None, ldo=0,
             accumulate=False, zero_empty_below=0, a_cols=None, b_rows=None, b_cols=None, b_ld=None, groups=None, num_ctas=None,
-            dynamic=False, ticket=None, push=None, push_w=None):
+            dynamic=False, ticket=None, push=None, push_w=None, ready=None):
     lib = _native.load()
     assert a.dtype == torch.bfloat16 and b0.dtype == torch.bfloat16
     assert cu.dtype == torch.int32 and cu.is_contiguous()
@@ -128,12 +148,16 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
     args.out, args.out2 = out.data_ptr(), _native.ptr(out2)
     args.row_scale, args.ldo = _native.ptr(row_scale), ldo
     args.status = _status(a.device).data_ptr()
+    args.status_host = _status_host(a.device).data_ptr()
     from ..engine import wait_budget_ns
     args.budget_ns = wait_budget_ns()
     if ticket is not None:
         args.sched, args.sched_ctas = ticket.ptr, ticket.total_ctas
     else:
         args.sched = _sched(a.device, dynamic)
+    if ready is not None:
+        assert mode in (GATE_UP, DGRAD), "ready flags gate the GEMMs that read the dispatched rows"
+        args.tile_done, args.tile_epoch = ready.done_ptr, ready.epoch_ptr
     if push is not None:
         assert mode in (DOWN, DGRAD, DGRAD_GU) and push.info.dtype == torch.int32 and push.info.numel() >= a.shape[0]
         args.push_info, args.push_base, args.push_stride = push.info.data_ptr(), push.base, push.stride
@@ -145,7 +169,7 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
     a_ld = a.stride(0)
     a_cols = a.shape[1] if a_cols is None else a_cols
     fn = lib.mep_grouped_gemm
-    if mode != WGRAD and push is None and os.environ.get("MOONEP_GEMM_2CTA", "0") == "1":
+    if mode != WGRAD and push is None and ready is None and os.environ.get("MOONEP_GEMM_2CTA", "0") == "1":
         fn = lib.mep_grouped_gemm_2cta      # CTA-pair kernels (tcgen05 cta_group::2), 256-token tiles
     rc = fn(mode, C.c_void_p(a.data_ptr()), C.c_int64(a_rows), C.c_int64(a_cols), C.c_int64(a_ld),
                               C.c_void_p(b0.data_ptr()), C.c_void_p(_native.ptr(b1)), C.c_int64(b_rows),
@@ -159,14 +183,19 @@ def _w2d(w):
     return w.shape[0] * w.shape[1], w.shape[2]
 
 
-def gate_up(x, wg, wu, cu, act_out, gu_out=None, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None):
+def gate_up(x, wg, wu, cu, act_out, gu_out=None, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None,
+            ready=None):
     """``act_out[r] = row_scale[r] * silu(x[r] Wg[g]) * (x[r] Wu[g])``; optionally stores the
-    pre-activations ``gu_out = [x Wg | x Wu]`` (``[NvS, 2*out]``) for the backward pass."""
+    pre-activations ``gu_out = [x Wg | x Wu]`` (``[NvS, 2*out]``) for the backward pass.
+    ``ready`` (a ``TileReady`` from ``Buffer.dispatch_ready``): ``x`` is still being filled by that
+    dispatch; every 128-row tile is loaded only once its flag says it is complete.  Launch with
+    ``num_ctas <= ready.free_sms`` while the dispatch kernel may still be running."""
     G, K, N = wg.shape
     assert wu.shape == wg.shape and x.shape[1] == K and N % 128 == 0 and K % 64 == 0
     rows, cols = _w2d(wg)
     _launch(GATE_UP, x, wg, wu, cu, N=N, K=K, b_group_rows=K, out=act_out, out2=gu_out, row_scale=row_scale,
-            ldo=act_out.stride(0), b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
+            ldo=act_out.stride(0), b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket,
+            ready=ready)
 
 
 def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None, push=None):
@@ -179,13 +208,13 @@ def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None, dynamic=F
             b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket, push=push)
 
 
-def dgrad(dy, w, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None):
-    """``out[r] = dy[r] W[g]^T`` with ``W [G, in, out]`` -> ``out [NvS, in]``."""
+def dgrad(dy, w, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None, ready=None):
+    """``out[r] = dy[r] W[g]^T`` with ``W [G, in, out]`` -> ``out [NvS, in]``.  ``ready``: as in ``gate_up``."""
     G, N, K = w.shape
     assert dy.shape[1] == K and N % 256 == 0 and K % 64 == 0
     rows, cols = _w2d(w)
     _launch(DGRAD, dy, w, None, cu, N=N, K=K, b_group_rows=N, out=out, ldo=out.stride(0),
-            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket, ready=ready)
 
 
 def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None, push=None, push_w=None):
@@ -219,6 +248,7 @@ def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num
         args.zero_empty_below = zero_empty_below
         args.out = out.data_ptr()
         args.status = _status(x.device).data_ptr()
+        args.status_host = _status_host(x.device).data_ptr()
         from ..engine import wait_budget_ns
         args.budget_ns = wait_budget_ns()
         if ticket is not None:

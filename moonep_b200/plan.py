@@ -44,6 +44,11 @@ class MoonEPCommPlan:
     dup_groups: torch.Tensor
     dup_loffs: torch.Tensor
     dup_counts: torch.Tensor
+    # Extension (plans made by ``Buffer.dispatch_ready``; None otherwise): the rows this rank puts on
+    # the wire, as entries ``s*K + k``, ordered by (destination tile, destination rank), and
+    # ``send_meta = [len(send_list), end of the used part of the local shard, 0, 0]``.
+    send_list: torch.Tensor | None = None
+    send_meta: torch.Tensor | None = None
 
     def __post_init__(self) -> None:
         epn = self.E // self.R
@@ -60,6 +65,9 @@ class MoonEPCommPlan:
         chk("dup_groups", (self.NvS, 3))
         chk("dup_loffs", (self.NvS,))
         chk("dup_counts", (2,))
+        if self.send_list is not None or self.send_meta is not None:
+            chk("send_list", (self.N,))
+            chk("send_meta", (4,))
 
     def tensors(self):
         """The tensor fields, in declaration order (used for record_stream)."""

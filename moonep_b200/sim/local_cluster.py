@@ -34,6 +34,17 @@ class LocalCluster(OpsMixin):
         return self._dispatch_lists(hidden, weights, topk, tpe, plans, inter_rank_sync=inter_rank_sync,
                                     zero_copy=zero_copy, w_zero_copy=router_weights_zero_copy)
 
+    def dispatch_ready(self, hidden, weights=None, topk=None, tpe=None, plans=None, *, inter_rank_sync=True,
+                       same_stream=False):
+        """Flagged dispatch of all hosted ranks (one launch); see ``Buffer.dispatch_ready``."""
+        if getattr(self, "_comm_stream", None) is None:
+            self._comm_stream = torch.cuda.Stream(device=self.device)
+        return self._dispatch_ready_lists(hidden, weights, topk, tpe, plans, None if same_stream else self._comm_stream,
+                                          inter_rank_sync=inter_rank_sync)
+
+    def tile_ready(self, rank: int):
+        return self._tile_ready(rank)
+
     def combine(self, plans, hidden_nvsh, weights_nvs=None, *, inter_rank_sync=True, zero_copy=False,
                 router_weights_zero_copy=False):
         return self._combine_lists(plans, hidden_nvsh, weights_nvs, inter_rank_sync=inter_rank_sync,

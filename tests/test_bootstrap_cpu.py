@@ -170,7 +170,7 @@ def test_ctypes_mirrors_match_the_compiled_struct_sizes():
         "DispatchArgs": _native.DispatchArgs, "DupFinalizeArgs": _native.DupFinalizeArgs,
         "DupArgs": _native.DupArgs, "DupFreshArgs": _native.DupArgs, "CombineArgs": _native.CombineArgs,
         "PushReduceArgs": _native.PushReduceArgs, "PrefetchArgs": _native.PrefetchArgs,
-        "GradReduceArgs": _native.GradReduceArgs, "GemmArgs": GemmArgs,
+        "GradReduceArgs": _native.GradReduceArgs, "GemmArgs": GemmArgs, "SendOrderArgs": _native.SendOrderArgs,
     }
     for name, cls in mirrors.items():
         native = getattr(lib, f"mep_sizeof_{name}")()

@@ -6,10 +6,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("ready_flags", [False, True], ids=["barrier", "flags"])
 @pytest.mark.parametrize("push_combine", [False, True], ids=["pull", "push"])
-def test_moe_layer_matches_dense_reference(push_combine, cuda_device, monkeypatch):
+def test_moe_layer_matches_dense_reference(push_combine, ready_flags, cuda_device, monkeypatch):
     from moonep_b200.models.moe_block import MoEBlock, MoEConfig
     monkeypatch.setenv("MOONEP_PUSH_COMBINE", "1" if push_combine else "0")
+    monkeypatch.setenv("MOONEP_READY_FLAGS", "1" if ready_flags else "0")
     cfg = MoEConfig("t", H=256, Hp=256, K=2, epn=4, shared_experts=0, S=192)
     blk = MoEBlock(cfg, num_sms=4, seed=3)
     torch.manual_seed(1)
