@@ -34,7 +34,7 @@
 
 namespace mep {
 
-constexpr int kExpWarps = 8;                                       // expander warps per CTA
+constexpr int kExpWarps = 12;                                      // expander warps per CTA
 constexpr int kFlagThreads = (kSendWarps + 1 + kExpWarps) * 32;    // senders + zero-fill warp + expanders
 constexpr int kSigLag = 2;          // a row's arrival is signalled once at most this many newer stores are pending
 constexpr int kSigRing = 8;
@@ -341,12 +341,12 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
         const int v = s_xlist[i];
         const char* srow = hid + (size_t)(v >> 7) * row_bytes;
         char* drow = hid + (size_t)(t * MEP_FLAG_ROWS + (v & 127)) * row_bytes;
-        for (int v0 = 0; v0 < nvec; v0 += 128) {      // 4 x 16-byte loads in flight per lane
-          int4 x[4];
+        for (int v0 = 0; v0 < nvec; v0 += 256) {      // 8 x 16-byte loads in flight per lane
+          int4 x[8];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { const int q = v0 + j * 32 + lane; if (q < nvec) x[j] = ld_cg_v4(srow + (size_t)q * 16); }
+          for (int j = 0; j < 8; ++j) { const int q = v0 + j * 32 + lane; if (q < nvec) x[j] = ld_cg_v4(srow + (size_t)q * 16); }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { const int q = v0 + j * 32 + lane; if (q < nvec) st_na_v4(drow + (size_t)q * 16, x[j]); }
+          for (int j = 0; j < 8; ++j) { const int q = v0 + j * 32 + lane; if (q < nvec) st_na_v4(drow + (size_t)q * 16, x[j]); }
         }
       }
       if (xt == 0) ndup += nd_;

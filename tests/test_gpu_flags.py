@@ -118,7 +118,7 @@ def test_gemm_consumes_tiles_while_dispatch_runs(R, mode, cuda_device):
     may only load a tile once its flag is up, so its result must equal the GEMM on the complete shard
     (a tile loaded early would contain the poison pattern)."""
     from moonep_b200.ops import grouped_gemm as gg
-    S, K, epn, H, Hp, pad, sms = 256, 4, 3, 256, 256, 128, 2
+    S, K, epn, H, Hp, pad, sms = 256, 4, 5, 256, 256, 128, 2
     cl, cp, topk, tpe, hidden, weights, dev = _setup(S, K, epn, H, R, sms, pad, "biased")
     g = cl.geo
     gen = torch.Generator(device="cuda").manual_seed(3)
