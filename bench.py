@@ -339,6 +339,38 @@ def run_ours(args):
     clocks = sampler.stop()
     peak_gb = torch.cuda.max_memory_allocated() / 2**30
 
+    def time_ops(fns, n=5):
+        """Device time of each callable (CUDA events on this stream, mean of n after 2 warm-up calls,
+        barrier on both sides, max over ranks), in microseconds."""
+        out = []
+        for fn in fns:
+            for _ in range(2):
+                fn()
+            barrier_sync(world)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            barrier_sync(world)
+            out.append(round(max_over_ranks(e0.elapsed_time(e1) / n * 1e3, world), 1))
+        return out
+
+    def comm_times(buf, xin, w, topk, tpe):
+        """The four public collectives one by one: dispatch (planning included), prefetch_weight,
+        combine (with the route-weight channel), reduce_grad -- what `dispatch_combine_us` runs in a row."""
+        h, wn, cu, plan = buf.dispatch(xin, w, topk, tpe, zero_copy=True, router_weights_zero_copy=True)
+        ops = [lambda: buf.dispatch(xin, w, topk, tpe, zero_copy=True, router_weights_zero_copy=True)]
+        if world > 1:
+            ops.append(lambda: buf.prefetch_weight(plan=plan, **blk.pools.prefetch_kwargs()))
+        ops.append(lambda: buf.combine(plan=plan, hidden_nvsh=h, route_weights_nvs=wn, zero_copy=True, router_weights_zero_copy=True))
+        if world > 1:
+            ops.append(lambda: buf.reduce_grad(plan=plan, **blk.pools.reduce_kwargs()))
+        t = time_ops(ops)
+        if world > 1:
+            return {"dispatch_us": t[0], "prefetch_us": t[1], "combine_us": t[2], "reduce_grad_us": t[3]}
+        return {"dispatch_us": t[0], "prefetch_us": None, "combine_us": t[1], "reduce_grad_us": None}
+
     sweep = []
     if not args.no_sweep:
         buf = blk.buf
@@ -370,9 +402,28 @@ def run_ours(args):
             us = max_over_ranks(e0.elapsed_time(e1) / 5 * 1e3, world)
             st = buf.stats(plan)
             sweep.append({"maxvio_target": mv, "maxvio": round(real, 3), "step_ms": round(sms, 3),
-                          "dispatch_combine_us": round(us, 1), "experts_received": st["experts_received"],
-                          "slots_sent": st["slots_sent"]})
+                          "dispatch_combine_us": round(us, 1), **comm_times(buf, xin, w, topk, tpe),
+                          "experts_received": st["experts_received"], "slots_sent": st["slots_sent"]})
         blk.buf.check(); gg.check_status()
+
+    # the communication collectives alone at the main skew, and their ratio to the reference arm's
+    # figures when a result line of `bench.py --impl reference` for the same N is supplied
+    calibrate_skew(blk, dev_batches[0], args.maxvio, world)
+    with torch.no_grad():
+        w_, topk_, tpe_ = blk.route(dev_batches[0])
+    comm = comm_times(blk.buf, dev_batches[0], w_, topk_, tpe_)
+    comm["sequence_us"] = round(sum(v for v in comm.values() if v is not None), 1)
+    comm_ratio = None
+    ref_path = os.environ.get("MOONEP_BENCH_REFERENCE_JSON")
+    if ref_path and os.path.exists(ref_path):
+        try:
+            with open(ref_path) as f:
+                ref = json.loads([l for l in f.read().splitlines() if l.startswith("{")][-1])
+            if ref.get("n_gpus") == world and ref.get("comm"):
+                comm_ratio = round(ref["comm"]["sequence_us"] / comm["sequence_us"], 3)       # > 1: this arm is faster
+        except Exception:      # noqa: BLE001
+            comm_ratio = None
+    blk.buf.check(); gg.check_status()
 
     published = None
     if world == 8 and not args.no_sweep:
@@ -387,16 +438,21 @@ def run_ours(args):
         "config": {"model": f"{cfg.name}-shape MoE layer (H={cfg.H}, H'={cfg.Hp}, K={cfg.K}, E={blk.E}, epn={cfg.epn})",
                    "global_batch": tokens, "seq_len": S, "parallelism": f"ep{world}", "token_padding": cfg.token_padding,
                    "num_sms": 32, "maxvio_target": args.maxvio, "maxvio": round(realised, 3),
-                   "step": "router + dispatch + grouped GEMM fwd/bwd + combine + reduce_grad + SGD"
-                           + (" (each projection's SGD is launched inside the backward pass, on a side stream, once its "
-                              "gradient is final)" if args.optimizer_in_backward else ""),
-                   "l2": "inputs larger than L2 (multi-GB working set per step)", "launch": graph_note, "path": path_note,
-                   "combine": ("pushed by the down GEMM's epilogue into the source ranks' memory, then a local sum"
-                               if blk.buf.geo.off_push else "pulled from the peers' shards after the down GEMM")},
+                   "l2": "inputs larger than L2 (multi-GB working set per step)"},
+        "notes": {"step": "router + dispatch + grouped GEMM fwd/bwd + combine + reduce_grad + SGD"
+                          + (" (each projection's SGD is launched inside the backward pass, on a side stream, once its "
+                             "gradient is final)" if args.optimizer_in_backward else ""),
+                  "launch": graph_note, "path": path_note,
+                  "dispatch": ("per-tile ready flags: gate/up and dgrad(down) GEMMs start while the dispatch kernel runs"
+                               if blk.moe.ready_flags else "the GEMMs start after the dispatch kernel's exit barrier"),
+                  "combine": ("pushed by the down GEMM's epilogue into the source ranks' memory, then a local sum"
+                              if blk.buf.geo.off_push else "pulled from the peers' shards after the down GEMM"),
+                  "comm": "moonep_b200.Buffer", "expert_ffn": "moonep_b200 tcgen05 grouped GEMM"},
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": S * H * 2, "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches),
+        "comm": comm, "comm_ratio": comm_ratio,
         "peak_mem_gib": round(peak_gb, 2), "loss": loss_val, "maxvio_sweep": sweep,
         "published_config": published,
     }

@@ -1,9 +1,13 @@
 """Reference arm: the same MoE-layer training step as bench.py, but every communication op
 goes through the UNMODIFIED reference package's public API (``moonep.Buffer``: dispatch,
 prefetch_weight, combine, reduce_grad) and the expert FFN -- which the reference leaves to the
-integrating framework -- is plain PyTorch (``torch._grouped_mm`` library kernels driven by the
-device-side ``cu_seqlens``; per-group ``torch.matmul`` if that op is missing).  Same shapes,
-routing generator, loss, optimizer step, timing rules and JSON line as the main arm.
+integrating framework -- is written the way an integrator without a grouped-GEMM library would:
+library GEMMs (either ``torch._grouped_mm`` driven by the device-side ``cu_seqlens``, or one cuBLAS
+``torch.mm`` per expert group writing straight into preallocated activations and, in fp32, into the
+weight-gradient views; the faster of the two is picked during warm-up), SwiGLU forward / backward
+and the SGD update as single fused element-wise kernels (``torch.compile``, eager if that is not
+available).  Nothing of ``moonep_b200`` runs here.  Same shapes, routing generator, loss,
+optimizer step, timing rules and JSON line as the main arm.
 Imported only by bench_reference.py after ``baseline/_ref`` has been put on ``sys.path``.
 """
 
@@ -108,37 +112,112 @@ def run(args):
             kw[f"{n}_reduce_buffer"] = Gd[n][:, epn:]
         return kw
 
+    NvS = buffer.NvS if hasattr(buffer, "NvS") else None
+    ffn = {"mode": os.environ.get("MOONEP_REF_FFN", "grouped")}      # "grouped" | "loop", settled in the warm-up
+
+    # ---- fused element-wise pieces (one kernel each when torch.compile works on this machine)
+    def _swiglu_fwd(gp, up, w):
+        g = gp.float()
+        return (torch.nn.functional.silu(g) * up.float() * w[:, None]).to(torch.bfloat16)
+
+    def _swiglu_bwd(dA, gp, up, w):
+        dAf, gf, uf = dA.float(), gp.float(), up.float()
+        sig = torch.sigmoid(gf)
+        silu = gf * sig
+        dw = (dAf * silu * uf).sum(dim=1)
+        d = dAf * w[:, None]
+        dg = (d * uf * sig * (1 + gf * (1 - sig))).to(torch.bfloat16)
+        du = (d * silu).to(torch.bfloat16)
+        return dg, du, dw
+
+    def _sgd(p, g, lr_):
+        p.copy_((p.float() - lr_ * g).to(torch.bfloat16))
+
+    fused = {"fwd": _swiglu_fwd, "bwd": _swiglu_bwd, "sgd": _sgd, "how": "eager"}
+    if os.environ.get("MOONEP_REF_COMPILE", "1") != "0":
+        try:
+            cf, cb, cs = torch.compile(_swiglu_fwd), torch.compile(_swiglu_bwd), torch.compile(_sgd)
+            t = torch.randn(256, 128, device=dev).to(torch.bfloat16)
+            ww = torch.rand(256, device=dev)
+            cf(t, t, ww); cb(t, t, t, ww)
+            pp = torch.zeros(64, 64, device=dev, dtype=torch.bfloat16)
+            cs(pp, torch.zeros(64, 64, device=dev), 1e-3)
+            torch.cuda.synchronize()
+            fused = {"fwd": cf, "bwd": cb, "sgd": cs, "how": "torch.compile"}
+        except Exception:      # noqa: BLE001  (no compiler toolchain for the generated kernels: stay eager)
+            pass
+
+    def _segments(cu):
+        """Non-empty (group, begin, end) row ranges; one host read of cu_seqlens per layer pass."""
+        out, beg = [], 0
+        for gidx, end in enumerate(cu.tolist()):
+            if end > beg:
+                out.append((gidx, beg, end))
+            beg = end
+        return out
+
+    def _fwd_mm(a, Wt, cu, segs, width):
+        """rows of a [M, K] times Wt[g] [K, width] per group -> [M, width] bf16."""
+        if ffn["mode"] == "grouped":
+            return _gmm(a, Wt, cu)
+        out = torch.empty(a.shape[0], width, dtype=torch.bfloat16, device=a.device)
+        for gidx, b, e in segs:
+            torch.mm(a[b:e], Wt[gidx], out=out[b:e])
+        return out
+
+    def _bwd_mm(dy, Wt, cu, segs, width, accumulate_into=None):
+        """dy [M, N] times Wt[g]^T per group -> [M, width] bf16 (optionally added to a previous result)."""
+        if ffn["mode"] == "grouped":
+            r = _gmm(dy, Wt.transpose(1, 2), cu)
+            return r if accumulate_into is None else accumulate_into + r
+        if accumulate_into is None:
+            out = torch.empty(dy.shape[0], width, dtype=torch.bfloat16, device=dy.device)
+            for gidx, b, e in segs:
+                torch.mm(dy[b:e], Wt[gidx].t(), out=out[b:e])
+            return out
+        for gidx, b, e in segs:
+            accumulate_into[b:e].addmm_(dy[b:e], Wt[gidx].t())
+        return accumulate_into
+
+    def _wgrad(a, dy, cu, segs, out):
+        """out[g] = a_g^T dy_g in fp32, written in place; groups without rows: local ones get zeros."""
+        if ffn["mode"] == "grouped":
+            out.copy_(_gmm_wgrad(a, dy, cu, 2 * epn))
+            return
+        seen = set()
+        for gidx, b, e in segs:
+            torch.mm(a[b:e].t(), dy[b:e], out_dtype=torch.float32, out=out[gidx])
+            seen.add(gidx)
+        for gidx in range(epn):
+            if gidx not in seen:
+                out[gidx].zero_()
+
     class MoE(torch.autograd.Function):
         @staticmethod
         def forward(ctx, hidden, w_sk, topk, tpe):
             x, w_nvs, cu, plan = buffer.dispatch(hidden, w_sk, topk, tpe)
             buffer.prefetch_weight(plan=plan, **prefetch_kwargs())
+            segs = _segments(cu) if ffn["mode"] == "loop" else None
             Wg, Wu, Wd = W["gate"][rank], W["up"][rank], W["down"][rank]
-            gp, up = _gmm(x, Wg, cu), _gmm(x, Wu, cu)
-            act = torch.nn.functional.silu(gp.float()) * up.float() * w_nvs[:, None]
-            act = act.to(torch.bfloat16)
-            y = _gmm(act, Wd, cu)
+            gp, up = _fwd_mm(x, Wg, cu, segs, Hp), _fwd_mm(x, Wu, cu, segs, Hp)
+            act = fused["fwd"](gp, up, w_nvs)
+            y = _fwd_mm(act, Wd, cu, segs, H)
             out, _, _ = buffer.combine(plan=plan, hidden_nvsh=y)
-            ctx.saved = (plan, cu, x, w_nvs, act, gp, up)
+            ctx.saved = (plan, cu, segs, x, w_nvs, act, gp, up)
             return out
 
         @staticmethod
         def backward(ctx, grad_out):
-            plan, cu, x, w_nvs, act, gp, up = ctx.saved
+            plan, cu, segs, x, w_nvs, act, gp, up = ctx.saved
             Wg, Wu, Wd = W["gate"][rank], W["up"][rank], W["down"][rank]
             dy, _, _, _ = buffer.dispatch(grad_out.contiguous(), plan=plan)
-            dA = _gmm(dy, Wd.transpose(1, 2), cu).float()
-            Gd["down"][rank].copy_(_gmm_wgrad(act, dy, cu, 2 * epn))
-            gf, uf = gp.float(), up.float()
-            sig = torch.sigmoid(gf)
-            silu = gf * sig
-            dw = (dA * silu * uf).sum(dim=1)
-            d = dA * w_nvs[:, None]
-            dg = (d * uf * sig * (1 + gf * (1 - sig))).to(torch.bfloat16)
-            du = (d * silu).to(torch.bfloat16)
-            dx = _gmm(dg, Wg.transpose(1, 2), cu) + _gmm(du, Wu.transpose(1, 2), cu)
-            Gd["gate"][rank].copy_(_gmm_wgrad(x, dg, cu, 2 * epn))
-            Gd["up"][rank].copy_(_gmm_wgrad(x, du, cu, 2 * epn))
+            dA = _bwd_mm(dy, Wd, cu, segs, Hp)
+            _wgrad(act, dy, cu, segs, Gd["down"][rank])
+            dg, du, dw = fused["bwd"](dA, gp, up, w_nvs)
+            dx = _bwd_mm(dg, Wg, cu, segs, H)
+            dx = _bwd_mm(du, Wu, cu, segs, H, accumulate_into=dx)
+            _wgrad(x, dg, cu, segs, Gd["gate"][rank])
+            _wgrad(x, du, cu, segs, Gd["up"][rank])
             gh, gw, _ = buffer.combine(plan=plan, hidden_nvsh=dx, route_weights_nvs=dw.contiguous())
             if R > 1:
                 buffer.reduce_grad(plan=plan, **reduce_kwargs())
@@ -154,8 +233,7 @@ def run(args):
         loss.backward()
         with torch.no_grad():
             for n in shapes:
-                p = W[n][rank, :epn]
-                p.copy_((p.float() - lr * Gd[n][rank, :epn]).to(torch.bfloat16))
+                fused["sgd"](W[n][rank, :epn], Gd[n][rank, :epn], lr)
             router.add_(router.grad.to(router.dtype), alpha=-lr)
             router.grad = None
         x.grad = None
@@ -206,6 +284,31 @@ def run(args):
     devb = [b.cuda() for b in host]
     realised = calibrate(devb[0], args.maxvio)
     W_ = max(3, args.warmup)
+    # which form of the expert GEMMs is faster here: two untimed steps each (after one to warm up), max over ranks
+    trial = {}
+    forms = ["grouped", "loop"] if hasattr(torch, "_grouped_mm") and "MOONEP_REF_FFN" not in os.environ else [ffn["mode"]]
+    if not hasattr(torch, "_grouped_mm"):
+        forms = ["loop"]
+    for mode in forms:
+        ffn["mode"] = mode
+        try:
+            step(devb[0].detach())
+            sync()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(2):
+                step(devb[i % 2].detach())
+            e1.record()
+            sync()
+            trial[mode] = mx(e0.elapsed_time(e1) / 2)
+        except Exception:      # noqa: BLE001  (e.g. an fp32-output GEMM this build of the library lacks)
+            trial[mode] = float("inf")
+        ok = torch.tensor([0 if trial[mode] == float("inf") else 1], device=dev)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok) == 0:
+            trial[mode] = float("inf")
+    ffn["mode"] = min(trial, key=trial.get)
     for _ in range(W_):
         step(devb[0].detach())
     sync()
@@ -250,6 +353,35 @@ def run(args):
     lv = read_loss(args.steps - 1)
     sync()
     e2e_ms = mx((time.perf_counter() - t0) * 1e3 / args.steps)
+    def time_ops(fns, n=5):
+        out = []
+        for fn in fns:
+            for _ in range(2):
+                fn()
+            sync()
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            sync()
+            out.append(round(mx(e0.elapsed_time(e1) / n * 1e3), 1))
+        return out
+
+    def comm_times(xin, w, topk, tpe):
+        """The four public collectives one by one (same calls and flags as the main arm)."""
+        h, wn, cu, plan = buffer.dispatch(xin, w, topk, tpe, zero_copy=True, router_weights_zero_copy=True)
+        ops = [lambda: buffer.dispatch(xin, w, topk, tpe, zero_copy=True, router_weights_zero_copy=True)]
+        if world > 1:
+            ops.append(lambda: buffer.prefetch_weight(plan=plan, **prefetch_kwargs()))
+        ops.append(lambda: buffer.combine(plan=plan, hidden_nvsh=h, route_weights_nvs=wn, zero_copy=True,
+                                          router_weights_zero_copy=True))
+        if world > 1:
+            ops.append(lambda: buffer.reduce_grad(plan=plan, **reduce_kwargs()))
+        t = time_ops(ops)
+        if world > 1:
+            return {"dispatch_us": t[0], "prefetch_us": t[1], "combine_us": t[2], "reduce_grad_us": t[3]}
+        return {"dispatch_us": t[0], "prefetch_us": None, "combine_us": t[1], "reduce_grad_us": None}
+
     sweep = []
     if not args.no_sweep:
         for mv in SWEEP:
@@ -280,7 +412,13 @@ def run(args):
             e1.record()
             sync()
             sweep.append({"maxvio_target": mv, "maxvio": round(real, 3), "step_ms": round(sms, 3),
-                          "dispatch_combine_us": round(mx(e0.elapsed_time(e1) / 5 * 1e3), 1)})
+                          "dispatch_combine_us": round(mx(e0.elapsed_time(e1) / 5 * 1e3), 1),
+                          **comm_times(devb[0], w, topk, tpe)})
+    calibrate(devb[0], args.maxvio)
+    with torch.no_grad():
+        w_, topk_, tpe_ = route(devb[0])
+    comm = comm_times(devb[0], w_, topk_, tpe_)
+    comm["sequence_us"] = round(sum(v for v in comm.values() if v is not None), 1)
     tokens = S * world
     out = {"metric": "moe_layer_train_step_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
            "n_gpus": world, "steps": args.steps, "warmup": W_, "ms_per_step": ms, "higher_is_better": True,
@@ -288,7 +426,15 @@ def run(args):
            "config": {"model": f"{args.model}-shape MoE layer (H={H}, H'={Hp}, K={K}, E={E}, epn={epn})",
                       "global_batch": tokens, "seq_len": S, "parallelism": f"ep{world}", "token_padding": 128,
                       "num_sms": 32, "maxvio_target": args.maxvio, "maxvio": round(realised, 3),
-                      "comm": "reference moonep.Buffer (unmodified)", "expert_ffn": "torch._grouped_mm" if hasattr(torch, "_grouped_mm") else "torch.matmul per group"},
+                      "l2": "inputs larger than L2 (multi-GB working set per step)"},
+           "notes": {"step": "router + dispatch + grouped GEMM fwd/bwd + combine + reduce_grad + SGD",
+                     "launch": "launched from Python", "path": "default",
+                     "dispatch": "the GEMMs start after the dispatch call returns",
+                     "combine": "pulled from the peers' shards after the down GEMM",
+                     "comm": "reference moonep.Buffer (unmodified)",
+                     "expert_ffn": ("torch._grouped_mm" if ffn["mode"] == "grouped" else "one cuBLAS torch.mm per expert group")
+                                   + f"; SwiGLU and SGD: {fused['how']}; trial step ms: {trial}"},
+           "comm": comm,
            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                    "h2d_bytes_per_step": S * H * 2, "d2h_bytes_per_step": 4},
            "loss": lv, "maxvio_sweep": sweep}

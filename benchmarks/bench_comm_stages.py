@@ -38,7 +38,7 @@ def main():
     scale, _ = routing.solve_scale_for_maxvio(a.maxvio, a.S, a.K, E, R, seed=0) if a.maxvio > 0 else (0.0, 0)
     topk, w, tpe = (t.cuda() for t in routing.softmax_topk(a.S, a.K, E, scale, 0, rank))
     hidden = torch.randn(a.S, a.H, device="cuda").to(torch.bfloat16)
-    plan, cu = engine.allocate_plan(st[0])
+    plan, cu = engine.allocate_plan(st[0], with_send_list=True)
     out = torch.empty(a.S, a.H, dtype=torch.bfloat16, device="cuda")
     outw = torch.empty(a.S, a.K, device="cuda")
     nd = buf._num_sms_dedup * 4
@@ -49,6 +49,10 @@ def main():
         ("dup_expand", lambda: engine.launch_dup_expand(st, [st[0].hidden_local], [plan], nd)),
         ("dup_reduce", lambda: engine.launch_dup_reduce(st, [st[0].hidden_local], [plan], nd)),
         ("combine", lambda: engine.launch_combine(st, [plan], [out], [outw], entry_barrier=True)),
+        # flagged path: send list, then the slot-ordered dispatch that also expands duplicate rows
+        ("send_order", lambda: engine.launch_send_order(st, [plan], [cu])),
+        ("dispatch_flagged", lambda: (engine.launch_flag_epoch_bump(st),
+                                      engine.launch_dispatch(st, [hidden], [w], [plan], fresh=True, entry_barrier=False, flagged=True))),
     ]
     pools = None
     if a.pools and world > 1:

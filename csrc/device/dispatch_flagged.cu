@@ -34,16 +34,21 @@
 
 namespace mep {
 
-constexpr int kExpWarps = 12;                                      // expander warps per CTA
+constexpr int kExpWarps = 8;                                       // expander warps per CTA (one row slot each)
 constexpr int kFlagThreads = (kSendWarps + 1 + kExpWarps) * 32;    // senders + zero-fill warp + expanders
-constexpr int kSigLag = 2;          // a row's arrival is signalled once at most this many newer stores are pending
-constexpr int kSigRing = 8;
+constexpr int kSigLag = 2;          // a unit's arrivals are signalled once at most this many newer units are pending
+constexpr int kSigBatch = 4;        // units between two signalling rounds (one system-scope fence per round)
+constexpr int kSigRing = 8;          // units whose slot lists are remembered until they are signalled (>= kSigLag + kSigBatch)
 
 __device__ __forceinline__ uint32_t* ready_of(const MepRankCtx& c, int d) { return (uint32_t*)peer_ptr(c, d, c.off_ready); }
 __device__ __forceinline__ int tile_rows(const MepRankCtx& c, int t) {
   const int r = c.NvS - t * MEP_FLAG_ROWS; return r < MEP_FLAG_ROWS ? r : MEP_FLAG_ROWS;
 }
 __device__ __forceinline__ void bar_expanders() { asm volatile("bar.sync 1, %0;" :: "n"(kExpWarps * 32) : "memory"); }
+__device__ __forceinline__ void red_relaxed_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void bulk_wait_done() { asm volatile("cp.async.bulk.wait_group %0;" :: "n"(N) : "memory"); }
 
 // ------------------------------------------------------------------ flag epoch
@@ -56,73 +61,88 @@ __global__ void flag_epoch_bump_kernel(MepCtxPack P) {
 
 // ------------------------------------------------------------------ send list
 // send_list = the entries whose row goes on the wire (per token and destination rank the slot with
-// the lowest offset), counting-sorted by bucket = (slot >> shift) * R + (d - rank mod R). One CTA per
-// rank, one warp per token (lane k holds entry k).
-struct SendOrderArgs { const int32_t* dst; const int32_t* cu_seqlens; int32_t* send_list; int32_t* send_meta; };
+// the lowest offset), counting-sorted by bucket = (slot >> shift) * R + (d - rank mod R). Three
+// grid-wide steps on a bucket histogram in device memory: classify + count, exclusive scan (one
+// CTA), place. The order inside a bucket is whatever the atomics give (all of a bucket's rows
+// belong to one tile of one destination).
+struct SendOrderArgs {
+  const int32_t* dst; const int32_t* cu_seqlens; int32_t* send_list; int32_t* send_meta;
+  int32_t* hist;      // [nbuckets] scratch, zero on entry
+  int32_t* bucket;    // [N] scratch: bucket of a wire entry, -1 for every other entry
+};
 struct SendOrderArgsPack { SendOrderArgs a[MEP_MAX_VRANKS]; };
 
-__global__ void __launch_bounds__(1024, 1) send_order_kernel(MepCtxPack P, SendOrderArgsPack A, int shift, int nbuckets) {
-  const MepRankCtx c = *P.ctx[blockIdx.y];
+__global__ void __launch_bounds__(256) send_classify_kernel(MepCtxPack P, SendOrderArgsPack A, int shift, int nbuckets) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
   const SendOrderArgs& a = A.a[blockIdx.y];
-  extern __shared__ int s_b[];            // [nbuckets] counts, then running cursors
+  const int K = c.K, NvS = c.NvS, R = c.R, N = c.N;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < N; i += gridDim.x * blockDim.x) {
+    const int s = i / K;
+    const int dv = a.dst[i];
+    const int raw = dv >= 0 ? dv : -dv - 1;
+    const int d = raw / NvS, loff = raw - d * NvS;
+    bool wire = d < R;
+    if (!wire) report(c, MEP_ERR_BOUNDS, MEP_K_DISPATCH, 50, s, (uint32_t)raw, (uint32_t)(R * NvS));
+    for (int k2 = 0; k2 < K && wire; ++k2) {
+      const int dv2 = a.dst[(size_t)s * K + k2];
+      const int raw2 = dv2 >= 0 ? dv2 : -dv2 - 1;
+      if (raw2 / NvS == d && raw2 < raw) wire = false;     // same rank, lower slot
+    }
+    int b = -1;
+    if (wire) {
+      b = (loff >> shift) * R + (d - c.rank + R) % R;
+      if (b >= nbuckets) b = nbuckets - 1;
+      atomicAdd(a.hist + b, 1);
+    }
+    a.bucket[i] = b;
+  }
+}
+
+__global__ void __launch_bounds__(1024, 1) send_scan_kernel(MepCtxPack P, SendOrderArgsPack A, int nbuckets) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const SendOrderArgs& a = A.a[blockIdx.y];
   __shared__ int s_part[32];
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
-  const int K = c.K, S = c.S, NvS = c.NvS, R = c.R;
-  for (int i = tid; i < nbuckets; i += nt) s_b[i] = 0;
+  // exclusive scan of the bucket counts: each thread owns a contiguous run of buckets
+  const int per = (nbuckets + nt - 1) / nt, b0 = tid * per, b1 = min(nbuckets, b0 + per);
+  int sum = 0;
+  for (int b = b0; b < b1; ++b) sum += a.hist[b];
+  const int incl = warp_incl_scan(sum);
+  if (lane == 31) s_part[warp] = incl;
   __syncthreads();
-  // pass 0 counts, pass 1 places; both classify every entry the same way
-  for (int pass = 0; pass < 2; ++pass) {
-    for (int s = warp; s < S; s += nwarps) {
-      int d = -1, loff = 0;
-      if (lane < K) {
-        const int dv = a.dst[(size_t)s * K + lane];
-        const int raw = dv >= 0 ? dv : -dv - 1;
-        d = raw / NvS; loff = raw - d * NvS;
-        if (d >= R) { if (pass == 0) report(c, MEP_ERR_BOUNDS, MEP_K_DISPATCH, 50, s, (uint32_t)raw, (uint32_t)(R * NvS)); d = -1; }
-      }
-      bool wire = d >= 0;
-      for (int k2 = 0; k2 < K; ++k2) {
-        const int d2 = __shfl_sync(0xffffffffu, d, k2), l2 = __shfl_sync(0xffffffffu, loff, k2);
-        if (d2 == d && l2 < loff) wire = false;
-      }
-      if (wire) {
-        int b = (loff >> shift) * R + (d - c.rank + R) % R;
-        if (b >= nbuckets) b = nbuckets - 1;
-        const int pos = atomicAdd(&s_b[b], 1);
-        if (pass == 1) a.send_list[pos] = s * K + lane;
-      }
-    }
-    __syncthreads();
-    if (pass == 0) {
-      // exclusive scan of the bucket counts: each thread owns a contiguous run of buckets
-      const int per = (nbuckets + nt - 1) / nt, b0 = tid * per, b1 = min(nbuckets, b0 + per);
-      int sum = 0;
-      for (int b = b0; b < b1; ++b) sum += s_b[b];
-      const int incl = warp_incl_scan(sum);
-      if (lane == 31) s_part[warp] = incl;
-      __syncthreads();
-      if (warp == 0) { const int v = lane < nwarps ? s_part[lane] : 0; const int iv = warp_incl_scan(v); s_part[lane] = iv - v; }
-      __syncthreads();
-      int run = s_part[warp] + incl - sum;
-      for (int b = b0; b < b1; ++b) { const int n = s_b[b]; s_b[b] = run; run += n; }
-      if (tid == nt - 1) {
-        a.send_meta[0] = run;
-        a.send_meta[1] = a.cu_seqlens[2 * c.epn - 1];
-        a.send_meta[2] = 0; a.send_meta[3] = 0;
-      }
-      __syncthreads();
-    }
+  if (warp == 0) { const int v = lane < nwarps ? s_part[lane] : 0; const int iv = warp_incl_scan(v); s_part[lane] = iv - v; }
+  __syncthreads();
+  int run = s_part[warp] + incl - sum;
+  for (int b = b0; b < b1; ++b) { const int n = a.hist[b]; a.hist[b] = run; run += n; }
+  if (tid == nt - 1) {
+    a.send_meta[0] = run;
+    a.send_meta[1] = a.cu_seqlens[2 * c.epn - 1];
+    a.send_meta[2] = 0; a.send_meta[3] = 0;
+  }
+}
+
+__global__ void __launch_bounds__(256) send_place_kernel(MepCtxPack P, SendOrderArgsPack A) {
+  const MepRankCtx& c = *P.ctx[blockIdx.y];
+  const SendOrderArgs& a = A.a[blockIdx.y];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < c.N; i += gridDim.x * blockDim.x) {
+    const int b = a.bucket[i];
+    if (b >= 0) a.send_list[atomicAdd(a.hist + b, 1)] = i;
   }
 }
 
 // ------------------------------------------------------------------ dispatch
+// Shared memory: [kSendWarps x stages rows: sender rings][kExpWarps rows: one slot per expander warp]
+// [padding-row tables]. Every data movement goes through the copy engine (bulk copies), so the
+// bytes in flight per SM are the rows staged in shared memory, not registers.
 __global__ void __launch_bounds__(kFlagThreads, 1)
 dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const DispatchArgs& a = A.a[blockIdx.y];
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[kSendWarps * kMaxStages];
-  __shared__ uint32_t s_sig[kSendWarps][kSigRing];
+  __shared__ __align__(8) uint64_t s_xbar[kExpWarps];
+  __shared__ uint32_t s_sig[kSendWarps][kSigRing];               // (destination << 8 | slots stored) of a unit
+  __shared__ int s_sloff[kSendWarps][kSigRing][MEP_MAX_TOPK];     // the slots a unit stored to
   __shared__ int s_znext, s_ztotal;
   __shared__ int s_xtile, s_xn, s_xfail;
   __shared__ int s_xlist[MEP_FLAG_ROWS];
@@ -136,9 +156,11 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   if (tid == 0) { s_xfail = 0; s_xn = 0; }
   if (tid < MEP_MAX_RANKS) s_peer[tid] = 0;
   if (tid < kSendWarps * kMaxStages) mbar_init(&s_bar[tid], 1);
+  if (tid < kExpWarps) mbar_init(&s_xbar[tid], 1);
   fence_mbar_init();
   const int ngroups = 2 * c.epn;
-  int* s_zpre = reinterpret_cast<int*>(smem + (size_t)kSendWarps * stages * row_bytes);
+  unsigned char* xslots = smem + (size_t)kSendWarps * stages * row_bytes;
+  int* s_zpre = reinterpret_cast<int*>(xslots + (size_t)kExpWarps * row_bytes);
   int* s_zstart = s_zpre + ngroups + 1;
   for (int g = tid; g < ngroups; g += blockDim.x) { s_zstart[g] = a.zero_fill[2 * g]; s_zpre[g + 1] = a.zero_fill[2 * g + 1]; }
   __syncthreads();
@@ -180,7 +202,7 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
         rsrc[prow] = -1;
       }
       __syncwarp();                                  // every lane's stores precede the releasing arrival
-      if (lane == 0) red_release_sys_add(my_ready + prow / MEP_FLAG_ROWS, 1u);
+      if (lane == 0) { fence_proxy_async(); red_release_sys_add(my_ready + prow / MEP_FLAG_ROWS, 1u); }
       ++done;
     }
     if (lane == 0 && done) count(c, MEP_CNT_PAD_ROWS, (unsigned long long)done);
@@ -227,9 +249,20 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       if (e0 >= 0 && e0 < S * K && lane < K) { const size_t o = (size_t)(e0 / K) * K + lane; nd = a.dst[o]; nwt = a.weights ? a.weights[o] : 0.f; }
     }
     int sent = 0, sent_remote = 0;
-    auto signal = [&](int j) {                     // lane 0: unit j's store has completed
-      const uint32_t v = s_sig[warp][j & (kSigRing - 1)];
-      if (v != 0xffffffffu) red_release_sys_add(ready_of(c, (int)(v >> 24)) + (v & 0xffffffu), 1u);
+    // lane 0: the stores of units [signalled, upto) have completed -- one arrival per slot the token owns
+    // on the destination (the slot that got the row, and on a peer its duplicates, whose rowsrc entry was
+    // written before the store was issued). One system-scope fence covers the whole round.
+    int signalled = 0;
+    auto signal_upto = [&](int upto) {
+      if (upto <= signalled) return;
+      fence_proxy_async();
+      fence_acq_rel_sys();
+      for (int j = signalled; j < upto; ++j) {
+        const uint32_t v = s_sig[warp][j & (kSigRing - 1)];
+        uint32_t* rdy = ready_of(c, (int)(v >> 8));
+        for (int i = 0; i < (int)(v & 0xffu); ++i) red_relaxed_sys_add(rdy + s_sloff[warp][j & (kSigRing - 1)][i] / MEP_FLAG_ROWS, 1u);
+      }
+      signalled = upto;
     };
     int it = 0;
     for (; it < n; ++it) {
@@ -257,35 +290,52 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       if (lane < K) { const int raw = dval >= 0 ? dval : -dval - 1; d = raw / NvS; loff = raw - d * NvS; }
       const int du = __shfl_sync(0xffffffffu, d, kp), lu = __shfl_sync(0xffffffffu, loff, kp);
       const bool good = du >= 0 && du < c.R && e < S * K;   // the send list only names valid entries; checked all the same
-      if (good && lane < K && d == du) {
-        // side tables of every slot this token owns on that rank; duplicate slots arrive here
+      const bool local = du == c.rank;
+      const bool mine = good && lane < K && d == du;
+      if (mine) {
+        // side tables of every slot this token owns on that rank. On the own rank every slot gets the
+        // row itself (a store costs no link bandwidth there); on a peer only slot `lu` does and the
+        // other slots are duplicates that the peer expands from it.
         if (a.weights) ((float*)peer_ptr(c, du, c.off_weights))[loff] = w;
         if (a.srcinfo_off) ((int*)peer_ptr(c, du, (size_t)a.srcinfo_off))[loff] = c.rank * (S * K) + s * K + lane;
-        ((int*)peer_ptr(c, du, c.off_rowsrc))[loff] = lu;
-        if (loff != lu) red_release_sys_add(ready_of(c, du) + loff / MEP_FLAG_ROWS, 1u);
+        ((int*)peer_ptr(c, du, c.off_rowsrc))[loff] = local ? loff : lu;
       }
+      const unsigned owned = __ballot_sync(0xffffffffu, mine);
+      const unsigned stores = __ballot_sync(0xffffffffu, mine && (local || loff == lu));
       __syncwarp();
+      int nst = 0, nown = 0;
+      for (unsigned m = owned; m; m &= m - 1) {
+        const int k = __ffs(m) - 1;
+        const int lk = __shfl_sync(0xffffffffu, loff, k);
+        if (lane == 0) {
+          if ((stores >> k) & 1u) {
+            bulk_s2g(peer_ptr(c, du, c.off_hidden) + (size_t)lk * row_bytes, ring + (size_t)st * row_bytes, row_bytes);
+            ++nst;
+          }
+          s_sloff[warp][it & (kSigRing - 1)][nown] = lk;
+        }
+        ++nown;
+      }
       if (lane == 0) {
         if (good) {
-          bulk_s2g(peer_ptr(c, du, c.off_hidden) + (size_t)lu * row_bytes, ring + (size_t)st * row_bytes, row_bytes);
-          s_sig[warp][it & (kSigRing - 1)] = ((uint32_t)du << 24) | (uint32_t)(lu / MEP_FLAG_ROWS);
-          ++sent; sent_remote += du != c.rank;
-          if (c.counters) atomicAdd(&s_peer[du], 1);
+          sent += nst; if (!local) sent_remote += nst;
+          if (c.counters) atomicAdd(&s_peer[du], nst);
         } else {
           report(c, MEP_ERR_BOUNDS, MEP_K_DISPATCH, 41, s, (uint32_t)dval, (uint32_t)(c.R * NvS));
-          s_sig[warp][it & (kSigRing - 1)] = 0xffffffffu;
         }
+        s_sig[warp][it & (kSigRing - 1)] = ((uint32_t)(good ? du : 0) << 8) | (uint32_t)nown;
         bulk_commit();                               // one bulk group per unit, empty for a dropped one
-        if (it >= kSigLag) { bulk_wait_done<kSigLag>(); fence_proxy_async(); signal(it - kSigLag); }
+        if ((it % kSigBatch) == kSigBatch - 1 && it >= kSigLag) { bulk_wait_done<kSigLag>(); signal_upto(it + 1 - kSigLag); }
       }
     }
     if (lane == 0) {
-      bulk_wait_done<0>(); fence_proxy_async();
-      if (it == n) for (int j = n > kSigLag ? n - kSigLag : 0; j < n; ++j) signal(j);
+      bulk_wait_done<0>();
+      if (it == n) signal_upto(n);
       if (sent) { count(c, MEP_CNT_ROWS_SENT, (unsigned long long)sent); count(c, MEP_CNT_ROWS_REMOTE, (unsigned long long)sent_remote); }
       trace_mark(c, MEP_K_DISPATCH, 2);
     }
     zero_fill_work();
+    if (lane == 0) trace_mark(c, MEP_K_DISPATCH, 3);
   } else if (warp == kSendWarps) {
     // ---------------------------------------------------------------- zero-fill warp
     if (blockIdx.x == 0) {
@@ -298,13 +348,15 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       if (lane == 0) count(c, MEP_CNT_DISPATCHES, 1);
     }
     zero_fill_work();
+    if (lane == 0) trace_mark(c, MEP_K_DISPATCH, 4);
   } else {
     // ---------------------------------------------------------------- expanders
     const int xt = tid - (kSendWarps + 1) * 32, xw = xt >> 5;
     const int used_tiles = (cu_end + MEP_FLAG_ROWS - 1) / MEP_FLAG_ROWS;
     const int* rsrc = (const int*)peer_ptr(c, c.rank, c.off_rowsrc);
     char* hid = peer_ptr(c, c.rank, c.off_hidden);
-    const int nvec = (int)(row_bytes >> 4);
+    unsigned char* slot = xslots + (size_t)xw * row_bytes;
+    uint32_t xparity = 0;
     auto tile_complete = [&](int t, int site) {      // bounded wait for tile t's arrivals (any thread)
       const uint32_t target = ep * (uint32_t)tile_rows(c, t);
       uint32_t seen = 0;
@@ -336,23 +388,31 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       }
       bar_expanders();
       if (s_xfail) break;
+      // duplicate rows of this tile: row of the same shard -> this warp's slot -> duplicate slot, one
+      // row in flight per warp; everything a copy reads was acquired above
       const int nd_ = s_xn;
-      for (int i = xw; i < nd_; i += kExpWarps) {
-        const int v = s_xlist[i];
-        const char* srow = hid + (size_t)(v >> 7) * row_bytes;
-        char* drow = hid + (size_t)(t * MEP_FLAG_ROWS + (v & 127)) * row_bytes;
-        for (int v0 = 0; v0 < nvec; v0 += 256) {      // 8 x 16-byte loads in flight per lane
-          int4 x[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { const int q = v0 + j * 32 + lane; if (q < nvec) x[j] = ld_cg_v4(srow + (size_t)q * 16); }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) { const int q = v0 + j * 32 + lane; if (q < nvec) st_na_v4(drow + (size_t)q * 16, x[j]); }
+      if (lane == 0) {
+        fence_proxy_async();
+        for (int i = xw; i < nd_; i += kExpWarps) {
+          const int v = s_xlist[i];
+          bulk_wait_read<0>();                      // the previous store has left the slot
+          mbar_expect_tx(&s_xbar[xw], row_bytes);
+          bulk_g2s(slot, hid + (size_t)(v >> 7) * row_bytes, row_bytes, &s_xbar[xw]);
+          if (!mbar_wait_bounded(&s_xbar[xw], xparity, c.wait_budget_ns)) {
+            report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_DISPATCH, 63, t, 0, 0); s_xfail = 1; break;
+          }
+          xparity ^= 1u;
+          bulk_s2g(hid + (size_t)(t * MEP_FLAG_ROWS + (v & 127)) * row_bytes, slot, row_bytes);
+          bulk_commit();
         }
+        bulk_wait_done<0>(); fence_proxy_async();
       }
       if (xt == 0) ndup += nd_;
       bar_expanders();
-      if (xt == 0) { __threadfence(); st_release_gpu(c.tile_done + t, ep); }
+      if (s_xfail) break;
+      if (xt == 0) { __threadfence(); st_release_gpu(c.tile_done + t, ep); trace_mark(c, MEP_K_DISPATCH, 7); }
     }
+    if (xt == 0) trace_mark(c, MEP_K_DISPATCH, 6);
     if (xt == 0 && ndup) count(c, MEP_CNT_DUP_ROWS, (unsigned long long)ndup);
   }
   cross_rank_barrier(c, nb, 1, MEP_K_DISPATCH, 30);
@@ -381,17 +441,29 @@ extern "C" int mep_launch_flag_epoch_bump(int nv, const MepRankCtx* const* ctxs,
   return mep::launch_plain(mep::flag_epoch_bump_kernel, dim3(1, nv), dim3(32), 0, stream, P);
 }
 
-extern "C" int mep_launch_send_order(int nv, const MepRankCtx* const* ctxs, const mep::SendOrderArgs* args,
-                                     int NvS, int R, cudaStream_t stream) {
-  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "send_order: nv=%d out of range", nv);
-  MepCtxPack P = {}; mep::SendOrderArgsPack A = {};
-  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  // one bucket per (flag tile, destination); coarser tiles if that would not fit shared memory
+// nbuckets for a geometry: one bucket per (flag tile, destination), coarser tiles beyond 40960 buckets.
+extern "C" int mep_send_order_buckets(int NvS, int R, int* shift_out) {
   int shift = 7;
   while ((((long long)NvS >> shift) + 1) * R > 40960) ++shift;
-  const int nbuckets = (int)((((long long)NvS >> shift) + 1) * R);
-  return mep::launch_plain(mep::send_order_kernel, dim3(1, nv), dim3(1024), (size_t)nbuckets * sizeof(int), stream,
-                           P, A, shift, nbuckets);
+  if (shift_out) *shift_out = shift;
+  return (int)((((long long)NvS >> shift) + 1) * R);
+}
+
+extern "C" int mep_launch_send_order(int nv, const MepRankCtx* const* ctxs, const mep::SendOrderArgs* args,
+                                     int N, int NvS, int R, cudaStream_t stream) {
+  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "send_order: nv=%d out of range", nv);
+  MepCtxPack P = {}; mep::SendOrderArgsPack A = {};
+  int shift = 7;
+  const int nbuckets = mep_send_order_buckets(NvS, R, &shift);
+  for (int i = 0; i < nv; ++i) {
+    P.ctx[i] = ctxs[i]; A.a[i] = args[i];
+    MEP_REQUIRE(args[i].hist && args[i].bucket, "send_order: scratch missing");
+    MEP_CUDA_CHECK(cudaMemsetAsync(args[i].hist, 0, (size_t)nbuckets * sizeof(int), stream));
+  }
+  const int blocks = (N + 255) / 256 < 128 ? (N + 255) / 256 : 128;
+  if (mep::launch_plain(mep::send_classify_kernel, dim3(blocks, nv), dim3(256), 0, stream, P, A, shift, nbuckets)) return -1;
+  if (mep::launch_plain(mep::send_scan_kernel, dim3(1, nv), dim3(1024), 0, stream, P, A, nbuckets)) return -1;
+  return mep::launch_plain(mep::send_place_kernel, dim3(blocks, nv), dim3(256), 0, stream, P, A);
 }
 
 extern "C" int mep_launch_dispatch_flagged(int nv, const MepRankCtx* const* ctxs, const mep::DispatchArgs* args,
@@ -403,11 +475,13 @@ extern "C" int mep_launch_dispatch_flagged(int nv, const MepRankCtx* const* ctxs
     MEP_REQUIRE(args[i].send_list && args[i].send_meta, "dispatch: the plan carries no send list (it was not made by a flagged dispatch)");
   }
   const size_t row = (size_t)H * 2;
-  int stages = (int)((200 * 1024) / (row * mep::kSendWarps));
+  const size_t tables = (size_t)(4 * epn + 2) * sizeof(int);
+  const size_t budget = 216 * 1024;
+  MEP_REQUIRE(budget > tables + row * (mep::kExpWarps + mep::kSendWarps),
+              "dispatch: H=%d rows (%zu B) with epn=%d do not fit shared memory", H, row, epn);
+  int stages = (int)((budget - tables - row * mep::kExpWarps) / (row * mep::kSendWarps));
   if (stages > mep::kMaxStages) stages = mep::kMaxStages;
-  MEP_REQUIRE(stages >= 1, "dispatch: H=%d rows (%zu B) do not fit the shared-memory ring", H, row);
-  const size_t smem = row * mep::kSendWarps * stages + (size_t)(4 * epn + 2) * sizeof(int);
-  MEP_REQUIRE(smem <= 220 * 1024, "dispatch: epn=%d padding tables do not fit shared memory", epn);
+  const size_t smem = row * (mep::kSendWarps * stages + mep::kExpWarps) + tables;
   return mep::launch_cooperative(mep::dispatch_flagged_kernel, dim3(num_sms, nv), dim3(mep::kFlagThreads), smem,
                                  stream, false, P, A, stages);
 }

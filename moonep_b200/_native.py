@@ -66,7 +66,8 @@ class DispatchArgs(C.Structure):
 
 
 class SendOrderArgs(C.Structure):
-    _fields_ = [("dst", C.c_void_p), ("cu_seqlens", C.c_void_p), ("send_list", C.c_void_p), ("send_meta", C.c_void_p)]
+    _fields_ = [("dst", C.c_void_p), ("cu_seqlens", C.c_void_p), ("send_list", C.c_void_p), ("send_meta", C.c_void_p),
+                ("hist", C.c_void_p), ("bucket", C.c_void_p)]
 
 
 class PushReduceArgs(C.Structure):

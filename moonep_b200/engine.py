@@ -230,10 +230,16 @@ def launch_send_order(states, plans, cu_list):
     lib = _native.load()
     n = len(states)
     args = (SendOrderArgs * n)()
-    for i in range(n):
-        args[i] = SendOrderArgs(ptr(plans[i].dst), ptr(cu_list[i]), ptr(plans[i].send_list), ptr(plans[i].send_meta))
     g = states[0].geo
-    _native.check(lib.mep_launch_send_order(n, _pack(states), args, g.NvS, g.R, _native.cur_stream()), "send_order")
+    for i in range(n):
+        sc = states[i].scratch
+        if "send_hist" not in sc:       # bucket histogram and per-entry bucket, sized on first use
+            nb = lib.mep_send_order_buckets(g.NvS, g.R, None)
+            sc["send_hist"] = torch.zeros(nb, dtype=torch.int32, device=states[i].device)
+            sc["send_bucket"] = torch.empty(g.N, dtype=torch.int32, device=states[i].device)
+        args[i] = SendOrderArgs(ptr(plans[i].dst), ptr(cu_list[i]), ptr(plans[i].send_list), ptr(plans[i].send_meta),
+                                ptr(sc["send_hist"]), ptr(sc["send_bucket"]))
+    _native.check(lib.mep_launch_send_order(n, _pack(states), args, g.N, g.NvS, g.R, _native.cur_stream()), "send_order")
 
 
 def launch_flag_epoch_bump(states):

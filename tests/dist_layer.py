@@ -1,0 +1,151 @@
+"""Multi-process check of the fused MoE layer on real GPUs (one rank per GPU, peer memory over
+NVLink): ``ExpertParallelMoE`` forward and backward against a dense fp32 implementation of the same
+top-k MoE built from all-gathered inputs and weights.
+
+Run:  torchrun --nproc-per-node N --master-addr 127.0.0.1 --master-port P tests/dist_layer.py
+Variants: push-combine on / off (peer stores from the down GEMM's epilogue), tile-ready flags on /
+off (GEMMs that consume the shard while the dispatch kernel is still receiving), backward overlap on /
+off (split launches beside the communication kernels).  Routing is skewed so that the planner creates
+redundant experts (prefetch + cross-rank gradient reduction are exercised).
+Counterpart of the reference's public-API scenario tests/test_e2e.py:195-397, one level up: through the
+layer that integrates the API with the expert GEMMs.  A failed check is agreed on collectively between
+variants, so no rank leaves while a peer still touches its memory.
+"""
+import itertools
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from moonep_b200 import Buffer, routing  # noqa: E402
+from moonep_b200.moe_layer import ExpertParallelMoE, moe_apply  # noqa: E402
+from moonep_b200.ops import grouped_gemm as gg  # noqa: E402
+from moonep_b200.pools import ExpertPools  # noqa: E402
+
+ERRORS = []
+
+
+def chk(cond, msg):
+    if not bool(cond):
+        ERRORS.append(str(msg))
+
+
+def agree(name):
+    """Collective: True if no rank has recorded an error so far."""
+    torch.cuda.synchronize()
+    ok = torch.tensor([0 if ERRORS else 1], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return int(ok) == 1
+
+
+def gather(t):
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t.contiguous())
+    return out
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+def dense_reference(xs, ws, topks, gys, Wg, Wu, Wd, rank, epn):
+    """fp32 MoE over ALL ranks' tokens; returns this rank's output, input grad, route-weight grad and the
+    weight grads of its own experts."""
+    R = len(xs)
+    X = [x.float().requires_grad_(True) for x in xs]
+    Wt = [w.clone().requires_grad_(True) for w in ws]
+    Wg, Wu, Wd = (t.float().requires_grad_(True) for t in (Wg, Wu, Wd))
+    outs = []
+    for r in range(R):
+        y = torch.zeros_like(X[r])
+        for k in range(topks[r].shape[1]):
+            e = topks[r][:, k].long()
+            h = torch.nn.functional.silu(torch.einsum("sh,shp->sp", X[r], Wg[e])) * torch.einsum("sh,shp->sp", X[r], Wu[e])
+            y = y + Wt[r][:, k:k + 1] * torch.einsum("sp,sph->sh", h, Wd[e])
+        outs.append(y)
+    torch.autograd.backward(outs, [g.float() for g in gys])
+    sl = slice(rank * epn, (rank + 1) * epn)
+    return outs[rank].detach(), X[rank].grad, Wt[rank].grad, Wg.grad[sl], Wu.grad[sl], Wd.grad[sl]
+
+
+def main():
+    dist.init_process_group("nccl")
+    rank, R = dist.get_rank(), dist.get_world_size()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    S, H, Hp, K, epn, pad = 256, 256, 256, 4, 4, 128
+    E = R * epn
+    topk = routing.lognormal_topk(S, K, E, R, 1.2, 3, rank)[0].to(dev)
+    tpe = torch.bincount(topk.flatten().long(), minlength=E).to(torch.int32)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    x0 = (torch.randn(S, H, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    w0 = torch.rand(S, K, device=dev, generator=g) + 0.1
+    w0 = (w0 / w0.sum(dim=1, keepdim=True)).contiguous()
+    gy = (torch.randn(S, H, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+    local_w = {n: (torch.randn(epn, *shp, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+               for n, shp in (("gate", (H, Hp)), ("up", (H, Hp)), ("down", (Hp, H)))}
+    xs, ws, topks, gys = gather(x0), gather(w0), gather(topk), gather(gy)
+    allw = {n: torch.cat(gather(t)) for n, t in local_w.items()}
+    want = dense_reference(xs, ws, topks, gys, allw["gate"], allw["up"], allw["down"], rank, epn)
+    redundancy_seen = False
+
+    variants = list(itertools.product((False, True), (False, True), (False, True)))     # push, flags, overlap
+    for push, flags, overlap in variants:
+        name = f"push={int(push)} flags={int(flags)} overlap={int(overlap)}"
+        buf = Buffer(S, H, K, E, R, num_sms=8, token_padding=pad, push_combine=push)
+        pools = ExpertPools(epn, (H, Hp), (H, Hp), (Hp, H), with_grads=True)
+        for n in ("gate", "up", "down"):
+            pools.local_weight(n).copy_(local_w[n])
+            pools.compute_grad(n).zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        layer = ExpertParallelMoE(buf, pools, overlap_backward=overlap, ready_flags=flags)
+        for rep in range(2):            # twice: barrier epochs, flag epochs and ticket counters carry over
+            x = x0.clone().requires_grad_(True)
+            w = w0.clone().requires_grad_(True)
+            y = moe_apply(layer, x, w, topk, tpe)
+            y.backward(gy)
+            layer.wait_grads()
+            torch.cuda.synchronize()
+            try:
+                buf.check()
+                gg.check_status()
+            except Exception as exc:      # noqa: BLE001
+                ERRORS.append(f"{name}: {type(exc).__name__}: {exc}")
+            got = (y, x.grad, w.grad, pools.local_grad("gate"), pools.local_grad("up"), pools.local_grad("down"))
+            for label, a, b, tol in zip(("output", "grad hidden", "grad route weights", "grad gate", "grad up", "grad down"),
+                                        got, want, (2e-2, 3e-2, 3e-2, 3e-2, 3e-2, 3e-2)):
+                chk(torch.isfinite(a.float()).all(), f"{name} rep {rep}: {label} is not finite")
+                chk(rel(a, b) < tol, f"{name} rep {rep}: {label} off by {rel(a, b):.4f}")
+        if not redundancy_seen:
+            c = buf.counters()
+            sent = torch.tensor([c.get("rows_sent_remote", 0)], device=dev)
+            dist.all_reduce(sent)
+            chk(int(sent) > 0 or R == 1, "no row crossed a link")
+            redundancy_seen = True
+        ok = agree(name)
+        if rank == 0:
+            print(f"[dist_layer] {name}: {'ok' if ok else 'FAILED'}", flush=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        pools.destroy()
+        buf.destroy()
+        dist.barrier()
+        if not ok:
+            break
+    if ERRORS:
+        for e in ERRORS[:8]:
+            print(f"[dist_layer] rank {rank}: {e}", flush=True)
+    failed = not agree("end")
+    dist.destroy_process_group()
+    if failed:
+        sys.exit(1)
+    if rank == 0:
+        print(f"[dist_layer] PASS on {R} ranks")
+
+
+if __name__ == "__main__":
+    main()

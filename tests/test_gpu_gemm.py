@@ -173,3 +173,69 @@ def test_two_launches_share_one_ticket_counter(pair_kernels, cuda_device, monkey
             assert _relerr(dW[gi], 3.0 + x[a:b].float().T @ dgu[a:b].float()) < 2e-3, f"group {gi}: wgrad (each tile once)"
     from moonep_b200.ops.grouped_gemm import _sched_cache
     assert int(_sched_cache[dA.device.index][0].abs().sum()) == 0, "ticket counters must be left at zero"
+
+
+@pytest.mark.parametrize("split", [False, True], ids=["one_launch", "116+32_ctas_one_ticket"])
+def test_benchmark_shape_against_fp32_on_sampled_tiles(split, cuda_device):
+    """The shape the step benchmark runs (hidden 7168, inner 2048, 32 groups of uneven size, i.e. 112
+    k-blocks per tile for gate/up and 32 for down, hundreds of tiles per CTA): every mode is checked
+    against fp32 on sampled rows of sampled groups, once as a single launch and once as the two
+    launches on one ticket counter that the layer uses beside a communication kernel."""
+    from moonep_b200.ops import grouped_gemm as gg
+    H, Hp, G = 7168, 2048, 32
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    rpg = [128 * int(v) for v in torch.randint(0, 7, (G,), generator=torch.Generator().manual_seed(4))]
+    rpg[3], rpg[17] = 0, 1152
+    cu, tot, rows, x, _ = _setup(G, rpg, H, Hp, seed=9)
+    wg = (torch.randn(G, H, Hp, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    wu = (torch.randn(G, H, Hp, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(G, Hp, H, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    scale = torch.rand(rows, device="cuda", generator=gen) + 0.5
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+
+    def run(fn):
+        """fn(num_ctas, ticket) launches one GEMM."""
+        if not split:
+            fn(None, None)
+            return
+        tk = gg.Ticket("cuda", sms)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        fn(sms - 32, tk)
+        with torch.cuda.stream(side):
+            fn(32, tk)
+        torch.cuda.current_stream().wait_stream(side)
+
+    act = torch.zeros(rows, Hp, dtype=torch.bfloat16, device="cuda")
+    gu = torch.zeros(rows, 2 * Hp, dtype=torch.bfloat16, device="cuda")
+    run(lambda n, tk: gg.gate_up(x, wg, wu, cu, act, gu, row_scale=scale, num_ctas=n, ticket=tk))
+    y = torch.zeros(rows, H, dtype=torch.bfloat16, device="cuda")
+    run(lambda n, tk: gg.down(act, wd, cu, y, num_ctas=n, ticket=tk))
+    dA = torch.zeros(rows, Hp, dtype=torch.bfloat16, device="cuda")
+    run(lambda n, tk: gg.dgrad(y, wd, cu, dA, num_ctas=n, ticket=tk))
+    dx = torch.zeros(rows, H, dtype=torch.bfloat16, device="cuda")
+    run(lambda n, tk: gg.dgrad_gate_up(gu, wg, wu, cu, dx, num_ctas=n, ticket=tk))
+    dW = torch.zeros(G, H, Hp, device="cuda")
+    run(lambda n, tk: gg.wgrad(x, act, cu, dW, accumulate=False, zero_empty_below=G, num_ctas=n, ticket=tk))
+    torch.cuda.synchronize()
+    gg.check_status()
+    pick = torch.Generator().manual_seed(1)
+    for gi, a, b in _group_slices(rpg):
+        if a == b:
+            assert (dW[gi] == 0).all()
+            continue
+        if gi % 3 and gi != 17:
+            continue
+        rsel = (a + torch.randperm(b - a, generator=pick)[:48]).cuda()       # rows from every 128-row tile region
+        xf = x[rsel].float()
+        gr, ur = xf @ wg[gi].float(), xf @ wu[gi].float()
+        assert _relerr(gu[rsel, :Hp], gr) < 1e-2 and _relerr(gu[rsel, Hp:], ur) < 1e-2, f"group {gi}: pre-activations"
+        assert _relerr(act[rsel], torch.nn.functional.silu(gr) * ur * scale[rsel, None]) < 1.5e-2, f"group {gi}: swiglu"
+        assert _relerr(y[rsel], act[rsel].float() @ wd[gi].float()) < 1e-2, f"group {gi}: down"
+        assert _relerr(dA[rsel], y[rsel].float() @ wd[gi].float().T) < 1e-2, f"group {gi}: dgrad"
+        ref = gu[rsel, :Hp].float() @ wg[gi].float().T + gu[rsel, Hp:].float() @ wu[gi].float().T
+        assert _relerr(dx[rsel], ref) < 1e-2, f"group {gi}: dgrad gate/up"
+        csel = torch.randperm(Hp, generator=pick)[:64].cuda()
+        wref = x[a:b].float().T @ act[a:b][:, csel].float()
+        assert _relerr(dW[gi][:, csel], wref) < 3e-3, f"group {gi}: wgrad"
+    assert (act[tot:] == 0).all() and (y[tot:] == 0).all(), "rows beyond cu_seqlens[-1] were written"
