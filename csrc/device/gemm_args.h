@@ -42,8 +42,14 @@ struct GemmArgs {
   const uint32_t* tile_done;
   const uint32_t* tile_epoch;
   int32_t* status_host;        // optional host-mapped copy of status[0]
+  // optional: the weights of groups g >= group_first are still being written by a prefetch. group_flags[g -
+  // group_first] holds the prefetch epoch at which that slot became complete; the TMA producer waits (bounded)
+  // for it to reach *group_epoch before it loads weights of such a group.
+  const uint32_t* group_flags;
+  const uint32_t* group_epoch;
   int32_t push_rows;
   int32_t push_ranks;
+  int32_t group_first;
   int32_t sched_ctas;          // dynamic order: CTAs over ALL launches that draw from `sched` (several launches of
                                // one GEMM may share a counter); 0 = just this launch
 };

@@ -4,10 +4,14 @@
 // launched three times (gate, up, down); here ONE launch handles all projections:
 //   1. prescan of experts_to_copy -> per local expert the list of (rank, slot) pairs holding
 //      one of its replicas, sorted ascending;
+//   1b. optional entry barrier: a replica may only be read once its holder's weight-gradient GEMM
+//      has finished (the reference leaves this to the caller, api.py:1154-1158; here the public
+//      call does it unless told otherwise, since nothing else orders the ranks at that point);
 //   2. local_grad[e] += reduce[d0, b0] + reduce[d1, b1] + ...  in that fixed order (bitwise
 //      reproducible), peer slots read with plain 16-byte loads;
 //   3. cross-rank barrier (every owner has consumed its replicas);
-//   4. each rank zeroes ITS OWN consumed slots for the next microbatch.
+//   4. each rank zeroes ITS OWN consumed slots for the next microbatch (steps 3 and 4 can be
+//      switched off by a caller whose next weight-gradient GEMM overwrites the slots it uses).
 #include "prims.cuh"
 #include "../host/launch.h"
 
@@ -22,7 +26,7 @@ struct ReduceTensor {
 struct GradReduceArgs {
   const int32_t* etc;
   int32_t ntensors;
-  int32_t pad;
+  int32_t flags;              // bit 0: cross-rank barrier before the first peer read; bit 1: leave the consumed slots as they are
   ReduceTensor t[3];
 };
 struct GradReduceArgsPack { GradReduceArgs a[MEP_MAX_VRANKS]; };
@@ -85,6 +89,7 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
   }
   __syncthreads();
   const int nact = s_nact;
+  if ((a.flags & 1) && !cross_rank_barrier(c, nb, 1, MEP_K_GRAD_REDUCE, 5)) return;
 
   // Each warp owns a 16 KB shared-memory stage of 32 slots (one slot = one 16-byte vector per
   // lane). A work unit is P vectors per lane of ONE expert matrix: the warp fetches them from EVERY
@@ -203,6 +208,7 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
     }
   }
 
+  if (a.flags & 2) return;
   if (!cross_rank_barrier(c, nb, 1, MEP_K_GRAD_REDUCE, 10)) return;
 
   // clear my own consumed slots

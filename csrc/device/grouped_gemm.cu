@@ -29,6 +29,17 @@ namespace mep {
 
 
 
+// Same for a flag that another GPU writes (system scope).
+__device__ __forceinline__ bool wait_flag_bounded_sys(const uint32_t* flag, uint32_t epoch, uint64_t budget_ns) {
+  if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+  const long long t0 = clock64(), lim = budget_cycles(budget_ns);
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) { __nanosleep(200); if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true; }
+    if (clock64() - t0 > lim) return false;
+  }
+}
+
 constexpr int kBM = 128, kBN = 256, kBK = 64;
 constexpr int kABytes = kBM * kBK * 2;            // 16 KB
 constexpr int kBBytes = kBN * kBK * 2;            // 32 KB
@@ -150,6 +161,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tq::Strided seq{(int)blockIdx.x, (int)gridDim.x, ntiles};
       const uint32_t flag_ep = args.tile_done ? *(volatile const uint32_t*)args.tile_epoch : 0u;
       int flag_tile = -1;                  // last row tile whose flag was seen complete
+      const uint32_t group_ep = args.group_flags ? *(volatile const uint32_t*)args.group_epoch : 0u;
+      int flag_group = -1;                 // last group whose weights were seen complete
       for (int t; !s_abort && (t = dyn ? sched.next(args.budget_ns) : seq.next()) != -1;) {
         if (t == -2) { fail(5, sched.n); break; }
         get_tile(t, gcur, ti);
@@ -160,6 +173,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           if (!wait_flag_bounded(f, flag_ep, args.budget_ns)) { fail(9, t); break; }
           fence_proxy_async();
           flag_tile = ti.row0 >> 7;
+        }
+        if (args.group_flags && ti.kblocks > 0 && ti.g >= args.group_first && ti.g != flag_group) {
+          // the weights of this group are a prefetched expert that may still be on its way
+          if (!wait_flag_bounded_sys(args.group_flags + (ti.g - args.group_first), group_ep, args.budget_ns)) { fail(9, t); break; }
+          fence_proxy_async();
+          flag_group = ti.g;
         }
         for (int kb = 0; kb < ti.kblocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (uint32_t)(it / kStages) & 1u;

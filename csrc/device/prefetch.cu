@@ -7,6 +7,10 @@
 // dealt round-robin to the CTAs and moved with 16-byte local loads and 16-byte peer stores
 // (eight per thread in flight) -- no TMA touches peer memory. Dtype-agnostic (bytes).
 // Ends with a cross-rank barrier: on return every rank's slots are complete.
+// Per-slot flags on top of that (the reference only has the trailing barrier, moonep/prefetch.py:467-470):
+// the CTA that finishes the LAST chunk of a slot release-stores the launch's prefetch epoch into the
+// holder's flag word for that slot, so a consumer on the holder (the grouped GEMM, group epn + b) can start
+// on a prefetched expert as soon as that expert has landed instead of waiting for the whole launch.
 #include "prims.cuh"
 #include "../host/launch.h"
 
@@ -37,6 +41,7 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
   __shared__ int s_n;
   const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x;
   const int R = c.R, epn = c.epn, lo = c.rank * epn;
+  const uint32_t ep = c.pf_epoch ? *(volatile uint32_t*)c.pf_epoch : 0u;
 
   // Slot list in ascending (rank, slot) order. Every CTA must build the IDENTICAL list, because
   // work unit u is mapped to list entry u / chunks_per_slot on whichever CTA owns u: one warp
@@ -79,11 +84,38 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
       for (int j = 0; j < kVec; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) st_na_v4(dstp + (size_t)v * 16, x[j]); }
     }
     for (int64_t i = ((int64_t)nvec << 4) + tid; i < len; i += nt) dstp[i] = src[i];   // ragged tail
+    if (c.slot_done) {
+      // count the chunk; whoever completes the slot publishes its flag on the holder
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence_system();
+        if (atomicAdd(c.slot_done + idx, 1u) == (uint32_t)chunks_per_slot - 1u) {
+          c.slot_done[idx] = 0u;
+          __threadfence();
+          st_release_sys((uint32_t*)peer_ptr(c, d, c.off_slotflag) + b, ep);
+        }
+      }
+    }
   }
   cross_rank_barrier(c, nb, 1, MEP_K_PREFETCH, 10);
 }
 
 }  // namespace mep
+
+// One thread: a prefetch is about to be issued (see MepRankCtx.pf_epoch).
+namespace mep {
+__global__ void pf_epoch_bump_kernel(MepCtxPack P) {
+  const MepRankCtx* c = P.ctx[blockIdx.y];
+  if (threadIdx.x == 0 && c->pf_epoch) c->pf_epoch[0] += 1u;
+}
+}  // namespace mep
+
+extern "C" int mep_launch_pf_epoch_bump(int nv, const MepRankCtx* const* ctxs, cudaStream_t stream) {
+  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "pf_epoch_bump: nv=%d out of range", nv);
+  MepCtxPack P = {};
+  for (int i = 0; i < nv; ++i) P.ctx[i] = ctxs[i];
+  return mep::launch_plain(mep::pf_epoch_bump_kernel, dim3(1, nv), dim3(32), 0, stream, P);
+}
 
 extern "C" int mep_launch_prefetch(int nv, const MepRankCtx* const* ctxs, const mep::PrefetchArgs* args,
                                    int num_sms, int R, int epn, cudaStream_t stream) {

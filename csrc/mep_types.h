@@ -107,6 +107,12 @@ typedef struct MepRankCtx {
   int32_t reserved1;
   // per-op counters (null = off), see MepCounters
   unsigned long long* counters;
+  // per-slot prefetch flags (prefetch -> consumer GEMM), see prefetch_kernel
+  //   heap, off_slotflag: uint32 [epn]: prefetch epoch at which slot b of this rank last became complete
+  int64_t off_slotflag;
+  uint32_t* slot_done;     // local [R * epn]: chunks of slot (d, b) this rank has finished copying (self-resetting)
+  uint32_t* pf_epoch;      // local [1]: prefetch launches issued so far (advanced by pf_epoch_bump in stream order
+                           // before the prefetch kernel and before every consumer of its slot flags)
 } MepRankCtx;
 
 typedef struct MepCtxPack { const MepRankCtx* ctx[MEP_MAX_VRANKS]; } MepCtxPack;

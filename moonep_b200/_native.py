@@ -45,7 +45,8 @@ class MepRankCtx(C.Structure):
                                      "alloc_cumsum", "expert_off", "etc_all", "stats_all", "send_cnt", "status")]
         + [("wait_budget_ns", C.c_uint64), ("trace", C.c_void_p), ("trace_cap", C.c_int64), ("mc_base", C.c_void_p), ("vb_flags", C.c_void_p)]
         + [("status_host", C.c_void_p), ("off_rowsrc", C.c_int64), ("tile_done", C.c_void_p), ("flag_epoch", C.c_void_p),
-           ("ntiles", C.c_int32), ("reserved1", C.c_int32), ("counters", C.c_void_p)]
+           ("ntiles", C.c_int32), ("reserved1", C.c_int32), ("counters", C.c_void_p),
+           ("off_slotflag", C.c_int64), ("slot_done", C.c_void_p), ("pf_epoch", C.c_void_p)]
     )
 
 COUNTER_SLOTS = 64
@@ -99,7 +100,7 @@ class ReduceTensor(C.Structure):
 
 
 class GradReduceArgs(C.Structure):
-    _fields_ = [("etc", C.c_void_p), ("ntensors", C.c_int32), ("pad", C.c_int32), ("t", ReduceTensor * 3)]
+    _fields_ = [("etc", C.c_void_p), ("ntensors", C.c_int32), ("flags", C.c_int32), ("t", ReduceTensor * 3)]
 
 
 def lib_path() -> Path:

@@ -95,6 +95,15 @@ class TileReady:
         self.done_ptr, self.epoch_ptr, self.free_sms = done_ptr, epoch_ptr, free_sms
 
 
+class SlotReady:
+    """Handle on the per-slot flags of ``prefetch_weight`` for the grouped GEMM that reads the prefetched
+    experts (``ops.grouped_gemm.gate_up(..., slots=...)``): group ``first + b`` of the compute view is
+    prefetch slot ``b``; the GEMM waits for a slot's flag before it loads that group's weights."""
+
+    def __init__(self, flags_ptr: int, epoch_ptr: int, first: int):
+        self.flags_ptr, self.epoch_ptr, self.first = flags_ptr, epoch_ptr, first
+
+
 class OpsMixin:
     """The collective operations, written over lists of per-rank arguments.  ``self._states``
     holds the ranks this process hosts (one for ``Buffer``)."""
@@ -157,6 +166,10 @@ class OpsMixin:
         out_h = [s.hidden_local for s in st]
         out_w = [s.weights_local if weights is not None else None for s in st]
         return out_h, out_w, cus, plans, ev
+
+    def _slot_ready(self, i: int = 0) -> SlotReady:
+        st, g = self._states[i], self.geo
+        return SlotReady(st.heap.base + st.rank * st.heap.chunk_bytes + g.off_slotflag, st.scratch["pf_epoch"].data_ptr(), g.epn)
 
     def _tile_ready(self, i: int = 0) -> TileReady:
         st = self._states[i]
@@ -285,8 +298,9 @@ class OpsMixin:
     def _prefetch_lists(self, plans, pairs_list):
         engine.launch_prefetch(self._states, [p.experts_to_copy for p in plans], pairs_list)
 
-    def _reduce_lists(self, plans, pairs_list):
-        engine.launch_grad_reduce(self._states, [p.experts_to_copy for p in plans], pairs_list)
+    def _reduce_lists(self, plans, pairs_list, inter_rank_sync: bool = True, clear_slots: bool = True):
+        engine.launch_grad_reduce(self._states, [p.experts_to_copy for p in plans], pairs_list,
+                                  entry_barrier=inter_rank_sync, clear_slots=clear_slots)
 
 
 class Buffer(OpsMixin):
@@ -402,7 +416,8 @@ class Buffer(OpsMixin):
         g = self.geo
         self._heap.view(st.rank, g.off_bar, (4 * 128,), torch.int32).zero_()
         self._heap.view(st.rank, g.off_ready, (g.ntiles,), torch.int32).zero_()
-        for name in ("grid_bar", "epoch", "send_cnt", "vb_flags", "tile_done", "flag_epoch"):
+        self._heap.view(st.rank, g.off_slotflag, (g.epn,), torch.int32).zero_()
+        for name in ("grid_bar", "epoch", "send_cnt", "vb_flags", "tile_done", "flag_epoch", "slot_done", "pf_epoch"):
             st.scratch[name].zero_()
         st.status.zero_()
         st.status_host.zero_()
@@ -566,6 +581,15 @@ class Buffer(OpsMixin):
         _, ev = self._run(async_finish, tensors, lambda: self._prefetch_lists([plan], [pairs]), "moonep.prefetch_weight")
         return ev
 
+    def slot_ready(self) -> SlotReady:
+        """Per-slot flags of the ``prefetch_weight`` launched last (extension; the reference only has the
+        launch's trailing barrier, moonep/prefetch.py:467-470).  Pass it as ``slots=`` to the grouped GEMMs
+        that read the compute view ``[local | slots]`` and are launched, in stream order, after that
+        ``prefetch_weight`` call was issued (it may still be running on the communication stream): groups of
+        prefetched experts are then loaded as soon as their own weights have landed."""
+        self._st()
+        return self._slot_ready(0)
+
     # ---- combine
     def combine(self, plan: MoonEPCommPlan | None = None, hidden_nvsh: torch.Tensor | None = None,
                 route_weights_nvs: torch.Tensor | None = None, async_finish: bool = False,
@@ -613,10 +637,14 @@ class Buffer(OpsMixin):
     # ---- reduce_grad
     def reduce_grad(self, plan: MoonEPCommPlan | None = None, async_finish: bool = False, *,
                     local_gate_grad=None, local_up_grad=None, local_down_grad=None,
-                    gate_reduce_buffer=None, up_reduce_buffer=None, down_reduce_buffer=None):
+                    gate_reduce_buffer=None, up_reduce_buffer=None, down_reduce_buffer=None,
+                    inter_rank_sync: bool = True):
         """Accumulate the gradients of this rank's replicated experts from every rank's reduce
         slots into the local fp32 parameter grads (fixed order), then zero this rank's own
-        consumed slots.  All ranks' reduce-buffer writes must be complete on entry."""
+        consumed slots.  The kernel first waits for every rank (``inter_rank_sync``, default on), so
+        each holder's reduce-buffer writes queued before its own call are complete when they are read;
+        pass ``inter_rank_sync=False`` only if something else already orders the ranks (the reference
+        leaves this to the caller, api.py:1154-1158 there)."""
         self._st()
         locals_ = (local_gate_grad, local_up_grad, local_down_grad)
         pools = (gate_reduce_buffer, up_reduce_buffer, down_reduce_buffer)
@@ -627,22 +655,26 @@ class Buffer(OpsMixin):
         self._check_weight_pairs(locals_, pools, (torch.float32,), "reduce_grad")
         pairs = list(zip(locals_, pools))
         tensors = [plan.experts_to_copy] + [t for pr in pairs for t in pr]
-        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs]), "moonep.reduce_grad")
+        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs], inter_rank_sync), "moonep.reduce_grad")
         return ev
 
-    def reduce_grad_subset(self, plan: MoonEPCommPlan, grads, async_finish: bool = False):
+    def reduce_grad_subset(self, plan: MoonEPCommPlan, grads, async_finish: bool = False, *, inter_rank_sync: bool = True,
+                           clear_slots: bool = True):
         """``reduce_grad`` for any non-empty subset of the projections: ``grads`` is a sequence of
         ``(local_grad [epn, ...] fp32, reduce_buffer [R, epn, ...] fp32)`` pairs.  Lets a training
         step reduce the gradient of one projection while it still computes the others.  Collective
-        like ``reduce_grad``: every rank must issue the same calls in the same order.  (Extension:
-        the reference only offers the three-projection call.)"""
+        like ``reduce_grad``: every rank must issue the same calls in the same order.
+        ``clear_slots=False`` leaves the consumed slots as they are (no second barrier, no zeroing): for a
+        caller whose next weight-gradient GEMM overwrites every slot it uses.  (Extension: the reference
+        only offers the three-projection call.)"""
         self._st()
         assert isinstance(plan, MoonEPCommPlan), "Buffer.reduce_grad_subset: plan is required"
         pairs = [(l, p) for l, p in grads]
         assert 1 <= len(pairs) <= 3, "reduce_grad_subset takes one to three (local_grad, reduce_buffer) pairs"
         self._check_weight_pairs([l for l, _ in pairs], [p for _, p in pairs], (torch.float32,), "reduce_grad_subset")
         tensors = [plan.experts_to_copy] + [t for pr in pairs for t in pr]
-        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs]), "moonep.reduce_grad")
+        _, ev = self._run(async_finish, tensors, lambda: self._reduce_lists([plan], [pairs], inter_rank_sync, clear_slots),
+                          "moonep.reduce_grad")
         return ev
 
     # ---- teardown

@@ -87,6 +87,8 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     s["send_cnt"] = torch.zeros(2 * R, dtype=torch.int64, device=dev)     # two halves, see planning_fast_kernel
     s["tile_done"] = torch.zeros(geo.ntiles, **i32)           # ready flags: epoch at which a tile became complete
     s["flag_epoch"] = torch.zeros(4, **i32)                   # [0] flagged dispatches issued, [1] expander ticket
+    s["slot_done"] = torch.zeros(R * epn, **i32)              # prefetch: chunks finished per (rank, slot), self-resetting
+    s["pf_epoch"] = torch.zeros(2, **i32)                     # prefetch launches issued
     if os.environ.get("MOONEP_COUNTERS", "1") != "0":
         s["counters"] = torch.zeros(_native.COUNTER_SLOTS, dtype=torch.int64, device=dev)
     st.status = torch.zeros(8, **i32)
@@ -101,11 +103,12 @@ def make_rank_state(geo: Geometry, rank: int, heap, device, budget_ns: int | Non
     c.checked = 1 if os.environ.get("MOONEP_CHECKED") == "1" else 0
     c.heap_base, c.chunk_stride = heap.base, heap.chunk_bytes
     for name in ("off_hidden", "off_weights", "off_tpe", "off_bar", "off_dupcnt", "off_dupgroups",
-                 "off_duploffs", "off_ready", "off_rowsrc"):
+                 "off_duploffs", "off_ready", "off_rowsrc", "off_slotflag"):
         setattr(c, name, getattr(geo, name))
     c.dup_group_cap, c.dup_loff_cap = geo.dup_group_cap, geo.dup_loff_cap
     for name in ("grid_bar", "epoch", "hist", "count", "tpe_prefix", "remaining", "alloc", "alloc_cumsum",
-                 "expert_off", "etc_all", "stats_all", "send_cnt", "vb_flags", "tile_done", "flag_epoch"):
+                 "expert_off", "etc_all", "stats_all", "send_cnt", "vb_flags", "tile_done", "flag_epoch", "slot_done",
+                 "pf_epoch"):
         setattr(c, name, s[name].data_ptr())
     c.ntiles = geo.ntiles
     c.counters = s["counters"].data_ptr() if "counters" in s else None
@@ -327,16 +330,23 @@ def launch_prefetch(states, etc_list, tensor_pairs_list):
             a.t[j].rank_stride = _rank_stride_bytes(pool)
         args[i] = a
     g = states[0].geo
+    # new prefetch epoch first (stream order): the kernel stamps completed slots with it and a GEMM that
+    # consumes the slots while the prefetch runs compares against it
+    _native.check(lib.mep_launch_pf_epoch_bump(n, _pack(states), _native.cur_stream()), "pf_epoch_bump")
     _native.check(lib.mep_launch_prefetch(n, _pack(states), args, g.num_sms, g.R, g.epn, _native.cur_stream()), "prefetch")
 
 
-def launch_grad_reduce(states, etc_list, tensor_pairs_list):
+def launch_grad_reduce(states, etc_list, tensor_pairs_list, entry_barrier: bool = True, clear_slots: bool = True):
+    """``entry_barrier``: wait for every rank before the first peer read (the holders' weight-gradient
+    GEMMs are then complete).  ``clear_slots=False`` skips the second barrier and the zeroing of the
+    consumed slots (for callers that overwrite, not accumulate into, the slots they use next time)."""
     lib = _native.load()
     n = len(states)
     args = (GradReduceArgs * n)()
     for i in range(n):
         a = GradReduceArgs()
         a.etc = ptr(etc_list[i])
+        a.flags = (1 if entry_barrier else 0) | (0 if clear_slots else 2)
         pairs = tensor_pairs_list[i]
         a.ntensors = len(pairs)
         for j, (local, pool) in enumerate(pairs):

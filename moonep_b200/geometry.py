@@ -52,6 +52,7 @@ class Geometry:
     off_ready: int = 0        # uint32 [ntiles] arrival counters of the ready-flag tiles
     off_rowsrc: int = 0       # int32 [NvS] slot a row's payload comes from (flagged dispatch)
     ntiles: int = 0           # ceil(NvS / FLAG_ROWS)
+    off_slotflag: int = 0     # uint32 [epn] prefetch epoch at which each prefetch slot of this rank became complete
     off_srcinfo: int = 0      # push-combine only (0 = not allocated): provenance table [NvS] int32,
     off_push: int = 0         # receive area [S*K, H] bf16,
     off_pushw: int = 0        # per-slot scalar receive area [S*K] fp32
@@ -101,6 +102,7 @@ class Geometry:
         ntiles = (NvS + FLAG_ROWS - 1) // FLAG_ROWS
         o_ready = take(4 * ntiles)
         o_rowsrc = take(4 * NvS)
+        o_slotflag = take(4 * epn)
         o_srcinfo = o_push = o_pushw = 0
         if push_combine:
             # the expert GEMM's epilogue sends every output row back to its source rank
@@ -110,4 +112,4 @@ class Geometry:
         chunk = align_up(off, 1024)
         return Geometry(S, H, K, E, R, token_padding, num_sms, epn, N, NvS, vb, nvb,
                         o_hidden, o_weights, o_tpe, o_bar, o_dupcnt, o_dupgroups,
-                        o_duploffs, o_ready, o_rowsrc, ntiles, o_srcinfo, o_push, o_pushw, gcap, lcap, chunk)
+                        o_duploffs, o_ready, o_rowsrc, ntiles, o_slotflag, o_srcinfo, o_push, o_pushw, gcap, lcap, chunk)

@@ -138,18 +138,19 @@ class ExpertParallelMoE:
                 stashed = self._side.record_event()
         gu = self._gu if need_backward else None
         Wg, Wu = self._W("gate"), self._W("up")
-        # local experts: one GEMM, two launches on one ticket counter -- now, on the SMs the dispatch
-        # kernel leaves free, and behind dispatch (+ prefetch) on the comm stream for the rest
+        # one GEMM over all groups, two launches on one ticket counter -- now, on the SMs the dispatch
+        # kernel leaves free, and behind dispatch (+ prefetch) on the comm stream for the rest. Token
+        # tiles are taken as their ready flags come up; the groups of prefetched experts (the last ones
+        # in tile order) additionally wait for their slot's flag, not for the whole prefetch.
+        slots = buf.slot_ready() if g.R > 1 else None
         tk = gg.Ticket(self._act.device, self._total_sms)
         free = min(ready.free_sms, self._total_sms - self._comm_sms)
-        gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, groups=(0, epn), num_ctas=free, ticket=tk, ready=ready)
+        gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, num_ctas=free, ticket=tk, ready=ready, slots=slots)
         with torch.cuda.stream(comm):
-            gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, groups=(0, epn), num_ctas=self._total_sms - free, ticket=tk,
-                       ready=ready)
+            gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, num_ctas=self._total_sms - free, ticket=tk,
+                       ready=ready, slots=slots)
             joined = comm.record_event()
-        main.wait_event(joined)             # also: dispatch finished, prefetched weights have landed
-        if g.R > 1:
-            gg.gate_up(x, Wg, Wu, cu, self._act, gu, row_scale=w, groups=(epn, 2 * epn))
+        main.wait_event(joined)
         return self._forward_tail(plan, cu, stashed, need_backward)
 
     def _forward_tail(self, plan, cu, stashed, need_backward):
@@ -231,7 +232,9 @@ class ExpertParallelMoE:
         gg.wgrad(ctx.x, self._dgu[:, :Hp], ctx.cu, self._dW("gate"), accumulate=acc, zero_empty_below=epn)
         ev_red = None
         if multi:
-            ev_red = buf.reduce_grad_subset(ctx.plan, [pair("down"), pair("gate")], async_finish=ov)
+            # the weight-gradient GEMMs overwrite the slots they use, so consumed slots need no zeroing
+            # unless gradients are accumulated over several backward passes
+            ev_red = buf.reduce_grad_subset(ctx.plan, [pair("down"), pair("gate")], async_finish=ov, clear_slots=acc)
             self._optimizer("down", ev_red if ov else main)
         if ov and multi:
             ev = self._beside_comm(lambda n, tk: gg.dgrad_gate_up(self._dgu, Wg, Wu, ctx.cu, shard, num_ctas=n, ticket=tk))
@@ -253,7 +256,7 @@ class ExpertParallelMoE:
             # the last reduction has nothing of the backward pass left to hide behind: with
             # ``defer_last_reduction`` it is left running on the comm stream and ``wait_grads()`` (or
             # ``wait_grads("up")``) joins it, so an optimizer can update ``down`` and ``gate`` meanwhile
-            ev_up = buf.reduce_grad_subset(ctx.plan, [pair("up")],
+            ev_up = buf.reduce_grad_subset(ctx.plan, [pair("up")], clear_slots=acc,
                                            async_finish=ov and self.defer_last_reduction and self.on_grad_ready is None)
             if ev_up is not None:
                 self.grads_pending = ("up", ev_up)

@@ -34,7 +34,8 @@ class GemmArgs(C.Structure):
                 ("push_info", C.c_void_p), ("push_base", C.c_void_p), ("push_wbase", C.c_void_p),
                 ("push_wsrc", C.c_void_p), ("push_stride", C.c_uint64),
                 ("tile_done", C.c_void_p), ("tile_epoch", C.c_void_p), ("status_host", C.c_void_p),
-                ("push_rows", C.c_int32), ("push_ranks", C.c_int32), ("sched_ctas", C.c_int32)]
+                ("group_flags", C.c_void_p), ("group_epoch", C.c_void_p),
+                ("push_rows", C.c_int32), ("push_ranks", C.c_int32), ("group_first", C.c_int32), ("sched_ctas", C.c_int32)]
 
 
 class PushTarget:
@@ -133,7 +134,7 @@ def check_status(device="cuda") -> None:
 
 def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=None, row_scale=None, ldo=0,
             accumulate=False, zero_empty_below=0, a_cols=None, b_rows=None, b_cols=None, b_ld=None, groups=None, num_ctas=None,
-            dynamic=False, ticket=None, push=None, push_w=None, ready=None):
+            dynamic=False, ticket=None, push=None, push_w=None, ready=None, slots=None):
     lib = _native.load()
     assert a.dtype == torch.bfloat16 and b0.dtype == torch.bfloat16
     assert cu.dtype == torch.int32 and cu.is_contiguous()
@@ -158,6 +159,8 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
     if ready is not None:
         assert mode in (GATE_UP, DGRAD), "ready flags gate the GEMMs that read the dispatched rows"
         args.tile_done, args.tile_epoch = ready.done_ptr, ready.epoch_ptr
+    if slots is not None:
+        args.group_flags, args.group_epoch, args.group_first = slots.flags_ptr, slots.epoch_ptr, slots.first
     if push is not None:
         assert mode in (DOWN, DGRAD, DGRAD_GU) and push.info.dtype == torch.int32 and push.info.numel() >= a.shape[0]
         args.push_info, args.push_base, args.push_stride = push.info.data_ptr(), push.base, push.stride
@@ -169,7 +172,7 @@ def _launch(mode, a, b0, b1, cu, *, N, K=0, M_w=0, b_group_rows=0, out, out2=Non
     a_ld = a.stride(0)
     a_cols = a.shape[1] if a_cols is None else a_cols
     fn = lib.mep_grouped_gemm
-    if mode != WGRAD and push is None and ready is None and os.environ.get("MOONEP_GEMM_2CTA", "0") == "1":
+    if mode != WGRAD and push is None and ready is None and slots is None and os.environ.get("MOONEP_GEMM_2CTA", "0") == "1":
         fn = lib.mep_grouped_gemm_2cta      # CTA-pair kernels (tcgen05 cta_group::2), 256-token tiles
     rc = fn(mode, C.c_void_p(a.data_ptr()), C.c_int64(a_rows), C.c_int64(a_cols), C.c_int64(a_ld),
                               C.c_void_p(b0.data_ptr()), C.c_void_p(_native.ptr(b1)), C.c_int64(b_rows),
@@ -184,18 +187,20 @@ def _w2d(w):
 
 
 def gate_up(x, wg, wu, cu, act_out, gu_out=None, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None,
-            ready=None):
+            ready=None, slots=None):
     """``act_out[r] = row_scale[r] * silu(x[r] Wg[g]) * (x[r] Wu[g])``; optionally stores the
     pre-activations ``gu_out = [x Wg | x Wu]`` (``[NvS, 2*out]``) for the backward pass.
     ``ready`` (a ``TileReady`` from ``Buffer.dispatch_ready``): ``x`` is still being filled by that
     dispatch; every 128-row tile is loaded only once its flag says it is complete.  Launch with
-    ``num_ctas <= ready.free_sms`` while the dispatch kernel may still be running."""
+    ``num_ctas <= ready.free_sms`` while the dispatch kernel may still be running.
+    ``slots`` (a ``SlotReady`` from ``Buffer.slot_ready``): the weights of the groups ``>= slots.first`` are
+    prefetched experts that may still be on their way; each such group is loaded once its slot is complete."""
     G, K, N = wg.shape
     assert wu.shape == wg.shape and x.shape[1] == K and N % 128 == 0 and K % 64 == 0
     rows, cols = _w2d(wg)
     _launch(GATE_UP, x, wg, wu, cu, N=N, K=K, b_group_rows=K, out=act_out, out2=gu_out, row_scale=row_scale,
             ldo=act_out.stride(0), b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket,
-            ready=ready)
+            ready=ready, slots=slots)
 
 
 def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None, dynamic=False, ticket=None, push=None):

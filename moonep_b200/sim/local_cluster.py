@@ -45,6 +45,9 @@ class LocalCluster(OpsMixin):
     def tile_ready(self, rank: int):
         return self._tile_ready(rank)
 
+    def slot_ready(self, rank: int):
+        return self._slot_ready(rank)
+
     def combine(self, plans, hidden_nvsh, weights_nvs=None, *, inter_rank_sync=True, zero_copy=False,
                 router_weights_zero_copy=False):
         return self._combine_lists(plans, hidden_nvsh, weights_nvs, inter_rank_sync=inter_rank_sync,
@@ -59,8 +62,8 @@ class LocalCluster(OpsMixin):
     def prefetch(self, plans, pairs_list):
         self._prefetch_lists(plans, pairs_list)
 
-    def reduce_grad(self, plans, pairs_list):
-        self._reduce_lists(plans, pairs_list)
+    def reduce_grad(self, plans, pairs_list, inter_rank_sync=True, clear_slots=True):
+        self._reduce_lists(plans, pairs_list, inter_rank_sync, clear_slots)
 
     def check(self):
         for s in self._states:

@@ -203,3 +203,69 @@ def test_consumer_wait_runs_out_when_no_dispatch_completes_the_tile(cuda_device)
             os.environ["MOONEP_WAIT_BUDGET_MS"] = old
     y = torch.ones(4, device="cuda") * 2
     assert float(y.sum()) == 8.0
+
+
+@pytest.mark.parametrize("R,epn", [(4, 4), (2, 5)])
+def test_prefetch_raises_one_flag_per_landed_slot(R, epn, cuda_device):
+    """Every slot that received an expert carries the launch's prefetch epoch afterwards, every other
+    slot's flag is untouched; the next launch stamps the next epoch (the per-slot chunk counters reset
+    themselves)."""
+    from gpu_helpers import run_case
+    S, K, H = 200, 6, 64
+    cl, cp, plans, *_ = run_case(S, K, epn, H, R, 3, 16, "biased", sigma=2.0, with_weights=False)
+    assert (cp.experts_to_copy >= 0).any(), "case must produce redundant experts"
+    dev, g = cl.device, cl.geo
+    rows, cols = 72, 40                 # 5760 B per expert and tensor: several 64 KB chunks only with all three
+    gen = torch.Generator().manual_seed(5)
+    names = ("gate", "up", "down")
+    local = {n: [torch.randn(epn, rows * 9, cols, generator=gen).to(torch.bfloat16) for _ in range(R)] for n in names}
+    pools = {n: cl.make_pool((epn, rows * 9, cols), torch.bfloat16, 0)[0] for n in names}
+    pairs = [[(local[n][r].to(dev), pools[n]) for n in names] for r in range(R)]
+    for epoch in (1, 2):
+        cl.prefetch(plans, pairs)
+        torch.cuda.synchronize()
+        cl.check()
+        for r in range(R):
+            flags = cl.heap.view(r, g.off_slotflag, (g.epn,), torch.int32).cpu().numpy()
+            want = np.where(cp.experts_to_copy[r] >= 0, epoch, 0)
+            assert np.array_equal(flags, want), f"rank {r}: slot flags {flags} != {want}"
+            assert int(cl._states[r].scratch["slot_done"].abs().sum()) == 0, "chunk counters did not reset"
+            assert int(cl._states[r].scratch["pf_epoch"][0]) == epoch
+
+
+def test_gemm_waits_for_prefetch_slots(cuda_device):
+    """gate/up over ``[local | slots]`` with slot flags: groups of prefetched experts are computed once
+    their flag is up (result equals the unflagged GEMM); when a slot never lands the wait gives up."""
+    import os
+    from moonep_b200.ops import grouped_gemm as gg
+    S, K, epn, H, Hp, pad = 128, 2, 2, 256, 256, 128
+    cl = LocalCluster(S, H, K, epn, 1, num_sms=2, token_padding=pad, budget_ms=30)
+    st, g = cl._states[0], cl.geo
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    x = (torch.randn(512, H, device="cuda", generator=gen) * 0.5).to(torch.bfloat16)
+    cu = torch.tensor([128, 256, 384, 512], dtype=torch.int32, device="cuda")      # groups 2, 3 = slots 0, 1
+    W = (torch.randn(4, H, Hp, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    ref = torch.zeros(512, Hp, dtype=torch.bfloat16, device="cuda")
+    gg.gate_up(x, W, W, cu, ref, None)
+    slots = cl.slot_ready(0)
+    flags = cl.heap.view(0, g.off_slotflag, (g.epn,), torch.int32)
+    st.scratch["pf_epoch"][0] = 3
+    flags.fill_(3)                      # both slots landed in prefetch epoch 3
+    out = torch.zeros_like(ref)
+    gg.gate_up(x, W, W, cu, out, None, slots=slots)
+    torch.cuda.synchronize()
+    gg.check_status()
+    assert torch.equal(out, ref)
+    flags[1] = 2                        # slot 1 still holds the previous launch's expert
+    old = os.environ.get("MOONEP_WAIT_BUDGET_MS")
+    os.environ["MOONEP_WAIT_BUDGET_MS"] = "30"
+    try:
+        gg.gate_up(x, W, W, cu, out, None, slots=slots)
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match="grouped GEMM aborted: code 4"):
+            gg.check_status()
+    finally:
+        if old is None:
+            os.environ.pop("MOONEP_WAIT_BUDGET_MS")
+        else:
+            os.environ["MOONEP_WAIT_BUDGET_MS"] = old
