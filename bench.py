@@ -236,7 +236,13 @@ def run_ours(args):
         # everyone back to launching from Python (not an error).
         try:
             c0 = lib.mep_launch_count()
-            gs = GraphedSteps(lambda x: step(x), dev_batches)
+            def health():      # a bounded wait that ran out in an earlier replay stops the run here
+                if not blk.buf.healthy():
+                    blk.buf.check()
+                if gg.failed():
+                    gg.check_status()
+
+            gs = GraphedSteps(lambda x: step(x), dev_batches, health=health)
             gs.launches_per_step = (lib.mep_launch_count() - c0) // len(gs)
             ok, note = 1, "whole step replayed from a captured CUDA graph"
         except Exception as e:      # noqa: BLE001

@@ -32,6 +32,9 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--maxvio", type=float, nargs="*", default=None)
+    ap.add_argument("--private-slots", action="store_true",
+                    help="every block gets its own Buffer and its own prefetch / reduce slots (default: the blocks "
+                         "share one Buffer and one set of slots when there is more than one rank)")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
@@ -40,7 +43,15 @@ def main():
     cfg = CONFIGS[a.model]
     layers = a.layers or (4 if a.model == "kimi_k2" else 1)
     sweep = a.maxvio or ([0.0, 1.0, 2.0, 3.0] if a.model == "kimi_k2" else [0.0, 1.0, 2.0])
-    blocks = [MoEBlock(cfg, world, rank, num_sms=32, seed=l) for l in range(layers)]
+    shared_buf = shared_slots = None
+    if world > 1 and layers > 1 and not a.private_slots:
+        from moonep_b200 import Buffer
+        from moonep_b200.pools import SharedSlots
+        push = os.environ.get("MOONEP_PUSH_COMBINE", "1") != "0"
+        shared_buf = Buffer(cfg.S, cfg.H, cfg.K, cfg.epn * world, world, num_sms=32, token_padding=cfg.token_padding,
+                            push_combine=push)
+        shared_slots = SharedSlots(cfg.epn, (cfg.H, cfg.Hp), (cfg.H, cfg.Hp), (cfg.Hp, cfg.H), with_grads=True)
+    blocks = [MoEBlock(cfg, world, rank, num_sms=32, seed=l, buffer=shared_buf, shared_slots=shared_slots) for l in range(layers)]
     x0 = torch.randn(cfg.S, cfg.H, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank)).to(torch.bfloat16)
 
     def step():
@@ -78,10 +89,18 @@ def main():
                               "tokens_per_rank": cfg.S, "maxvio_target": mv, "maxvio": round(real, 3),
                               "iteration_ms": round(ms, 3), "tokens_per_s": round(cfg.S * world / ms * 1e3),
                               "peak_torch_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2),
-                              "symmetric_mem_gib": round(sum(b.pools.bytes_per_rank + b.buf._heap.chunk_bytes for b in blocks) / 2**30, 2),
+                              "slots": "shared by all blocks" if shared_slots is not None else "one set per block",
+                              "expert_and_comm_mem_gib": round((sum(b.pools.bytes_per_rank for b in blocks)
+                                                                + (shared_slots.bytes_per_rank if shared_slots is not None else 0)
+                                                                + sum(bf._heap.chunk_bytes for bf in {id(b.buf): b.buf for b in blocks}.values()))
+                                                               / 2**30, 2),
                               "loss": float(loss)}), flush=True)
     for b in blocks:
         b.destroy()
+    if shared_slots is not None:
+        shared_slots.destroy()
+    if shared_buf is not None:
+        shared_buf.destroy()
     if world > 1:
         dist.destroy_process_group()
 

@@ -44,6 +44,12 @@ struct Mapping {
   std::vector<bool> mapped;
 };
 
+// [fresh local memory | an existing chunk] in one virtual range, see mep_alias_map
+struct AliasMap {
+  int dev; CUdeviceptr va; size_t local_bytes, tail_bytes;
+  CUmemGenericAllocationHandle local; bool local_live, local_mapped, tail_mapped;
+};
+
 struct Multicast {
   int dev; size_t bytes;
   CUmemGenericAllocationHandle mc; bool mc_live;
@@ -243,6 +249,61 @@ int mep_map_remote_one(int dev, int kind, size_t bytes, const unsigned char* sha
     return set_error("map_remote_one: %s failed: %s", what, s ? s : "?");
   }
   *mapping_out = m; *base_out = (unsigned long long)m->base;
+  return 0;
+}
+
+// One virtual range [local_bytes | chunk]: the first part is backed by NEW physical memory, the
+// second part maps the physical memory of `tail_chunk` a second time. This is how several layers
+// share one set of prefetch / reduce slots: each layer's compute view is [its own experts | the
+// shared slots], contiguous for the grouped GEMM, while the slots exist once (and peers reach them
+// through the slot heap's all-rank mapping). `local_bytes` must be a multiple of the granularity.
+int mep_alias_map(int dev, size_t local_bytes, void* tail_chunk, void** alias_out, unsigned long long* va_out) {
+  const DriverApi* d = driver(); if (!d) return -1;
+  LocalChunk* lc = static_cast<LocalChunk*>(tail_chunk);
+  MEP_REQUIRE(lc && lc->handle_live, "alias_map: the chunk to alias has been released");
+  CUmemAllocationProp p = alloc_prop(dev, lc->kind);
+  size_t gran = 0;
+  MEP_CU_CHECK(d->MemGetAllocationGranularity(&gran, &p, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
+  MEP_REQUIRE(local_bytes > 0 && local_bytes % gran == 0,
+              "alias_map: %zu local bytes are not a multiple of the mapping granularity %zu", local_bytes, gran);
+  AliasMap* a = new AliasMap{dev, 0, local_bytes, lc->bytes, 0, false, false, false};
+  const char* what = "reserve";
+  CUresult r = d->MemAddressReserve(&a->va, local_bytes + lc->bytes, gran, 0, 0);
+  if (r == CUDA_SUCCESS) { r = d->MemCreate(&a->local, local_bytes, &p, 0); what = "create"; a->local_live = r == CUDA_SUCCESS; }
+  if (r == CUDA_SUCCESS) { r = d->MemMap(a->va, local_bytes, 0, a->local, 0); what = "map(local)"; a->local_mapped = r == CUDA_SUCCESS; }
+  if (r == CUDA_SUCCESS) { r = d->MemMap(a->va + local_bytes, lc->bytes, 0, lc->handle, 0); what = "map(alias)"; a->tail_mapped = r == CUDA_SUCCESS; }
+  if (r == CUDA_SUCCESS) {
+    CUmemAccessDesc acc = {};
+    acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE; acc.location.id = dev; acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    r = d->MemSetAccess(a->va, local_bytes + lc->bytes, &acc, 1); what = "set_access";
+  }
+  if (r != CUDA_SUCCESS) {
+    const char* es = nullptr; d->GetErrorString(r, &es);
+    size_t fr = 0, tot = 0; cudaMemGetInfo(&fr, &tot);
+    const size_t lb = a->local_bytes;
+    if (a->tail_mapped) d->MemUnmap(a->va + a->local_bytes, a->tail_bytes);
+    if (a->local_mapped) d->MemUnmap(a->va, a->local_bytes);
+    if (a->local_live) d->MemRelease(a->local);
+    if (a->va) d->MemAddressFree(a->va, a->local_bytes + a->tail_bytes);
+    delete a;
+    return set_error("alias_map: %s failed: %s (%zu local bytes, %zu MiB free of %zu MiB)", what, es ? es : "?", lb, fr >> 20, tot >> 20);
+  }
+  *alias_out = a; *va_out = (unsigned long long)a->va;
+  return 0;
+}
+
+// Undo mep_alias_map (the aliased chunk itself is untouched). Caller must have synchronised the device.
+int mep_alias_unmap(void* alias) {
+  AliasMap* a = static_cast<AliasMap*>(alias);
+  if (!a) return 0;
+  const DriverApi* d = driver();
+  if (d) {
+    if (a->tail_mapped) d->MemUnmap(a->va + a->local_bytes, a->tail_bytes);
+    if (a->local_mapped) d->MemUnmap(a->va, a->local_bytes);
+    if (a->local_live) d->MemRelease(a->local);
+    d->MemAddressFree(a->va, a->local_bytes + a->tail_bytes);
+  }
+  delete a;
   return 0;
 }
 

@@ -133,6 +133,8 @@ def load(build_if_missing: bool = True):
     lib.mep_map_all.argtypes = [i32, i32, i32, vp, C.POINTER(C.c_ubyte), C.POINTER(vp), C.POINTER(C.c_ulonglong)]
     lib.mep_unmap_all.argtypes = [vp]
     lib.mep_map_remote_one.argtypes = [i32, i32, sz, C.POINTER(C.c_ubyte), C.POINTER(vp), C.POINTER(C.c_ulonglong)]
+    lib.mep_alias_map.argtypes = [i32, sz, vp, C.POINTER(vp), C.POINTER(C.c_ulonglong)]
+    lib.mep_alias_unmap.argtypes = [vp]
     lib.mep_mc_create.argtypes = [i32, i32, sz, i32, C.POINTER(vp), C.POINTER(C.c_ubyte)]
     lib.mep_mc_import.argtypes = [i32, sz, i32, C.POINTER(C.c_ubyte), C.POINTER(vp)]
     lib.mep_mc_add_device.argtypes = [vp]

@@ -49,16 +49,22 @@ class MoEBlock:
     """One MoE FFN block on this rank of the EP group (weights random-init N(0, 0.02))."""
 
     def __init__(self, cfg: MoEConfig, world: int = 1, rank: int = 0, group=None, num_sms: int = 32, seed: int = 0,
-                 router_skew: float = 0.0):
+                 router_skew: float = 0.0, buffer: Buffer | None = None, shared_slots=None):
+        """``buffer`` / ``shared_slots``: a ``Buffer`` and a ``pools.SharedSlots`` that several blocks of
+        one model use in turn (the communication buffers and the prefetch / reduce slots are scratch
+        between a layer's dispatch and its combine, so a model needs them once); without them the
+        block creates its own."""
         self.cfg, self.world, self.rank = cfg, world, rank
         dev = torch.device("cuda", torch.cuda.current_device())
         self.E = cfg.epn * world
         # the down GEMM's epilogue sends its rows to their source ranks itself; costs a [S*K, H]
         # receive area per rank (MOONEP_PUSH_COMBINE=0: plain stores, then the combine pulls)
         push = os.environ.get("MOONEP_PUSH_COMBINE", "1") != "0"
-        self.buf = Buffer(cfg.S, cfg.H, cfg.K, self.E, world, num_sms=num_sms, token_padding=cfg.token_padding, group=group,
-                          push_combine=push)
-        self.pools = ExpertPools(cfg.epn, (cfg.H, cfg.Hp), (cfg.H, cfg.Hp), (cfg.Hp, cfg.H), group=group, with_grads=True)
+        self._own_buffer = buffer is None
+        self.buf = buffer if buffer is not None else Buffer(cfg.S, cfg.H, cfg.K, self.E, world, num_sms=num_sms,
+                                                            token_padding=cfg.token_padding, group=group, push_combine=push)
+        self.pools = ExpertPools(cfg.epn, (cfg.H, cfg.Hp), (cfg.H, cfg.Hp), (cfg.Hp, cfg.H), group=group, with_grads=True,
+                                 shared=shared_slots if world > 1 else None)
         g = torch.Generator(device=dev).manual_seed(seed * 7919 + rank)
         for n in ("gate", "up", "down"):
             w = self.pools.local_weight(n)
@@ -132,7 +138,8 @@ class MoEBlock:
     def destroy(self):
         self.moe.wait_grads()        # nothing of this layer may still be queued on the comm stream
         self.pools.destroy()
-        self.buf.destroy()
+        if self._own_buffer:
+            self.buf.destroy()
 
 
 def smoke_step() -> float:

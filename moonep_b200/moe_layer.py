@@ -96,6 +96,8 @@ class ExpertParallelMoE:
     def forward(self, hidden_sh, route_weights_sk, topk_sk, tokens_per_expert, need_backward: bool = True):
         buf, g, epn = self.buf, self.geo, self.geo.epn
         self._join_deferred()
+        if gg.failed(self._act.device):     # a GEMM of an earlier step gave up a wait (host-visible flag, no sync)
+            gg.check_status(self._act.device)
         if self.ready_flags:
             return self._forward_flagged(hidden_sh, route_weights_sk, topk_sk, tokens_per_expert, need_backward)
         h_view, w_view, cu, plan = buf.dispatch(hidden_sh, route_weights_sk, topk_sk, tokens_per_expert,
@@ -211,19 +213,31 @@ class ExpertParallelMoE:
         pair = lambda n: (pools.local_grad(n), pools.reduce_view(n))      # noqa: E731
         Wg, Wu, Wd = self._W("gate"), self._W("up"), self._W("down")
         shard = buf.hidden_nvsh_buffer_view
+        # slots shared with other layers hold someone else's experts by now: fetch this layer's again
+        # (on the comm stream, behind the dispatch); the dgrad GEMMs wait per slot
+        refetch = multi and getattr(pools, "shared", None) is not None
+        slots, ev_pf = None, None
         if self.ready_flags and ctx.plan.send_list is not None:
             # dgrad(down) starts on the tiles of the re-dispatched output grad as they complete
             dy, _, _, _, ready, _ = buf.dispatch_ready(grad_out_sh, plan=ctx.plan)
+            if refetch:
+                ev_pf = buf.prefetch_weight(plan=ctx.plan, async_finish=True, **pools.prefetch_kwargs())
+                slots = buf.slot_ready()
             tk = gg.Ticket(self._act.device, self._total_sms)
             free = min(ready.free_sms, self._total_sms - self._comm_sms)
-            gg.dgrad(dy, Wd, ctx.cu, self._dA, num_ctas=free, ticket=tk, ready=ready)
+            gg.dgrad(dy, Wd, ctx.cu, self._dA, num_ctas=free, ticket=tk, ready=ready, slots=slots)
             with torch.cuda.stream(buf.comm_stream):
-                gg.dgrad(dy, Wd, ctx.cu, self._dA, num_ctas=self._total_sms - free, ticket=tk, ready=ready)
+                gg.dgrad(dy, Wd, ctx.cu, self._dA, num_ctas=self._total_sms - free, ticket=tk, ready=ready, slots=slots)
                 joined = buf.comm_stream.record_event()
             main.wait_event(joined)
         else:
             dy, _, _, _ = buf.dispatch(grad_out_sh, plan=ctx.plan, zero_copy=True)
-            gg.dgrad(dy, Wd, ctx.cu, self._dA)
+            if refetch:
+                ev_pf = buf.prefetch_weight(plan=ctx.plan, async_finish=True, **pools.prefetch_kwargs())
+                slots = buf.slot_ready()
+            gg.dgrad(dy, Wd, ctx.cu, self._dA, slots=slots)
+        if ev_pf is not None:
+            main.wait_event(ev_pf)      # dgrad(gate/up) further down reads the other two projections' slots
         dw_view = buf.router_weight_buffer_view
         gg.swiglu_bwd(self._dA, ctx.gu, ctx.w_nvs, self._dgu, dw_view, ctx.cu)
         gg.wgrad(ctx.act, dy, ctx.cu, self._dW("down"), accumulate=acc, zero_empty_below=epn)

@@ -213,13 +213,14 @@ def down(act, wd, cu, out, row_scale=None, groups=None, num_ctas=None, dynamic=F
             b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket, push=push)
 
 
-def dgrad(dy, w, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None, ready=None):
-    """``out[r] = dy[r] W[g]^T`` with ``W [G, in, out]`` -> ``out [NvS, in]``.  ``ready``: as in ``gate_up``."""
+def dgrad(dy, w, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None, ready=None, slots=None):
+    """``out[r] = dy[r] W[g]^T`` with ``W [G, in, out]`` -> ``out [NvS, in]``.  ``ready`` / ``slots``: as in ``gate_up``."""
     G, N, K = w.shape
     assert dy.shape[1] == K and N % 256 == 0 and K % 64 == 0
     rows, cols = _w2d(w)
     _launch(DGRAD, dy, w, None, cu, N=N, K=K, b_group_rows=N, out=out, ldo=out.stride(0),
-            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket, ready=ready)
+            b_rows=rows, b_cols=cols, b_ld=cols, groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket, ready=ready,
+            slots=slots)
 
 
 def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None, dynamic=False, ticket=None, push=None, push_w=None):

@@ -25,7 +25,12 @@ class GraphedSteps:
     Run a few eager warm-up steps before constructing this object.
     """
 
-    def __init__(self, step_fn: Callable[[torch.Tensor], torch.Tensor], inputs: Sequence[torch.Tensor]):
+    def __init__(self, step_fn: Callable[[torch.Tensor], torch.Tensor], inputs: Sequence[torch.Tensor],
+                 health: Callable[[], None] | None = None):
+        """``health``: called before every replay; it should raise if an earlier replay recorded a
+        device-side failure (e.g. ``lambda: (buf.healthy() or buf.check())``).  Such checks read a
+        flag in host memory, so they cost nothing and do not synchronise."""
+        self.health = health
         self.inputs = list(inputs)
         self.graphs, self.losses, self.host_losses = [], [], []
         pool = None
@@ -44,4 +49,6 @@ class GraphedSteps:
         return len(self.graphs)
 
     def replay(self, i: int) -> None:
+        if self.health is not None:
+            self.health()
         self.graphs[i % len(self.graphs)].replay()

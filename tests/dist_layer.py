@@ -71,6 +71,68 @@ def dense_reference(xs, ws, topks, gys, Wg, Wu, Wd, rank, epn):
     return outs[rank].detach(), X[rank].grad, Wt[rank].grad, Wg.grad[sl], Wu.grad[sl], Wd.grad[sl]
 
 
+def shared_slots_scenario(rank, R, dev):
+    """Two layers with different experts share ONE Buffer and ONE set of prefetch / reduce slots
+    (``pools.SharedSlots``): forward A, forward B, backward B, backward A.  By the time a layer runs its
+    backward pass the slots hold the other layer's experts, so it must fetch its own again; each layer is
+    compared with its own dense reference."""
+    from moonep_b200.pools import SharedSlots
+    S, H, Hp, K, epn, pad = 256, 512, 512, 4, 4, 128        # 4 x 512 x 512 bf16 = one mapping granule per projection
+    E = R * epn
+    gen = torch.Generator(device=dev).manual_seed(500 + rank)
+    buf = Buffer(S, H, K, E, R, num_sms=8, token_padding=pad, push_combine=True)
+    shared = SharedSlots(epn, (H, Hp), (H, Hp), (Hp, H), with_grads=True)
+    layers = []
+    for li in range(2):
+        topk = routing.lognormal_topk(S, K, E, R, 1.2, 11 + li, rank)[0].to(dev)
+        tpe = torch.bincount(topk.flatten().long(), minlength=E).to(torch.int32)
+        x0 = (torch.randn(S, H, device=dev, generator=gen) * 0.5).to(torch.bfloat16)
+        w0 = torch.rand(S, K, device=dev, generator=gen) + 0.1
+        w0 = (w0 / w0.sum(dim=1, keepdim=True)).contiguous()
+        gy = (torch.randn(S, H, device=dev, generator=gen) * 0.1).to(torch.bfloat16)
+        lw = {n: (torch.randn(epn, *shp, device=dev, generator=gen) * 0.04).to(torch.bfloat16)
+              for n, shp in (("gate", (H, Hp)), ("up", (H, Hp)), ("down", (Hp, H)))}
+        allw = {n: torch.cat(gather(t)) for n, t in lw.items()}
+        want = dense_reference(gather(x0), gather(w0), gather(topk), gather(gy), allw["gate"], allw["up"], allw["down"], rank, epn)
+        pools = ExpertPools(epn, (H, Hp), (H, Hp), (Hp, H), with_grads=True, shared=shared)
+        for n in ("gate", "up", "down"):
+            pools.local_weight(n).copy_(lw[n])
+            pools.compute_grad(n).zero_()
+        layers.append(dict(topk=topk, tpe=tpe, x0=x0, w0=w0, gy=gy, want=want, pools=pools,
+                           moe=ExpertParallelMoE(buf, pools)))
+    torch.cuda.synchronize()
+    dist.barrier()
+    for rep in range(2):
+        ys = []
+        for L in layers:
+            L["x"], L["w"] = L["x0"].clone().requires_grad_(True), L["w0"].clone().requires_grad_(True)
+            ys.append(moe_apply(L["moe"], L["x"], L["w"], L["topk"], L["tpe"]))
+        for L, y in reversed(list(zip(layers, ys))):
+            y.backward(L["gy"])
+            L["moe"].wait_grads()
+        torch.cuda.synchronize()
+        try:
+            buf.check()
+            gg.check_status()
+        except Exception as exc:      # noqa: BLE001
+            ERRORS.append(f"shared slots: {type(exc).__name__}: {exc}")
+        for li, (L, y) in enumerate(zip(layers, ys)):
+            p = L["pools"]
+            got = (y, L["x"].grad, L["w"].grad, p.local_grad("gate"), p.local_grad("up"), p.local_grad("down"))
+            for label, a, b in zip(("output", "grad hidden", "grad route weights", "grad gate", "grad up", "grad down"), got, L["want"]):
+                chk(torch.isfinite(a.float()).all() and rel(a, b) < 3e-2, f"shared slots, layer {li} rep {rep}: {label} off by {rel(a, b):.4f}")
+    ok = agree("shared slots")
+    if rank == 0:
+        print(f"[dist_layer] two layers on one Buffer and one set of slots: {'ok' if ok else 'FAILED'}", flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for L in layers:
+        L["pools"].destroy()
+    shared.destroy()
+    buf.destroy()
+    dist.barrier()
+
+
 def main():
     dist.init_process_group("nccl")
     rank, R = dist.get_rank(), dist.get_world_size()
@@ -136,6 +198,8 @@ def main():
         dist.barrier()
         if not ok and any("Timeout" in e or "aborted" in e for e in ERRORS):
             break           # a device-side wait ran out: later variants would only repeat it
+    if not ERRORS:
+        shared_slots_scenario(rank, R, dev)
     if ERRORS:
         for e in ERRORS[:24]:
             print(f"[dist_layer] rank {rank}: {e}", flush=True)

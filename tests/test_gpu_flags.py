@@ -269,3 +269,34 @@ def test_gemm_waits_for_prefetch_slots(cuda_device):
             os.environ.pop("MOONEP_WAIT_BUDGET_MS")
         else:
             os.environ["MOONEP_WAIT_BUDGET_MS"] = old
+
+
+def test_a_failed_wait_stops_the_next_public_call(cuda_device, monkeypatch):
+    """Once a kernel of a Buffer has given up a wait, the next public op raises at its entry (the
+    failure code is mirrored into host memory, so no synchronisation is needed to notice), instead of
+    launching more work on unsynchronised data; ``reset()`` makes the Buffer usable again."""
+    from moonep_b200 import Buffer
+    monkeypatch.setenv("MOONEP_WAIT_BUDGET_MS", "30")
+    S, H, K, E = 64, 256, 2, 4
+    buf = Buffer(S, H, K, E, 1, num_sms=2, token_padding=16)
+    x = torch.randn(S, H, device="cuda").to(torch.bfloat16)
+    topk = torch.randint(0, E, (S, K), dtype=torch.int32, device="cuda")
+    tpe = torch.bincount(topk.flatten().long(), minlength=E).to(torch.int32)
+    w = torch.rand(S, K, device="cuda")
+    buf.dispatch(x, w, topk, tpe)
+    assert buf.healthy()
+    st = buf._states[0]
+    engine.launch_flag_epoch_bump([st])
+    engine.launch_tile_wait_probe(st, 0)          # nothing completes this tile: the wait runs out
+    torch.cuda.synchronize()
+    assert not buf.healthy()
+    with pytest.raises(engine.MoonEPTimeout):
+        buf.dispatch(x, w, topk, tpe)
+    with pytest.raises(engine.MoonEPTimeout):
+        buf.combine(plan=None, hidden_nvsh=None)
+    buf.reset()
+    assert buf.healthy()
+    h, wn, cu, plan = buf.dispatch(x, w, topk, tpe)
+    torch.cuda.synchronize()
+    buf.check()
+    buf.destroy()
