@@ -37,6 +37,7 @@ from .plan import MoonEPCommPlan
 logger = logging.getLogger(__name__)
 _NVTX = os.environ.get("MOONEP_NVTX", "0") == "1"
 _VERIFY_PLANS = os.environ.get("MOONEP_VERIFY_PLANS", "0") == "1"     # debugging: see Buffer.verify_plan
+_SLOT_ORDER = os.environ.get("MOONEP_DISPATCH_SLOT_ORDER", "0")       # "0" | "1" | "auto" (4 or more ranks)
 
 PREFETCH_DTYPES = (torch.bfloat16, torch.int8, torch.uint8, torch.float16, torch.float32)
 
@@ -192,6 +193,9 @@ class OpsMixin:
                 assert w.dtype == torch.float32 and w.is_contiguous() and w.numel() == g.N, \
                     "route_weights_sk must be a contiguous [S, K] fp32 tensor"
         cus = [None] * n
+        # MOONEP_DISPATCH_SLOT_ORDER=1: the plain call also uses the slot-ordered kernel that expands
+        # duplicate rows itself while rows are still arriving (no separate expansion pass)
+        slot_order = _SLOT_ORDER == "1" or (_SLOT_ORDER == "auto" and g.R >= 4)
         if fresh:
             plans, cus = [], []
             for i in range(n):
@@ -200,22 +204,32 @@ class OpsMixin:
                     "topk_experts_sk must be a contiguous [S, K] int32 tensor"
                 assert c.dtype == torch.int32 and c.numel() == g.E and c.is_contiguous(), \
                     "tokens_per_expert must be a contiguous [E] int32 tensor"
-                p, cu = engine.allocate_plan(st[i])
+                p, cu = engine.allocate_plan(st[i], with_send_list=slot_order)
                 plans.append(p)
                 cus.append(cu)
             engine.launch_planning(st, [t.reshape(-1) for t in topk], tpe, plans, cus)
+            if slot_order:
+                engine.launch_send_order(st, plans, cus)
         else:
             for p in plans:
                 assert isinstance(p, MoonEPCommPlan), "plan must be a MoonEPCommPlan"
                 assert (p.N, p.R, p.E, p.NvS, p.K) == (g.N, g.R, g.E, g.NvS, g.K), "plan belongs to another Buffer geometry"
+            slot_order = slot_order and all(p.send_list is not None for p in plans)
         # planning's barrier already orders this op after every rank's previous one
-        engine.launch_dispatch(st, hidden, weights, plans, fresh=fresh,
-                               entry_barrier=(not fresh) and inter_rank_sync)
-        pdl = bool(getattr(self, "enable_pdl", False))      # the expansion is scheduled while dispatch drains
-        if fresh:
-            engine.launch_dup_expand_fresh(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4, pdl)
+        if slot_order:
+            engine.launch_flag_epoch_bump(st)
+            engine.launch_dispatch(st, hidden, weights, plans, fresh=fresh, entry_barrier=(not fresh) and inter_rank_sync,
+                                   flagged=True)
+            if fresh:
+                engine.launch_dup_finalize(st, plans)
         else:
-            engine.launch_dup_expand(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4, pdl)
+            engine.launch_dispatch(st, hidden, weights, plans, fresh=fresh,
+                                   entry_barrier=(not fresh) and inter_rank_sync)
+            pdl = bool(getattr(self, "enable_pdl", False))      # the expansion is scheduled while dispatch drains
+            if fresh:
+                engine.launch_dup_expand_fresh(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4, pdl)
+            else:
+                engine.launch_dup_expand(st, [s.hidden_local for s in st], plans, self._num_sms_dedup * 4, pdl)
         out_h, out_w = [], []
         for i in range(n):
             if zero_copy:
@@ -295,8 +309,8 @@ class OpsMixin:
             assert pool.device == local.device
             assert (local[0].numel() * local.element_size()) % 16 == 0, f"{what}: expert payload must be a multiple of 16 bytes"
 
-    def _prefetch_lists(self, plans, pairs_list):
-        engine.launch_prefetch(self._states, [p.experts_to_copy for p in plans], pairs_list)
+    def _prefetch_lists(self, plans, pairs_list, bump_epoch: bool = True):
+        engine.launch_prefetch(self._states, [p.experts_to_copy for p in plans], pairs_list, bump_epoch)
 
     def _reduce_lists(self, plans, pairs_list, inter_rank_sync: bool = True, clear_slots: bool = True):
         engine.launch_grad_reduce(self._states, [p.experts_to_copy for p in plans], pairs_list,
@@ -578,7 +592,10 @@ class Buffer(OpsMixin):
                                      if hasattr(torch, "float8_e8m0fnu") else PREFETCH_DTYPES, "prefetch_weight scales")
             pairs += list(zip(scales, spools))
         tensors = [plan.experts_to_copy] + [t for pr in pairs for t in pr]
-        _, ev = self._run(async_finish, tensors, lambda: self._prefetch_lists([plan], [pairs]), "moonep.prefetch_weight")
+        # the prefetch epoch advances on the CALLER's stream: a GEMM launched there afterwards with
+        # slot_ready() reads the new epoch even while the prefetch itself still waits on the comm stream
+        engine.launch_pf_epoch_bump(self._states)
+        _, ev = self._run(async_finish, tensors, lambda: self._prefetch_lists([plan], [pairs], False), "moonep.prefetch_weight")
         return ev
 
     def slot_ready(self) -> SlotReady:

@@ -313,8 +313,16 @@ def _rank_stride_bytes(pool: torch.Tensor) -> int:
     return int(pool.stride(0)) * pool.element_size()
 
 
-def launch_prefetch(states, etc_list, tensor_pairs_list):
-    """``tensor_pairs_list[i]`` = sequence of up to six ``(local[epn,...], pool[R,epn,...])``."""
+def launch_pf_epoch_bump(states):
+    """A prefetch is about to be issued: advance the prefetch epoch.  Must run in stream order before the
+    prefetch kernel AND before any GEMM that waits on its slot flags, i.e. on the stream both are forked from."""
+    lib = _native.load()
+    _native.check(lib.mep_launch_pf_epoch_bump(len(states), _pack(states), _native.cur_stream()), "pf_epoch_bump")
+
+
+def launch_prefetch(states, etc_list, tensor_pairs_list, bump_epoch: bool = True):
+    """``tensor_pairs_list[i]`` = sequence of up to six ``(local[epn,...], pool[R,epn,...])``.
+    ``bump_epoch=False``: the caller has already advanced the prefetch epoch (``launch_pf_epoch_bump``)."""
     lib = _native.load()
     n = len(states)
     args = (PrefetchArgs * n)()
@@ -332,7 +340,8 @@ def launch_prefetch(states, etc_list, tensor_pairs_list):
     g = states[0].geo
     # new prefetch epoch first (stream order): the kernel stamps completed slots with it and a GEMM that
     # consumes the slots while the prefetch runs compares against it
-    _native.check(lib.mep_launch_pf_epoch_bump(n, _pack(states), _native.cur_stream()), "pf_epoch_bump")
+    if bump_epoch:
+        launch_pf_epoch_bump(states)
     _native.check(lib.mep_launch_prefetch(n, _pack(states), args, g.num_sms, g.R, g.epn, _native.cur_stream()), "prefetch")
 
 
