@@ -39,6 +39,9 @@ def parse():
                     help="update each projection of the experts inside the backward pass, on a side stream, as soon "
                          "as its gradient is final (measured slower than updating after the backward pass)")
     ap.add_argument("--maxvio", type=float, default=MAXVIO_MAIN)
+    ap.add_argument("--verify-plans", action="store_true",
+                    help="instead of the benchmark: identical routing through this package's and the reference's "
+                         "Buffer on N >= 2 GPUs, plans and dispatched rows compared (benchmarks/verify_plans.py)")
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="launch every kernel of every step from Python instead of replaying a captured step")
     return ap.parse_args()
@@ -491,6 +494,9 @@ def _reserve_stdout() -> None:
 
 def main():
     args = parse()
+    if args.verify_plans:
+        from benchmarks.verify_plans import run
+        return run(args)
     if args.impl == "reference":
         from benchmarks.bench_reference import run_reference
         return run_reference(args)

@@ -20,7 +20,8 @@ import torch.distributed as dist
 
 from benchmarks._loss import mean_square
 
-CFG = {"deepseek_v3": dict(H=7168, Hp=2048, K=8, epn=32, S=4096)}
+CFG = {"deepseek_v3": dict(H=7168, Hp=2048, K=8, epn=32, S=4096),
+       "qwen3_30b_a3b": dict(H=2048, Hp=768, K=8, epn=16, S=8192)}
 SWEEP = (0.0, 0.5, 1.0, 2.0, 3.0)
 
 

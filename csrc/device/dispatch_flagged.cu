@@ -34,7 +34,7 @@
 
 namespace mep {
 
-constexpr int kExpWarps = 8;                                       // expander warps per CTA (one row slot each)
+constexpr int kExpWarps = 3;                                       // expander warps per CTA (one row slot each)
 constexpr int kFlagThreads = (kSendWarps + 1 + kExpWarps) * 32;    // senders + zero-fill warp + expanders
 constexpr int kSigLag = 2;          // a unit's arrivals are signalled once at most this many newer units are pending
 constexpr int kSigBatch = 4;        // units between two signalling rounds (one system-scope fence per round)
@@ -202,7 +202,7 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
         rsrc[prow] = -1;
       }
       __syncwarp();                                  // every lane's stores precede the releasing arrival
-      if (lane == 0) { fence_proxy_async(); red_release_sys_add(my_ready + prow / MEP_FLAG_ROWS, 1u); }
+      if (lane == 0) red_release_sys_add(my_ready + prow / MEP_FLAG_ROWS, 1u);
       ++done;
     }
     if (lane == 0 && done) count(c, MEP_CNT_PAD_ROWS, (unsigned long long)done);
@@ -373,15 +373,15 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       if (xt == 0) tile_complete(t, 60);
       bar_expanders();
       if (s_xfail) break;
-      if (xt < MEP_FLAG_ROWS) {
-        const int row = t * MEP_FLAG_ROWS + xt;
+      for (int r = xt; r < MEP_FLAG_ROWS; r += kExpWarps * 32) {
+        const int row = t * MEP_FLAG_ROWS + r;
         if (row < NvS) {
           const int src = __ldcg(rsrc + row);
           if (src >= 0 && src != row) {
             if (src >= NvS) report(c, MEP_ERR_BOUNDS, MEP_K_DISPATCH, 61, row, (uint32_t)src, (uint32_t)NvS);
             else {
               const int st = src / MEP_FLAG_ROWS;
-              if (st == t || tile_complete(st, 62)) s_xlist[atomicAdd(&s_xn, 1)] = (src << 7) | xt;
+              if (st == t || tile_complete(st, 62)) s_xlist[atomicAdd(&s_xn, 1)] = (src << 7) | r;
             }
           }
         }
