@@ -80,28 +80,44 @@ __device__ __forceinline__ void reduce_rows_auto(const char* myrow, unsigned pri
 struct DupArgs { __nv_bfloat16* buf; const int32_t* dup_groups; const int32_t* dup_loffs; const int32_t* dup_counts; };
 struct DupArgsPack { DupArgs a[MEP_MAX_VRANKS]; };
 
+// Checked mode (MOONEP_CHECKED=1): a pass of its own over the duplicate tables that reports entries the
+// expansion / reduction kernels skip silently. A separate kernel on purpose: with the report inside
+// dup_reduce_kernel, that kernel went from 56 to 92-98 registers and lost a third of its throughput.
+__global__ void __launch_bounds__(256) dup_check_kernel(MepCtxPack P, DupArgsPack A, int kernel_id) {
+  const MepRankCtx* cp = P.ctx[blockIdx.y];
+  const DupArgs& a = A.a[blockIdx.y];
+  const int NvS = cp->NvS, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
+  const int ng = a.dup_counts[0];
+  for (int g = gw; g < ng; g += nw) {
+    const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
+    const bool bad_head = (unsigned)p >= (unsigned)NvS || n <= 0 || n >= MEP_MAX_TOPK;
+    int q = 0;
+    if (!bad_head && lane < n) q = a.dup_loffs[st + lane];
+    if (bad_head) { if (lane == 0) report(*cp, MEP_ERR_BOUNDS, kernel_id, 1, g, (uint32_t)p, (uint32_t)n); }
+    else if ((unsigned)q >= (unsigned)NvS) report(*cp, MEP_ERR_BOUNDS, kernel_id, 2, g, (uint32_t)q, (uint32_t)NvS);
+  }
+}
+
 __global__ void __launch_bounds__(256) dup_reduce_kernel(MepCtxPack P, DupArgsPack A) {
-  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
+  const MepRankCtx* cp = P.ctx[blockIdx.y];   // two fields only: no need to copy the whole context
+  const int NvS = cp->NvS;
   const DupArgs& a = A.a[blockIdx.y];
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
   const int ng = a.dup_counts[0];
-  const size_t row_bytes = (size_t)c.H * 2;
+  const size_t row_bytes = (size_t)cp->H * 2;
   const int nvec = (int)(row_bytes >> 4);
   char* base = (char*)a.buf;
   for (int g = gw; g < ng; g += nw) {
     const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
-    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) {
-      if (c.checked && lane == 0) report(c, MEP_ERR_BOUNDS, MEP_K_DUP_REDUCE, 1, g, (uint32_t)p, (uint32_t)n);
-      continue;
-    }
+    if ((unsigned)p >= (unsigned)NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
     // lane 0 holds the primary row, lanes 1..n the duplicates in table order
     const char* myrow = nullptr;
     if (lane == 0) myrow = base + (size_t)p * row_bytes;
     else if (lane <= n) {
       const int q = a.dup_loffs[st + lane - 1];
-      if ((unsigned)q < (unsigned)c.NvS) myrow = base + (size_t)q * row_bytes;
-      else if (c.checked) report(c, MEP_ERR_BOUNDS, MEP_K_DUP_REDUCE, 2, g, (uint32_t)q, (uint32_t)c.NvS);
+      if ((unsigned)q < (unsigned)NvS) myrow = base + (size_t)q * row_bytes;
     }
     const unsigned rows = __ballot_sync(0xffffffffu, myrow != nullptr);
     reduce_rows_auto<false>(myrow, rows, __popc(rows), base + (size_t)p * row_bytes, nvec, lane);
@@ -292,6 +308,14 @@ __global__ void wait_probe_kernel(MepCtxPack P, const uint32_t* flag, uint32_t e
 }
 
 }  // namespace mep
+
+// Checked-mode validation of the duplicate tables (see dup_check_kernel); `kernel_id` names the caller in the report.
+extern "C" int mep_launch_dup_check(int nv, const MepRankCtx* const* ctxs, const mep::DupArgs* args,
+                                    int num_blocks, int kernel_id, cudaStream_t stream) {
+  MepCtxPack P = {}; mep::DupArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  return mep::launch_plain(mep::dup_check_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A, kernel_id);
+}
 
 extern "C" int mep_launch_dup_reduce(int nv, const MepRankCtx* const* ctxs, const mep::DupArgs* args,
                                      int num_blocks, cudaStream_t stream) {

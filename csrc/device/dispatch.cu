@@ -243,26 +243,24 @@ struct DupArgsPack { DupArgs a[MEP_MAX_VRANKS]; };
 
 __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPack A) {
   pdl_wait();                                // the plan tables and the rows come from the kernel before
-  const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
+  const MepRankCtx* cp = P.ctx[blockIdx.y];  // two fields only (see dup_reduce_kernel; checked mode: dup_check_kernel)
+  const int NvS = cp->NvS;
   const DupArgs& a = A.a[blockIdx.y];
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
   const int ng = a.dup_counts[0];
-  const size_t row_bytes = (size_t)c.H * 2;
+  const size_t row_bytes = (size_t)cp->H * 2;
   const int nvec = (int)(row_bytes >> 4);
   char* base = (char*)a.buf;
   for (int g = gw; g < ng; g += nw) {
     const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
-    if ((unsigned)p >= (unsigned)c.NvS || n <= 0 || n >= MEP_MAX_TOPK) {
-      if (c.checked && lane == 0) report(c, MEP_ERR_BOUNDS, MEP_K_EXPAND, 1, g, (uint32_t)p, (uint32_t)n);
-      continue;
-    }
+    if ((unsigned)p >= (unsigned)NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
     const char* src = base + (size_t)p * row_bytes;
     // duplicate offsets of this group live in lanes 0..n-1
     int myq = -1;
     if (lane < n) {
       myq = a.dup_loffs[st + lane];
-      if ((unsigned)myq >= (unsigned)c.NvS) { if (c.checked) report(c, MEP_ERR_BOUNDS, MEP_K_EXPAND, 2, g, (uint32_t)myq, (uint32_t)c.NvS); myq = -1; }
+      if ((unsigned)myq >= (unsigned)NvS) myq = -1;
     }
     for (int v0 = 0; v0 < nvec; v0 += 128) {          // 4 x 16-byte loads in flight per lane
       int4 x[4];

@@ -34,11 +34,12 @@
 
 namespace mep {
 
-constexpr int kExpWarps = 3;                                       // expander warps per CTA (one row slot each)
-constexpr int kFlagThreads = (kSendWarps + 1 + kExpWarps) * 32;    // senders + zero-fill warp + expanders
+constexpr int kFSend = 5;                                          // sender warps per CTA (`stages` row slots each)
+constexpr int kExpWarps = 2;                                       // expander warps per CTA (two row slots each)
+constexpr int kFlagThreads = (kFSend + 1 + kExpWarps) * 32;        // senders + zero-fill warp + expanders
 constexpr int kSigLag = 2;          // a unit's arrivals are signalled once at most this many newer units are pending
-constexpr int kSigBatch = 4;        // units between two signalling rounds (one system-scope fence per round)
-constexpr int kSigRing = 8;          // units whose slot lists are remembered until they are signalled (>= kSigLag + kSigBatch)
+constexpr int kSigBatch = 8;        // units between two signalling rounds (one system-scope fence per round)
+constexpr int kSigRing = 16;         // units whose slot lists are remembered until they are signalled (>= kSigLag + kSigBatch)
 
 __device__ __forceinline__ uint32_t* ready_of(const MepRankCtx& c, int d) { return (uint32_t*)peer_ptr(c, d, c.off_ready); }
 __device__ __forceinline__ int tile_rows(const MepRankCtx& c, int t) {
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(256) send_place_kernel(MepCtxPack P, SendOrder
 }
 
 // ------------------------------------------------------------------ dispatch
-// Shared memory: [kSendWarps x stages rows: sender rings][kExpWarps rows: one slot per expander warp]
+// Shared memory: [kFSend x stages rows: sender rings][kExpWarps x 2 rows: two slots per expander warp]
 // [padding-row tables]. Every data movement goes through the copy engine (bulk copies), so the
 // bytes in flight per SM are the rows staged in shared memory, not registers.
 __global__ void __launch_bounds__(kFlagThreads, 1)
@@ -139,10 +140,10 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const DispatchArgs& a = A.a[blockIdx.y];
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t s_bar[kSendWarps * kMaxStages];
-  __shared__ __align__(8) uint64_t s_xbar[kExpWarps];
-  __shared__ uint32_t s_sig[kSendWarps][kSigRing];               // (destination << 8 | slots stored) of a unit
-  __shared__ int s_sloff[kSendWarps][kSigRing][MEP_MAX_TOPK];     // the slots a unit stored to
+  __shared__ __align__(8) uint64_t s_bar[kFSend * kMaxStages];
+  __shared__ __align__(8) uint64_t s_xbar[kExpWarps * 2];
+  __shared__ uint32_t s_sig[kFSend][kSigRing];               // (destination << 8 | slots stored) of a unit
+  __shared__ int s_sloff[kFSend][kSigRing][MEP_MAX_TOPK];     // the slots a unit stored to
   __shared__ int s_znext, s_ztotal;
   __shared__ int s_xtile, s_xn, s_xfail;
   __shared__ int s_xlist[MEP_FLAG_ROWS];
@@ -155,12 +156,12 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
 
   if (tid == 0) { s_xfail = 0; s_xn = 0; }
   if (tid < MEP_MAX_RANKS) s_peer[tid] = 0;
-  if (tid < kSendWarps * kMaxStages) mbar_init(&s_bar[tid], 1);
-  if (tid < kExpWarps) mbar_init(&s_xbar[tid], 1);
+  if (tid < kFSend * kMaxStages) mbar_init(&s_bar[tid], 1);
+  if (tid < kExpWarps * 2) mbar_init(&s_xbar[tid], 1);
   fence_mbar_init();
   const int ngroups = 2 * c.epn;
-  unsigned char* xslots = smem + (size_t)kSendWarps * stages * row_bytes;
-  int* s_zpre = reinterpret_cast<int*>(xslots + (size_t)kExpWarps * row_bytes);
+  unsigned char* xslots = smem + (size_t)kFSend * stages * row_bytes;
+  int* s_zpre = reinterpret_cast<int*>(xslots + (size_t)kExpWarps * 2 * row_bytes);
   int* s_zstart = s_zpre + ngroups + 1;
   for (int g = tid; g < ngroups; g += blockDim.x) { s_zstart[g] = a.zero_fill[2 * g]; s_zpre[g + 1] = a.zero_fill[2 * g + 1]; }
   __syncthreads();
@@ -220,12 +221,12 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
     }
   }
 
-  if (warp < kSendWarps) {
+  if (warp < kFSend) {
     // ---------------------------------------------------------------- senders
     unsigned char* ring = smem + (size_t)warp * stages * row_bytes;
     uint64_t* bars = s_bar + warp * kMaxStages;
     const int nunits = a.send_meta[0];
-    const int gw = blockIdx.x * kSendWarps + warp, nw = nb * kSendWarps;
+    const int gw = blockIdx.x * kFSend + warp, nw = nb * kFSend;
     const int n = gw < nunits ? (nunits - gw + nw - 1) / nw : 0;       // this warp's units: gw, gw + nw, ...
     const int D = stages >= 3 ? 1 : 0, pre = stages - 1 - D;
     // the warp's list entries live in two register chunks of 32 (lane j of chunk A = unit cbase + j)
@@ -336,7 +337,7 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
     }
     zero_fill_work();
     if (lane == 0) trace_mark(c, MEP_K_DISPATCH, 3);
-  } else if (warp == kSendWarps) {
+  } else if (warp == kFSend) {
     // ---------------------------------------------------------------- zero-fill warp
     if (blockIdx.x == 0) {
       // slots behind the last group take no data: they arrive unwritten, so that every tile's
@@ -351,12 +352,12 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
     if (lane == 0) trace_mark(c, MEP_K_DISPATCH, 4);
   } else {
     // ---------------------------------------------------------------- expanders
-    const int xt = tid - (kSendWarps + 1) * 32, xw = xt >> 5;
+    const int xt = tid - (kFSend + 1) * 32, xw = xt >> 5;
     const int used_tiles = (cu_end + MEP_FLAG_ROWS - 1) / MEP_FLAG_ROWS;
     const int* rsrc = (const int*)peer_ptr(c, c.rank, c.off_rowsrc);
     char* hid = peer_ptr(c, c.rank, c.off_hidden);
-    unsigned char* slot = xslots + (size_t)xw * row_bytes;
-    uint32_t xparity = 0;
+    unsigned char* slot = xslots + (size_t)xw * 2 * row_bytes;      // this warp's two slots
+    uint32_t xpar = 0;                                              // bit s = parity of slot s's mbarrier
     auto tile_complete = [&](int t, int site) {      // bounded wait for tile t's arrivals (any thread)
       const uint32_t target = ep * (uint32_t)tile_rows(c, t);
       uint32_t seen = 0;
@@ -388,21 +389,28 @@ dispatch_flagged_kernel(MepCtxPack P, DispatchArgsPack A, int stages) {
       }
       bar_expanders();
       if (s_xfail) break;
-      // duplicate rows of this tile: row of the same shard -> this warp's slot -> duplicate slot, one
-      // row in flight per warp; everything a copy reads was acquired above
+      // duplicate rows of this tile: row of the same shard -> one of this warp's two slots -> duplicate
+      // slot; the load of the next row is under way while this one is stored. Everything a copy reads
+      // was acquired above.
       const int nd_ = s_xn;
       if (lane == 0) {
+        const int nj = nd_ > xw ? (nd_ - xw + kExpWarps - 1) / kExpWarps : 0;
+        auto issue_load = [&](int j) {
+          const int v = s_xlist[xw + j * kExpWarps], sl = j & 1;
+          mbar_expect_tx(&s_xbar[xw * 2 + sl], row_bytes);
+          bulk_g2s(slot + (size_t)sl * row_bytes, hid + (size_t)(v >> 7) * row_bytes, row_bytes, &s_xbar[xw * 2 + sl]);
+        };
         fence_proxy_async();
-        for (int i = xw; i < nd_; i += kExpWarps) {
-          const int v = s_xlist[i];
-          bulk_wait_read<0>();                      // the previous store has left the slot
-          mbar_expect_tx(&s_xbar[xw], row_bytes);
-          bulk_g2s(slot, hid + (size_t)(v >> 7) * row_bytes, row_bytes, &s_xbar[xw]);
-          if (!mbar_wait_bounded(&s_xbar[xw], xparity, c.wait_budget_ns)) {
+        if (nj > 0) issue_load(0);
+        for (int j = 0; j < nj; ++j) {
+          if (j + 1 < nj) { bulk_wait_read<0>(); issue_load(j + 1); }     // that slot's previous store has left it
+          const int sl = j & 1;
+          if (!mbar_wait_bounded(&s_xbar[xw * 2 + sl], (xpar >> sl) & 1u, c.wait_budget_ns)) {
             report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_DISPATCH, 63, t, 0, 0); s_xfail = 1; break;
           }
-          xparity ^= 1u;
-          bulk_s2g(hid + (size_t)(t * MEP_FLAG_ROWS + (v & 127)) * row_bytes, slot, row_bytes);
+          xpar ^= 1u << sl;
+          const int v = s_xlist[xw + j * kExpWarps];
+          bulk_s2g(hid + (size_t)(t * MEP_FLAG_ROWS + (v & 127)) * row_bytes, slot + (size_t)sl * row_bytes, row_bytes);
           bulk_commit();
         }
         bulk_wait_done<0>(); fence_proxy_async();
@@ -476,12 +484,12 @@ extern "C" int mep_launch_dispatch_flagged(int nv, const MepRankCtx* const* ctxs
   }
   const size_t row = (size_t)H * 2;
   const size_t tables = (size_t)(4 * epn + 2) * sizeof(int);
-  const size_t budget = 216 * 1024;
-  MEP_REQUIRE(budget > tables + row * (mep::kExpWarps + mep::kSendWarps),
+  const size_t budget = 212 * 1024;      // dynamic part; the kernel's static tables take another ~14 KB of the 227 KB
+  MEP_REQUIRE(budget > tables + row * (2 * mep::kExpWarps + mep::kFSend),
               "dispatch: H=%d rows (%zu B) with epn=%d do not fit shared memory", H, row, epn);
-  int stages = (int)((budget - tables - row * mep::kExpWarps) / (row * mep::kSendWarps));
+  int stages = (int)((budget - tables - row * 2 * mep::kExpWarps) / (row * mep::kFSend));
   if (stages > mep::kMaxStages) stages = mep::kMaxStages;
-  const size_t smem = row * (mep::kSendWarps * stages + mep::kExpWarps) + tables;
+  const size_t smem = row * (mep::kFSend * stages + 2 * mep::kExpWarps) + tables;
   return mep::launch_cooperative(mep::dispatch_flagged_kernel, dim3(num_sms, nv), dim3(mep::kFlagThreads), smem,
                                  stream, false, P, A, stages);
 }

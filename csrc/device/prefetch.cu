@@ -8,7 +8,7 @@
 // (eight per thread in flight) -- no TMA touches peer memory. Dtype-agnostic (bytes).
 // Ends with a cross-rank barrier: on return every rank's slots are complete.
 // Per-slot flags on top of that (the reference only has the trailing barrier, moonep/prefetch.py:467-470):
-// the CTA that finishes the LAST chunk of a slot release-stores the launch's prefetch epoch into the
+// the CTA that finishes the last share of a slot release-stores the launch's prefetch epoch into the
 // holder's flag word for that slot, so a consumer on the holder (the grouped GEMM, group epn + b) can start
 // on a prefetched expert as soon as that expert has landed instead of waiting for the whole launch.
 #include "prims.cuh"
@@ -64,8 +64,28 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
   int64_t chunks_per_slot = 0;
   for (int t = 0; t < a.ntensors; ++t) chunks_per_slot += (a.t[t].expert_bytes + kChunk - 1) / kChunk;
   const int64_t total = (int64_t)nslots * chunks_per_slot;
+  // Slot flags: chunks of one slot are consecutive work units, so a CTA finishes its share of slot `si`
+  // when its next unit belongs to another slot. Only then -- once per slot and CTA, not per chunk, so the
+  // stores of consecutive chunks stay in flight together -- it makes its stores visible, adds its chunk
+  // count to the slot's counter, and whoever completes the count publishes the flag on the holder.
+  int cur_si = -1, cur_cnt = 0;
+  auto finish_slot = [&]() {
+    if (cur_si < 0 || !c.slot_done) return;
+    __syncthreads();
+    if (tid == 0) {
+      const int idx = s_list[cur_si], d = idx / epn, b = idx - d * epn;
+      __threadfence_system();
+      if (atomicAdd(c.slot_done + idx, (uint32_t)cur_cnt) + (uint32_t)cur_cnt == (uint32_t)chunks_per_slot) {
+        c.slot_done[idx] = 0u;
+        __threadfence();
+        st_release_sys((uint32_t*)peer_ptr(c, d, c.off_slotflag) + b, ep);
+      }
+    }
+  };
   for (int64_t u = blockIdx.x; u < total; u += nb) {
     const int si = (int)(u / chunks_per_slot);
+    if (si != cur_si) { finish_slot(); cur_si = si; cur_cnt = 0; }
+    ++cur_cnt;
     int64_t ck = u - (int64_t)si * chunks_per_slot;
     int t = 0;
     for (;; ++t) { const int64_t n = (a.t[t].expert_bytes + kChunk - 1) / kChunk; if (ck < n) break; ck -= n; }
@@ -84,19 +104,8 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
       for (int j = 0; j < kVec; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) st_na_v4(dstp + (size_t)v * 16, x[j]); }
     }
     for (int64_t i = ((int64_t)nvec << 4) + tid; i < len; i += nt) dstp[i] = src[i];   // ragged tail
-    if (c.slot_done) {
-      // count the chunk; whoever completes the slot publishes its flag on the holder
-      __syncthreads();
-      if (tid == 0) {
-        __threadfence_system();
-        if (atomicAdd(c.slot_done + idx, 1u) == (uint32_t)chunks_per_slot - 1u) {
-          c.slot_done[idx] = 0u;
-          __threadfence();
-          st_release_sys((uint32_t*)peer_ptr(c, d, c.off_slotflag) + b, ep);
-        }
-      }
-    }
   }
+  finish_slot();
   cross_rank_barrier(c, nb, 1, MEP_K_PREFETCH, 10);
 }
 

@@ -282,14 +282,25 @@ def _dup_args(states, bufs, plans):
     return args
 
 
+def _dup_check(states, bufs, plans, num_blocks: int, kernel_id: int):
+    """MOONEP_CHECKED=1: validate the duplicate tables in a pass of their own before they are used."""
+    if states[0].ctx_host.checked:
+        lib = _native.load()
+        _native.check(lib.mep_launch_dup_check(len(states), _pack(states), _dup_args(states, bufs, plans), num_blocks,
+                                               kernel_id, _native.cur_stream()), "dup_check")
+
+
 def launch_dup_expand(states, bufs, plans, num_blocks: int, pdl: bool = False):
     lib = _native.load()
+    _dup_check(states, bufs, plans, num_blocks, 4)
+    pdl = pdl and not states[0].ctx_host.checked        # the check sits between dispatch and this kernel
     _native.check(lib.mep_launch_dup_expand(len(states), _pack(states), _dup_args(states, bufs, plans),
                                             num_blocks, 1 if pdl else 0, _native.cur_stream()), "dup_expand")
 
 
 def launch_dup_reduce(states, bufs, plans, num_blocks: int):
     lib = _native.load()
+    _dup_check(states, bufs, plans, num_blocks, 5)
     _native.check(lib.mep_launch_dup_reduce(len(states), _pack(states), _dup_args(states, bufs, plans),
                                             num_blocks, _native.cur_stream()), "dup_reduce")
 

@@ -22,6 +22,8 @@ CASES = [
     ("r4_dup_heavy",  64,  8, 2,   1024, 4, 2,  16,  "random"),
     ("r8_k1",         80,  1, 3,   256,  8, 1,  16,  "random"),
     ("r3_deep_ring",  300, 6, 5,   64,   3, 2,  8,   "biased"),
+    ("r8_k8",         96,  8, 2,   512,  8, 2,  16,  "biased"),
+    ("r8_wide_rows",  64,  8, 4,   7168, 8, 1,  128, "random"),
 ]
 
 
