@@ -26,7 +26,9 @@ struct ReduceTensor {
 struct GradReduceArgs {
   const int32_t* etc;
   int32_t ntensors;
-  int32_t flags;              // bit 0: cross-rank barrier before the first peer read; bit 1: leave the consumed slots as they are
+  int32_t flags;              // bit 0: cross-rank barrier before the first peer read; bit 1: leave the consumed slots as
+                              // they are (no second barrier either); bit 2: second barrier, but the slots are cleared
+                              // by grad_clear_kernel on all SMs afterwards instead of by this kernel's few CTAs
   ReduceTensor t[3];
 };
 struct GradReduceArgsPack { GradReduceArgs a[MEP_MAX_VRANKS]; };
@@ -210,6 +212,7 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
 
   if (a.flags & 2) return;
   if (!cross_rank_barrier(c, nb, 1, MEP_K_GRAD_REDUCE, 10)) return;
+  if (a.flags & 4) return;
 
   // clear my own consumed slots
   const int4 z = make_int4(0, 0, 0, 0);
@@ -225,7 +228,36 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
   }
 }
 
+// Zero this rank's consumed slots (the slots named by experts_to_copy[rank, :]). Launched behind
+// grad_reduce_kernel, whose second barrier guarantees that every owner has read them: a plain grid
+// over all SMs, because the 32 CTAs of the cooperative kernel can only store ~55 GB/s each.
+__global__ void __launch_bounds__(256) grad_clear_kernel(MepCtxPack P, GradReduceArgsPack A) {
+  const MepRankCtx* cp = P.ctx[blockIdx.y];
+  const GradReduceArgs& a = A.a[blockIdx.y];
+  const int epn = cp->epn, rank = cp->rank;
+  const int4 z = make_int4(0, 0, 0, 0);
+  const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, gnt = (int64_t)gridDim.x * blockDim.x;
+  for (int b = 0; b < epn; ++b) {
+    if (a.etc[(size_t)rank * epn + b] < 0) continue;
+    for (int t = 0; t < a.ntensors; ++t) {
+      const ReduceTensor& T = a.t[t];
+      char* sp = T.pool + (int64_t)rank * T.rank_stride + (int64_t)b * T.expert_elems * 4;
+      const int64_t nvec = T.expert_elems >> 2;
+      for (int64_t v = gtid; v < nvec; v += gnt) st_v4(sp + v * 16, z);
+      if (blockIdx.x == 0) for (int64_t i = (nvec << 2) + threadIdx.x; i < T.expert_elems; i += blockDim.x) reinterpret_cast<float*>(sp)[i] = 0.f;
+    }
+  }
+}
+
 }  // namespace mep
+
+extern "C" int mep_launch_grad_clear(int nv, const MepRankCtx* const* ctxs, const mep::GradReduceArgs* args,
+                                     int num_blocks, cudaStream_t stream) {
+  MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "grad_clear: nv=%d out of range", nv);
+  MepCtxPack P = {}; mep::GradReduceArgsPack A = {};
+  for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
+  return mep::launch_plain(mep::grad_clear_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A);
+}
 
 extern "C" int mep_launch_grad_reduce(int nv, const MepRankCtx* const* ctxs, const mep::GradReduceArgs* args,
                                       int num_sms, int R, int epn, cudaStream_t stream) {

@@ -30,21 +30,27 @@ struct PrefetchArgs {
 };
 struct PrefetchArgsPack { PrefetchArgs a[MEP_MAX_VRANKS]; };
 
-constexpr int kCopyThreads = 512;
-constexpr int64_t kChunk = 65536;
-constexpr int kVec = 8;               // 16-byte vectors per thread in flight
+constexpr int kPfWarps = 6;                 // copy warps per CTA (two 16 KB slots each at the usual sizes)
+constexpr int kCopyThreads = kPfWarps * 32;
+constexpr int64_t kChunk = 16384;           // bytes per piece (one shared-memory slot)
+constexpr int kPfMaxStages = 4;
 
-__global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P, PrefetchArgsPack A) {
+__global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P, PrefetchArgsPack A, int stages, int list_bytes) {
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
   const PrefetchArgs& a = A.a[blockIdx.y];
-  extern __shared__ int s_list[];
+  extern __shared__ __align__(128) unsigned char pf_smem[];
+  int* s_list = reinterpret_cast<int*>(pf_smem);
+  unsigned char* slots = pf_smem + list_bytes;
   __shared__ int s_n;
-  const int nb = gridDim.x, tid = threadIdx.x, nt = blockDim.x;
+  __shared__ __align__(8) uint64_t s_bar[kPfWarps * kPfMaxStages];
+  const int nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int R = c.R, epn = c.epn, lo = c.rank * epn;
   const uint32_t ep = c.pf_epoch ? *(volatile uint32_t*)c.pf_epoch : 0u;
+  if (tid < kPfWarps * kPfMaxStages) mbar_init(&s_bar[tid], 1);
+  fence_mbar_init();
 
   // Slot list in ascending (rank, slot) order. Every CTA must build the IDENTICAL list, because
-  // work unit u is mapped to list entry u / chunks_per_slot on whichever CTA owns u: one warp
+  // work unit u is mapped to list entry u / chunks_per_slot on whichever warp owns u: one warp
   // compacts with ballots (no atomics, whose arrival order could differ between CTAs).
   if (tid < 32) {
     int n = 0;
@@ -64,15 +70,38 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
   int64_t chunks_per_slot = 0;
   for (int t = 0; t < a.ntensors; ++t) chunks_per_slot += (a.t[t].expert_bytes + kChunk - 1) / kChunk;
   const int64_t total = (int64_t)nslots * chunks_per_slot;
-  // Slot flags: chunks of one slot are consecutive work units, so a CTA finishes its share of slot `si`
-  // when its next unit belongs to another slot. Only then -- once per slot and CTA, not per chunk, so the
-  // stores of consecutive chunks stay in flight together -- it makes its stores visible, adds its chunk
-  // count to the slot's counter, and whoever completes the count publishes the flag on the holder.
-  int cur_si = -1, cur_cnt = 0;
-  auto finish_slot = [&]() {
-    if (cur_si < 0 || !c.slot_done) return;
-    __syncthreads();
-    if (tid == 0) {
+  if (lane == 0) {
+    // One thread per warp drives the warp's pipeline. Pieces of one slot are consecutive work units, so
+    // the warp has finished its share of a slot when its next unit belongs to another one: only then it
+    // waits for its stores to complete, makes them visible and adds its count to the slot's counter;
+    // whoever completes the count publishes the slot's flag on the holder.
+    unsigned char* ring = slots + (size_t)warp * stages * kChunk;
+    uint64_t* bars = s_bar + warp * kPfMaxStages;
+    const int64_t gw = (int64_t)blockIdx.x * kPfWarps + warp, nw = (int64_t)nb * kPfWarps;
+    const int64_t n = gw < total ? (total - gw + nw - 1) / nw : 0;
+    struct Piece { const char* src; char* dst; uint32_t len; int si; };
+    auto piece = [&](int64_t j) {
+      const int64_t u = gw + j * nw;
+      const int si = (int)(u / chunks_per_slot);
+      int64_t ck = u - (int64_t)si * chunks_per_slot;
+      int t = 0;
+      for (;; ++t) { const int64_t m = (a.t[t].expert_bytes + kChunk - 1) / kChunk; if (ck < m) break; ck -= m; }
+      const CopyTensor& T = a.t[t];
+      const int idx = s_list[si], d = idx / epn, b = idx - d * epn, le = a.etc[idx] - lo;
+      const int64_t beg = ck * kChunk;
+      const int64_t len = (T.expert_bytes - beg) < kChunk ? (T.expert_bytes - beg) : kChunk;
+      return Piece{T.local + (int64_t)le * T.expert_bytes + beg, T.pool + (int64_t)d * T.rank_stride + (int64_t)b * T.expert_bytes + beg,
+                   (uint32_t)len, si};
+    };
+    auto load = [&](int64_t j) {
+      const Piece p = piece(j); const int st = (int)(j % stages);
+      mbar_expect_tx(&bars[st], p.len);
+      bulk_g2s(ring + (size_t)st * kChunk, p.src, p.len, &bars[st]);
+    };
+    int cur_si = -1, cur_cnt = 0;
+    auto finish_slot = [&]() {
+      if (cur_si < 0 || !c.slot_done) return;
+      bulk_wait_all<0>(); fence_proxy_async();
       const int idx = s_list[cur_si], d = idx / epn, b = idx - d * epn;
       __threadfence_system();
       if (atomicAdd(c.slot_done + idx, (uint32_t)cur_cnt) + (uint32_t)cur_cnt == (uint32_t)chunks_per_slot) {
@@ -80,32 +109,24 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
         __threadfence();
         st_release_sys((uint32_t*)peer_ptr(c, d, c.off_slotflag) + b, ep);
       }
+    };
+    const int pre = stages - 1;
+    for (int64_t i = 0; i < pre && i < n; ++i) load(i);
+    for (int64_t j = 0; j < n; ++j) {
+      const Piece p = piece(j);
+      if (p.si != cur_si) { finish_slot(); cur_si = p.si; cur_cnt = 0; }
+      ++cur_cnt;
+      if (j + pre < n) { bulk_wait_read<0>(); load(j + pre); }       // that slot's previous store has left it
+      const int st = (int)(j % stages);
+      if (!mbar_wait_bounded(&bars[st], (uint32_t)(j / stages) & 1u, c.wait_budget_ns)) {
+        report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_PREFETCH, 20, (int)j, 0, 0); break;
+      }
+      bulk_s2g(p.dst, ring + (size_t)st * kChunk, p.len);
+      bulk_commit();
     }
-  };
-  for (int64_t u = blockIdx.x; u < total; u += nb) {
-    const int si = (int)(u / chunks_per_slot);
-    if (si != cur_si) { finish_slot(); cur_si = si; cur_cnt = 0; }
-    ++cur_cnt;
-    int64_t ck = u - (int64_t)si * chunks_per_slot;
-    int t = 0;
-    for (;; ++t) { const int64_t n = (a.t[t].expert_bytes + kChunk - 1) / kChunk; if (ck < n) break; ck -= n; }
-    const CopyTensor& T = a.t[t];
-    const int idx = s_list[si], d = idx / epn, b = idx - d * epn, le = a.etc[idx] - lo;
-    const int64_t beg = ck * kChunk;
-    const int64_t len = (T.expert_bytes - beg) < kChunk ? (T.expert_bytes - beg) : kChunk;
-    const char* src = T.local + (int64_t)le * T.expert_bytes + beg;
-    char* dstp = T.pool + (int64_t)d * T.rank_stride + (int64_t)b * T.expert_bytes + beg;
-    const int nvec = (int)(len >> 4);
-    for (int v0 = 0; v0 < nvec; v0 += kVec * nt) {
-      int4 x[kVec];
-#pragma unroll
-      for (int j = 0; j < kVec; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) x[j] = ld_nc_v4(src + (size_t)v * 16); }
-#pragma unroll
-      for (int j = 0; j < kVec; ++j) { const int v = v0 + j * nt + tid; if (v < nvec) st_na_v4(dstp + (size_t)v * 16, x[j]); }
-    }
-    for (int64_t i = ((int64_t)nvec << 4) + tid; i < len; i += nt) dstp[i] = src[i];   // ragged tail
+    finish_slot();
+    bulk_wait_all<0>(); fence_proxy_async();
   }
-  finish_slot();
   cross_rank_barrier(c, nb, 1, MEP_K_PREFETCH, 10);
 }
 
@@ -131,10 +152,13 @@ extern "C" int mep_launch_prefetch(int nv, const MepRankCtx* const* ctxs, const 
   MEP_REQUIRE(nv >= 1 && nv <= MEP_MAX_VRANKS, "prefetch: nv=%d out of range", nv);
   MepCtxPack P = {}; mep::PrefetchArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  const size_t smem = (size_t)R * epn * sizeof(int);
-  MEP_REQUIRE(smem <= 160 * 1024, "prefetch: R*epn=%d exceeds the slot-list capacity", R * epn);
+  const size_t list_bytes = (((size_t)R * epn * sizeof(int)) + 127) & ~(size_t)127;
+  MEP_REQUIRE(list_bytes <= 96 * 1024, "prefetch: R*epn=%d exceeds the slot-list capacity", R * epn);
+  int stages = (int)((220 * 1024 - list_bytes) / ((size_t)mep::kPfWarps * mep::kChunk));
+  if (stages > mep::kPfMaxStages) stages = mep::kPfMaxStages;
+  const size_t smem = list_bytes + (size_t)mep::kPfWarps * stages * mep::kChunk;
   return mep::launch_cooperative(mep::prefetch_kernel, dim3(num_sms, nv), dim3(mep::kCopyThreads), smem,
-                                 stream, false, P, A);
+                                 stream, false, P, A, stages, (int)list_bytes);
 }
 
 MEP_EXPORT_SIZEOF(PrefetchArgs, mep::PrefetchArgs)

@@ -308,6 +308,7 @@ class OpsMixin:
             assert tuple(pool.shape[2:]) == tuple(local.shape[1:])
             assert pool.device == local.device
             assert (local[0].numel() * local.element_size()) % 16 == 0, f"{what}: expert payload must be a multiple of 16 bytes"
+            assert local.data_ptr() % 16 == 0, f"{what}: local tensors must be 16-byte aligned"
 
     def _prefetch_lists(self, plans, pairs_list, bump_epoch: bool = True):
         engine.launch_prefetch(self._states, [p.experts_to_copy for p in plans], pairs_list, bump_epoch)

@@ -366,7 +366,7 @@ def launch_grad_reduce(states, etc_list, tensor_pairs_list, entry_barrier: bool 
     for i in range(n):
         a = GradReduceArgs()
         a.etc = ptr(etc_list[i])
-        a.flags = (1 if entry_barrier else 0) | (0 if clear_slots else 2)
+        a.flags = (1 if entry_barrier else 0) | (4 if clear_slots else 2)
         pairs = tensor_pairs_list[i]
         a.ntensors = len(pairs)
         for j, (local, pool) in enumerate(pairs):
@@ -377,6 +377,9 @@ def launch_grad_reduce(states, etc_list, tensor_pairs_list, entry_barrier: bool 
         args[i] = a
     g = states[0].geo
     _native.check(lib.mep_launch_grad_reduce(n, _pack(states), args, g.num_sms, g.R, g.epn, _native.cur_stream()), "grad_reduce")
+    if clear_slots:     # behind the kernel's second barrier, on all SMs (the cooperative kernel's few CTAs store slowly)
+        sms = torch.cuda.get_device_properties(states[0].device).multi_processor_count
+        _native.check(lib.mep_launch_grad_clear(n, _pack(states), args, 2 * sms, _native.cur_stream()), "grad_clear")
 
 
 def launch_push_reduce(states, outs, out_ws, num_blocks):
