@@ -91,7 +91,9 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
   }
   __syncthreads();
   const int nact = s_nact;
-  if ((a.flags & 1) && !cross_rank_barrier(c, nb, 1, MEP_K_GRAD_REDUCE, 5)) return;
+  if (tid == 0) trace_mark(c, MEP_K_GRAD_REDUCE, 1);
+  if ((a.flags & 1) && !cross_rank_barrier(c, nb, kWeightLaneRow, MEP_K_GRAD_REDUCE, 5)) return;
+  if (tid == 0) trace_mark(c, MEP_K_GRAD_REDUCE, 2);
 
   // Each warp owns a 16 KB shared-memory stage of 32 slots (one slot = one 16-byte vector per
   // lane). A work unit is P vectors per lane of ONE expert matrix: the warp fetches them from EVERY
@@ -210,8 +212,10 @@ __global__ void __launch_bounds__(kRedThreads, 1) grad_reduce_kernel(MepCtxPack 
     }
   }
 
+  if (tid == 0) trace_mark(c, MEP_K_GRAD_REDUCE, 3);
   if (a.flags & 2) return;
-  if (!cross_rank_barrier(c, nb, 1, MEP_K_GRAD_REDUCE, 10)) return;
+  if (!cross_rank_barrier(c, nb, kWeightLaneRow, MEP_K_GRAD_REDUCE, 10)) return;
+  if (tid == 0) trace_mark(c, MEP_K_GRAD_REDUCE, 4);
   if (a.flags & 4) return;
 
   // clear my own consumed slots

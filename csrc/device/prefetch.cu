@@ -3,9 +3,10 @@
 // Counterpart of the reference's PrefetchKernel (moonep/prefetch.py:45-470): one launch
 // copies up to six tensors (gate/up/down and optionally their block scales) of every local
 // expert that the plan placed in some rank's slot (experts_to_copy[d, b] in this rank's id
-// range) to pool[d, b]. Expert payloads are contiguous, so the copy is 1-D: 64 KB chunks are
-// dealt round-robin to the CTAs and moved with 16-byte local loads and 16-byte peer stores
-// (eight per thread in flight) -- no TMA touches peer memory. Dtype-agnostic (bytes).
+// range) to pool[d, b]. Expert payloads are contiguous, so the copy is 1-D: 16 KB pieces are
+// dealt round-robin to the copy warps of all CTAs; one thread per warp runs a ring of shared-memory
+// slots, filling each with an untiled bulk copy from local memory and draining it with an untiled
+// bulk store to the holder's slot (no multicast, no tensor map). Dtype-agnostic (bytes).
 // Ends with a cross-rank barrier: on return every rank's slots are complete.
 // Per-slot flags on top of that (the reference only has the trailing barrier, moonep/prefetch.py:467-470):
 // the CTA that finishes the last share of a slot release-stores the launch's prefetch epoch into the
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
   }
   __syncthreads();
   const int nslots = s_n;
+  if (tid == 0) trace_mark(c, MEP_K_PREFETCH, 1);
 
   int64_t chunks_per_slot = 0;
   for (int t = 0; t < a.ntensors; ++t) chunks_per_slot += (a.t[t].expert_bytes + kChunk - 1) / kChunk;
@@ -126,8 +128,10 @@ __global__ void __launch_bounds__(kCopyThreads, 1) prefetch_kernel(MepCtxPack P,
     }
     finish_slot();
     bulk_wait_all<0>(); fence_proxy_async();
+    trace_mark(c, MEP_K_PREFETCH, 2);
   }
-  cross_rank_barrier(c, nb, 1, MEP_K_PREFETCH, 10);
+  cross_rank_barrier(c, nb, kWeightLaneRow, MEP_K_PREFETCH, 10);
+  if (tid == 0) trace_mark(c, MEP_K_PREFETCH, 3);
 }
 
 }  // namespace mep

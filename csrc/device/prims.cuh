@@ -161,6 +161,11 @@ __device__ __forceinline__ void trace_value(const MepRankCtx& c, int kernel, int
 // co-resident (cooperative launch). Self-resetting: CTA 0 adds 0x80000000-(n-1), the
 // others add 1, so the top bit flips exactly when everyone has arrived.
 // `sys` makes this CTA's earlier writes to peer memory visible system-wide first.
+// The weight-pool kernels (prefetch, grad_reduce) use a barrier word and a cross-rank flag row of their own
+// (kWeightLaneRow), so that one of them may run beside a token kernel (dispatch, combine) of the same Buffer
+// on another stream; two kernels of the same lane must still be ordered by their streams.
+constexpr int kWeightLaneRow = 3;
+__device__ __forceinline__ int bar_lane(int kernel) { return (kernel == MEP_K_PREFETCH || kernel == MEP_K_GRAD_REDUCE) ? 1 : 0; }
 __device__ __forceinline__ bool grid_sync(const MepRankCtx& c, int nblocks, int kernel, int site, bool sys = false) {
   __shared__ int s_ok;
   __syncthreads();
@@ -169,9 +174,10 @@ __device__ __forceinline__ bool grid_sync(const MepRankCtx& c, int nblocks, int 
     bool ok = true;
     if (nblocks > 1) {
       const uint32_t inc = (blockIdx.x == 0) ? (0x80000000u - (uint32_t)(nblocks - 1)) : 1u;
-      const uint32_t old = atom_add_release_gpu(c.grid_bar, inc);
+      uint32_t* word = c.grid_bar + bar_lane(kernel);
+      const uint32_t old = atom_add_release_gpu(word, inc);
       uint32_t now = 0;
-      ok = bounded_wait(c, [&] { now = ld_acquire_gpu(c.grid_bar); return ((now ^ old) & 0x80000000u) != 0; });
+      ok = bounded_wait(c, [&] { now = ld_acquire_gpu(word); return ((now ^ old) & 0x80000000u) != 0; });
       if (!ok) report(c, MEP_ERR_GRID_SYNC_TIMEOUT, kernel, site, blockIdx.x, now, old);
     }
     s_ok = ok ? 1 : 0;

@@ -66,7 +66,7 @@ typedef struct MepRankCtx {
       off_duploffs, off_ready;
   int64_t dup_group_cap, dup_loff_cap;   // per-source capacity of the staging tables
   // local scratch (ordinary device memory)
-  uint32_t* grid_bar;      // [1] software grid barrier word
+  uint32_t* grid_bar;      // [2] software grid barrier words: [0] token kernels, [1] weight-pool kernels
   uint32_t* epoch;         // [MEP_BAR_ROWS] cross-rank barrier epochs
   int32_t* hist;           // [num_vblocks, E]
   int32_t* count;          // [E]   tokens per expert over the whole group
