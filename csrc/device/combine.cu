@@ -146,11 +146,12 @@ __device__ __forceinline__ void cp_async_commit_wait_all() {
 }
 
 // Each warp owns a 16 KB shared-memory stage and walks its tokens: for a token with np rows it
-// fetches, per pass, floor(32/np) 16-byte vectors per lane from EVERY row with asynchronous
-// 16-byte copies (peer or local memory -> shared memory, no registers held while in flight),
-// waits for its own copies, adds the rows in fp32 (ascending k) and stores the bf16 result.
-// A lane only ever reads back what it copied itself, so no cross-lane synchronisation is needed.
-// With 14 warps per CTA up to 224 KB per SM are in flight, which is what hides NVLink latency.
+// fetches, per pass, floor(16/np) 16-byte vectors per lane from EVERY row -- one untiled bulk copy per
+// row (peer or local memory -> shared memory, issued by the warp's first lane, completion on a barrier
+// of the stage half; no multicast, no tensor map) -- into one half of the stage while the other half
+// is summed: the rows are added in fp32 (ascending k) and the bf16 result is stored.
+// A token with more than 16 rows takes the unpipelined path (one 16-byte asynchronous copy per lane
+// and vector into the whole stage). With 14 warps per CTA up to 224 KB per SM are in flight.
 __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, CombineArgsPack A) {
   pdl_wait();                                // rows of this shard were pre-reduced by the kernel before
   const MepRankCtx c = *P.ctx[blockIdx.y];   // by value: fields stay in registers across asm memory clobbers
@@ -162,6 +163,10 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, 
   const int nvec = (int)(row_bytes >> 4);
   const int vpl = (nvec + 31) >> 5;                  // vectors per lane in a full row
 
+  __shared__ __align__(8) uint64_t s_cbar[kCombWarps * 2];     // one barrier per warp and stage half
+  if (tid < kCombWarps * 2) mbar_init(&s_cbar[tid], 1);
+  fence_mbar_init();
+  __syncthreads();
   if (tid == 0) trace_mark(c, MEP_K_COMBINE, 1);
   if (a.entry_barrier) { if (!cross_rank_barrier(c, nb, 2, MEP_K_COMBINE, 10)) return; }
   if (tid == 0) trace_mark(c, MEP_K_COMBINE, 2);
@@ -169,75 +174,127 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(MepCtxPack P, 
   if (tid == 0 && blockIdx.x == 0) count(c, MEP_CNT_COMBINES, 1);
   int pulled = 0;
   const uint32_t stage = smem_u32(smem) + (uint32_t)warp * (kCombSlots * 32 * 16);
-  const unsigned char* stage_g = smem + (size_t)warp * (kCombSlots * 32 * 16);
-  for (int s = blockIdx.x * kCombWarps + warp; s < S; s += nb * kCombWarps) {
-    int dval = -1;
-    if (lane < K) dval = a.dst[(size_t)s * K + lane];
-    const char* myrow = nullptr;
-    if (lane < K) {
-      const int raw = dval >= 0 ? dval : -dval - 1;
+  unsigned char* stage_g = smem + (size_t)warp * (kCombSlots * 32 * 16);
+  uint64_t* bars = s_cbar + warp * 2;
+  uint32_t half_phase = 0;                   // parity of the two halves' barriers
+  // A token's K table entries as one lane each sees them. They are fetched one token ahead (the route
+  // weight comes from the peer, a full NVLink round trip), and the first pass of the next token is issued
+  // before the last pass of this one is summed, so a warp always has copies outstanding.
+  struct Tok { int dval; const char* myrow; float w; int bad; };
+  auto fetch = [&](int s) {
+    Tok t; t.dval = -1; t.myrow = nullptr; t.w = 0.f; t.bad = 0;
+    if (s < S && lane < K) {
+      t.dval = a.dst[(size_t)s * K + lane];
+      const int raw = t.dval >= 0 ? t.dval : -t.dval - 1;
       const int d = raw / NvS, loff = raw - d * NvS;
-      if (d >= c.R) {         // corrupt or foreign plan: report, form no address from the entry
-        report(c, MEP_ERR_BOUNDS, MEP_K_COMBINE, 20, s, (uint32_t)raw, (uint32_t)(c.R * NvS));
-        if (a.out_weights) a.out_weights[(size_t)s * K + lane] = 0.f;
-      } else {
-        if (a.out_weights)
-          a.out_weights[(size_t)s * K + lane] = __ldcg((const float*)peer_ptr(c, d, c.off_weights) + loff);
-        if (dval >= 0) myrow = peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes;
+      if (d >= c.R) t.bad = raw + 1;      // corrupt or foreign plan: form no address from the entry
+      else {
+        if (a.out_weights) t.w = __ldcg((const float*)peer_ptr(c, d, c.off_weights) + loff);
+        if (t.dval >= 0) t.myrow = peer_ptr(c, d, c.off_hidden) + (size_t)loff * row_bytes;
       }
     }
-    const unsigned prim = __ballot_sync(0xffffffffu, myrow != nullptr);
-    const int np = __popc(prim);
+    return t;
+  };
+  // One pass moves `per` 16-byte vectors per lane from EVERY row of the token into the warp's stage,
+  // then sums them. With up to kCombSlots / 2 rows the stage is split in two halves and the next pass
+  // is already in flight while this one is summed.
+  struct Shape { unsigned prim; int np, per, npass; bool pipelined; };
+  auto shape_of = [&](const Tok& t) {
+    Shape h; h.prim = __ballot_sync(0xffffffffu, t.myrow != nullptr); h.np = __popc(h.prim);
+    h.pipelined = h.np > 0 && h.np <= kCombSlots / 2;
+    h.per = h.np ? (h.pipelined ? kCombSlots / 2 : kCombSlots) / h.np : 1;
+    if (h.per > vpl) h.per = vpl;
+    h.npass = (vpl + h.per - 1) / h.per;
+    return h;
+  };
+  unsigned pending = 0;                      // halves with a bulk copy issued and not yet waited for
+  // pipelined pass p of a token into half h: one bulk copy per row -- this pass's share of a row is
+  // contiguous there and in the stage
+  auto issue_bulk = [&](const Tok& t, const Shape& sh, int p, int h) {
+    const int j0 = p * sh.per, nj = vpl - j0 < sh.per ? vpl - j0 : sh.per;
+    const size_t b0 = (size_t)j0 * 512;
+    const uint32_t bytes = (uint32_t)(row_bytes - b0 < (size_t)nj * 512 ? row_bytes - b0 : (size_t)nj * 512);
+    __syncwarp();                            // every lane has finished reading the half that is refilled now
+    if (lane == 0) mbar_expect_tx(&bars[h], bytes * (uint32_t)sh.np);
+    unsigned rest = sh.prim;
+    for (int r = 0; r < sh.np; ++r) {
+      const int src = __ffs(rest) - 1; rest &= rest - 1;
+      const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)t.myrow, src);
+      if (lane == 0)
+        bulk_g2s(stage_g + (size_t)h * (kCombSlots / 2 * 32 * 16) + (size_t)r * sh.per * 512, rp + b0, bytes, &bars[h]);
+    }
+    pending |= 1u << h;
+  };
+  auto consume = [&](const Shape& sh, int p, const unsigned char* base, char* orow) {
+    const int j0 = p * sh.per, nj = vpl - j0 < sh.per ? vpl - j0 : sh.per;
+    for (int j = 0; j < nj; ++j) {
+      const int v = (j0 + j) * 32 + lane;
+      if (v >= nvec) continue;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int r = 0; r < sh.np; ++r)
+        acc_bf16x8(acc, *reinterpret_cast<const int4*>(base + (size_t)((r * sh.per + j) * 32 + lane) * 16));
+      st_na_v4(orow + (size_t)v * 16, pack_bf16x8(acc));
+    }
+  };
+  const int stride = nb * kCombWarps;
+  int s = blockIdx.x * kCombWarps + warp;
+  Tok cur = fetch(s);
+  Shape cs = shape_of(cur);
+  uint32_t q = 0;                            // passes waited for so far: the next one sits in half q & 1
+  bool cur_issued = false, ok = true;
+  if (s < S && cs.pipelined) { issue_bulk(cur, cs, 0, 0); cur_issued = true; }
+  for (; s < S && ok; s += stride) {
+    const int sn = s + stride;
+    const Tok nxt = fetch(sn);
+    const Shape nsh = shape_of(nxt);
+    bool nxt_issued = false;
+    if (lane < K) {
+      if (cur.bad) {
+        report(c, MEP_ERR_BOUNDS, MEP_K_COMBINE, 20, s, (uint32_t)(cur.bad - 1), (uint32_t)(c.R * NvS));
+        if (a.out_weights) a.out_weights[(size_t)s * K + lane] = 0.f;
+      } else if (a.out_weights) a.out_weights[(size_t)s * K + lane] = cur.w;
+    }
     char* orow = (char*)a.out + (size_t)s * row_bytes;
-    if (np == 0) {            // no valid primary row (only possible with a corrupt plan): the token's output is zero
+    pulled += cs.np;
+    if (cs.np == 0) {         // no valid primary row (only possible with a corrupt plan): the token's output is zero
       if (lane == 0) report(c, MEP_ERR_BOUNDS, MEP_K_COMBINE, 21, s, 0u, (uint32_t)K);
       for (int v = lane; v < nvec; v += 32) st_na_v4(orow + (size_t)v * 16, make_int4(0, 0, 0, 0));
-      continue;
-    }
-    pulled += np;
-    // One pass moves `per` 16-byte vectors per lane from EVERY row of the token into the warp's stage,
-    // then sums them. With up to kCombSlots / 2 rows the stage is split in two halves and pass p + 1
-    // is already in flight while pass p is summed, so the warp always has copies outstanding.
-    const bool pipelined = np <= kCombSlots / 2;
-    int per = (pipelined ? kCombSlots / 2 : kCombSlots) / np;
-    if (per > vpl) per = vpl;
-    const int npass = (vpl + per - 1) / per;
-    auto issue = [&](int p) {
-      const int j0 = p * per, nj = vpl - j0 < per ? vpl - j0 : per;
-      const uint32_t base = stage + (pipelined ? (uint32_t)(p & 1) * (kCombSlots / 2 * 32 * 16) : 0u);
-      unsigned rest = prim;
-      for (int r = 0; r < np; ++r) {
-        const int src = __ffs(rest) - 1; rest &= rest - 1;
-        const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)myrow, src);
-        for (int j = 0; j < nj; ++j) {
-          const int v = (j0 + j) * 32 + lane;
-          if (v < nvec) cp_async16(base + (uint32_t)((r * per + j) * 32 + lane) * 16, rp + (size_t)v * 16);
+    } else if (!cs.pipelined) {
+      // more than kCombSlots / 2 rows: whole stage per pass, one 16-byte asynchronous copy per lane and vector
+      for (int p = 0; p < cs.npass; ++p) {
+        const int j0 = p * cs.per, nj = vpl - j0 < cs.per ? vpl - j0 : cs.per;
+        unsigned rest = cs.prim;
+        for (int r = 0; r < cs.np; ++r) {
+          const int src = __ffs(rest) - 1; rest &= rest - 1;
+          const char* rp = (const char*)__shfl_sync(0xffffffffu, (unsigned long long)cur.myrow, src);
+          for (int j = 0; j < nj; ++j) {
+            const int v = (j0 + j) * 32 + lane;
+            if (v < nvec) cp_async16(stage + (uint32_t)((r * cs.per + j) * 32 + lane) * 16, rp + (size_t)v * 16);
+          }
         }
+        cp_async_commit_wait_all();
+        consume(cs, p, stage_g, orow);
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    auto consume = [&](int p) {
-      const int j0 = p * per, nj = vpl - j0 < per ? vpl - j0 : per;
-      const unsigned char* base = stage_g + (pipelined ? (size_t)(p & 1) * (kCombSlots / 2 * 32 * 16) : 0);
-      for (int j = 0; j < nj; ++j) {
-        const int v = (j0 + j) * 32 + lane;
-        if (v >= nvec) continue;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int r = 0; r < np; ++r)
-          acc_bf16x8(acc, *reinterpret_cast<const int4*>(base + (size_t)((r * per + j) * 32 + lane) * 16));
-        st_na_v4(orow + (size_t)v * 16, pack_bf16x8(acc));
-      }
-    };
-    if (!pipelined) {
-      for (int p = 0; p < npass; ++p) { issue(p); asm volatile("cp.async.wait_group 0;" ::: "memory"); consume(p); }
     } else {
-      issue(0);
-      for (int p = 0; p < npass; ++p) {
-        if (p + 1 < npass) { issue(p + 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
-        else asm volatile("cp.async.wait_group 0;" ::: "memory");
-        consume(p);
+      if (!cur_issued) issue_bulk(cur, cs, 0, q & 1);
+      for (int p = 0; p < cs.npass; ++p) {
+        const int h = q & 1;
+        if (p + 1 < cs.npass) issue_bulk(cur, cs, p + 1, h ^ 1);
+        else if (sn < S && nsh.pipelined) { issue_bulk(nxt, nsh, 0, h ^ 1); nxt_issued = true; }
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bars[h], (half_phase >> h) & 1u, c.wait_budget_ns))) {
+          if (lane == 0) report(c, MEP_ERR_MBAR_TIMEOUT, MEP_K_COMBINE, 22, s, (uint32_t)p, 0);
+          ok = false; break;
+        }
+        half_phase ^= 1u << h; pending &= ~(1u << h);
+        consume(cs, p, stage_g + (size_t)h * (kCombSlots / 2 * 32 * 16), orow);
+        ++q;
       }
     }
+    cur = nxt; cs = nsh; cur_issued = nxt_issued;
+  }
+  if (!ok) {                  // a copy never arrived: give the other one its time too before the stage goes away
+    for (int h = 0; h < 2; ++h)
+      if (((pending >> h) & 1u) && h != (int)(q & 1)) mbar_wait_bounded(&bars[h], (half_phase >> h) & 1u, c.wait_budget_ns);
   }
   if (lane == 0 && pulled) count(c, MEP_CNT_ROWS_PULLED, (unsigned long long)pulled);
 }

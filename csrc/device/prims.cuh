@@ -261,7 +261,7 @@ __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // 1-D bulk copy global -> this CTA's shared memory, completion counted on `bar`.
-// Source must be LOCAL device memory. Size and both addresses multiples of 16 bytes.
+// The source may be local or peer memory (this form has no multicast). Size and both addresses multiples of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                :: "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
