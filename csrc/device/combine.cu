@@ -7,8 +7,8 @@
 // token's rows; duplicates of one destination rank are summed in fp32 and rounded to bf16
 // once into the primary row, the per-rank partial sums are then added in fp32 (ascending k)
 // and rounded once; the optional [S,K] channel gathers the per-slot fp32 route weights back
-// bit-exactly. Peer rows are pulled with per-lane asynchronous 16-byte copies into shared memory
-// (see combine_kernel); bulk copies are not used for peer reads.
+// bit-exactly. Peer rows are pulled with untiled bulk copies into shared memory
+// (see combine_kernel).
 #include "prims.cuh"
 #include "../host/launch.h"
 #include <stdlib.h>
@@ -104,23 +104,31 @@ __global__ void __launch_bounds__(256) dup_reduce_kernel(MepCtxPack P, DupArgsPa
   const int NvS = cp->NvS;
   const DupArgs& a = A.a[blockIdx.y];
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
   const int ng = a.dup_counts[0];
   const size_t row_bytes = (size_t)cp->H * 2;
   const int nvec = (int)(row_bytes >> 4);
   char* base = (char*)a.buf;
-  for (int g = gw; g < ng; g += nw) {
+  // Every row is split into kDupParts column parts (runs of whole 128-vector steps) and a block works on
+  // one part of all groups: with one warp per whole group a launch has only two or three groups per warp,
+  // and the warps with one group more set the time.
+  const int part = blockIdx.x % kDupParts, nsteps = (nvec + 127) >> 7;
+  const int vb = (part * nsteps / kDupParts) << 7;
+  int ve = ((part + 1) * nsteps / kDupParts) << 7; if (ve > nvec) ve = nvec;
+  if (vb >= ve) { pdl_trigger(); return; }
+  const int pgw = (blockIdx.x / kDupParts) * wpb + (threadIdx.x >> 5);
+  const int pnw = ((gridDim.x - part + kDupParts - 1) / kDupParts) * wpb;
+  for (int g = pgw; g < ng; g += pnw) {
     const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
     if ((unsigned)p >= (unsigned)NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
     // lane 0 holds the primary row, lanes 1..n the duplicates in table order
     const char* myrow = nullptr;
-    if (lane == 0) myrow = base + (size_t)p * row_bytes;
+    if (lane == 0) myrow = base + (size_t)p * row_bytes + (size_t)vb * 16;
     else if (lane <= n) {
       const int q = a.dup_loffs[st + lane - 1];
-      if ((unsigned)q < (unsigned)NvS) myrow = base + (size_t)q * row_bytes;
+      if ((unsigned)q < (unsigned)NvS) myrow = base + (size_t)q * row_bytes + (size_t)vb * 16;
     }
     const unsigned rows = __ballot_sync(0xffffffffu, myrow != nullptr);
-    reduce_rows_auto<false>(myrow, rows, __popc(rows), base + (size_t)p * row_bytes, nvec, lane);
+    reduce_rows_auto<false>(myrow, rows, __popc(rows), base + (size_t)p * row_bytes + (size_t)vb * 16, ve - vb, lane);
   }
   pdl_trigger();                               // the combine may be scheduled while this grid drains
 }
@@ -378,7 +386,7 @@ extern "C" int mep_launch_dup_reduce(int nv, const MepRankCtx* const* ctxs, cons
                                      int num_blocks, cudaStream_t stream) {
   MepCtxPack P = {}; mep::DupArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  return mep::launch_plain(mep::dup_reduce_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, P, A);
+  return mep::launch_plain(mep::dup_reduce_kernel, dim3(mep::dup_grid(num_blocks), nv), dim3(256), 0, stream, P, A);
 }
 
 extern "C" int mep_launch_combine(int nv, const MepRankCtx* const* ctxs, const mep::CombineArgs* args,

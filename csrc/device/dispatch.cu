@@ -247,12 +247,17 @@ __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPa
   const int NvS = cp->NvS;
   const DupArgs& a = A.a[blockIdx.y];
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
   const int ng = a.dup_counts[0];
   const size_t row_bytes = (size_t)cp->H * 2;
   const int nvec = (int)(row_bytes >> 4);
   char* base = (char*)a.buf;
-  for (int g = gw; g < ng; g += nw) {
+  // a block copies one column part [vb, ve) of all groups (see dup_reduce_kernel)
+  const int part = blockIdx.x % kDupParts, nsteps = (nvec + 127) >> 7;
+  const int vb = (part * nsteps / kDupParts) << 7;
+  int ve = ((part + 1) * nsteps / kDupParts) << 7; if (ve > nvec) ve = nvec;
+  const int pgw = (blockIdx.x / kDupParts) * wpb + (threadIdx.x >> 5);
+  const int pnw = ((gridDim.x - part + kDupParts - 1) / kDupParts) * wpb;
+  for (int g = pgw; g < ng; g += pnw) {
     const int p = a.dup_groups[3 * g], st = a.dup_groups[3 * g + 1], n = a.dup_groups[3 * g + 2];
     if ((unsigned)p >= (unsigned)NvS || n <= 0 || n >= MEP_MAX_TOPK) continue;
     const char* src = base + (size_t)p * row_bytes;
@@ -262,7 +267,7 @@ __global__ void __launch_bounds__(256) dup_expand_kernel(MepCtxPack P, DupArgsPa
       myq = a.dup_loffs[st + lane];
       if ((unsigned)myq >= (unsigned)NvS) myq = -1;
     }
-    for (int v0 = 0; v0 < nvec; v0 += 128) {          // 4 x 16-byte loads in flight per lane
+    for (int v0 = vb; v0 < ve; v0 += 128) {           // 4 x 16-byte loads in flight per lane
       int4 x[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) { const int v = v0 + j * 32 + lane; if (v < nvec) x[j] = ld_nc_v4(src + (size_t)v * 16); }
@@ -313,12 +318,17 @@ __global__ void __launch_bounds__(256) dup_expand_fresh_kernel(MepCtxPack P, Dup
   }
   // expansion, one warp per group, groups addressed through the staging regions
   const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = gridDim.x * wpb;
   const int total = s_goff[c.R];
   const size_t row_bytes = (size_t)c.H * 2;
   const int nvec = (int)(row_bytes >> 4);
   char* base = (char*)a.buf;
-  for (int g = gw; g < total; g += nw) {
+  // a block copies one column part [vb, ve) of all groups (see dup_reduce_kernel)
+  const int part = blockIdx.x % kDupParts, nsteps = (nvec + 127) >> 7;
+  const int vb = (part * nsteps / kDupParts) << 7;
+  int ve = ((part + 1) * nsteps / kDupParts) << 7; if (ve > nvec) ve = nvec;
+  const int pgw = (blockIdx.x / kDupParts) * wpb + (threadIdx.x >> 5);
+  const int pnw = ((gridDim.x - part + kDupParts - 1) / kDupParts) * wpb;
+  for (int g = pgw; g < total; g += pnw) {
     int lo = 0, hi = c.R - 1;                         // source r with s_goff[r] <= g < s_goff[r+1]
     while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (s_goff[mid] <= g) lo = mid; else hi = mid - 1; }
     const int r = lo, j = g - s_goff[r];
@@ -328,7 +338,7 @@ __global__ void __launch_bounds__(256) dup_expand_fresh_kernel(MepCtxPack P, Dup
     const char* src = base + (size_t)p * row_bytes;
     int myq = -1;
     if (lane < n) { myq = __ldcg(sl + (size_t)r * c.dup_loff_cap + st + lane); if ((unsigned)myq >= (unsigned)c.NvS) myq = -1; }
-    for (int v0 = 0; v0 < nvec; v0 += 128) {
+    for (int v0 = vb; v0 < ve; v0 += 128) {
       int4 x[4];
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) { const int v = v0 + jj * 32 + lane; if (v < nvec) x[jj] = ld_nc_v4(src + (size_t)v * 16); }
@@ -380,14 +390,14 @@ extern "C" int mep_launch_dup_expand(int nv, const MepRankCtx* const* ctxs, cons
                                      int num_blocks, int pdl, cudaStream_t stream) {
   MepCtxPack P = {}; mep::DupArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  return mep::launch_plain_pdl(mep::dup_expand_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, pdl != 0, P, A);
+  return mep::launch_plain_pdl(mep::dup_expand_kernel, dim3(mep::dup_grid(num_blocks), nv), dim3(256), 0, stream, pdl != 0, P, A);
 }
 
 extern "C" int mep_launch_dup_expand_fresh(int nv, const MepRankCtx* const* ctxs, const mep::DupFreshArgs* args,
                                            int num_blocks, int pdl, cudaStream_t stream) {
   MepCtxPack P = {}; mep::DupFreshArgsPack A = {};
   for (int i = 0; i < nv; ++i) { P.ctx[i] = ctxs[i]; A.a[i] = args[i]; }
-  return mep::launch_plain_pdl(mep::dup_expand_fresh_kernel, dim3(num_blocks, nv), dim3(256), 0, stream, pdl != 0, P, A);
+  return mep::launch_plain_pdl(mep::dup_expand_fresh_kernel, dim3(mep::dup_grid(num_blocks), nv), dim3(256), 0, stream, pdl != 0, P, A);
 }
 
 MEP_EXPORT_SIZEOF(DispatchArgs, mep::DispatchArgs)

@@ -165,6 +165,10 @@ __device__ __forceinline__ void trace_value(const MepRankCtx& c, int kernel, int
 // (kWeightLaneRow), so that one of them may run beside a token kernel (dispatch, combine) of the same Buffer
 // on another stream; two kernels of the same lane must still be ordered by their streams.
 constexpr int kWeightLaneRow = 3;
+// The duplicate expansion / reduction kernels split every row into this many column parts, one warp each.
+constexpr int kDupParts = 4;
+// ... so their grids are whole multiples of it (block b works on part b % kDupParts).
+inline int dup_grid(int num_blocks) { return (num_blocks + kDupParts - 1) / kDupParts * kDupParts; }
 __device__ __forceinline__ int bar_lane(int kernel) { return (kernel == MEP_K_PREFETCH || kernel == MEP_K_GRAD_REDUCE) ? 1 : 0; }
 __device__ __forceinline__ bool grid_sync(const MepRankCtx& c, int nblocks, int kernel, int site, bool sys = false) {
   __shared__ int s_ok;
