@@ -13,6 +13,7 @@ Imported only by bench_reference.py after ``baseline/_ref`` has been put on ``sy
 
 import json
 import os
+import sys
 import time
 
 import torch
@@ -49,6 +50,21 @@ def _gmm_wgrad(x, dy, offs, G):
             out[g] = x[s:e].t() @ dy[s:e]
         s = e
     return out
+
+
+def _clock_sampler(local_rank):
+    """nvidia-smi sampler of the clocks during the timed region.  The class is loaded from its source
+    file (standard library only), so that the package with the kernels is not imported on this path."""
+    import importlib.util
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "moonep_b200", "utils", "clocks.py")
+    try:
+        spec = importlib.util.spec_from_file_location("_mep_clocks", path)
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["_mep_clocks"] = mod
+        spec.loader.exec_module(mod)
+        return mod.ClockSampler(local_rank).start()
+    except Exception:      # noqa: BLE001
+        return None
 
 
 def run(args):
@@ -310,6 +326,7 @@ def run(args):
         if int(ok) == 0:
             trial[mode] = float("inf")
     ffn["mode"] = min(trial, key=trial.get)
+    sampler = _clock_sampler(int(os.environ.get("LOCAL_RANK", "0")))     # started before the warm-up, as in the other arm
     for _ in range(W_):
         step(devb[0].detach())
     sync()
@@ -320,6 +337,7 @@ def run(args):
     e1.record()
     sync()
     ms = mx(e0.elapsed_time(e1) / args.steps)
+    clocks = sampler.stop() if sampler is not None else {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
     copy_stream = torch.cuda.Stream()
 
     def fetch(i):
@@ -436,6 +454,7 @@ def run(args):
                      "expert_ffn": ("torch._grouped_mm" if ffn["mode"] == "grouped" else "one cuBLAS torch.mm per expert group")
                                    + f"; SwiGLU and SGD: {fused['how']}; trial step ms: {trial}"},
            "comm": comm,
+           "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                    "h2d_bytes_per_step": S * H * 2, "d2h_bytes_per_step": 4},
            "loss": lv, "maxvio_sweep": sweep}
