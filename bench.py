@@ -178,16 +178,26 @@ def run_ours(args):
     if args.optimizer_in_backward:
         blk.fuse_optimizer(lr)      # each projection's SGD runs beside the remaining backward GEMMs
 
-    def step(x):
+    # where in a captured step the host-to-device copy of the NEXT step's batch starts (end-to-end run)
+    copy_at = os.environ.get("MOONEP_BENCH_COPY_AT", "optimizer")
+
+    def step(x, stage_next=None):
         x.requires_grad_(True)
+        if stage_next is not None and copy_at == "start":
+            stage_next()
         y = blk.forward(x)
         loss = mean_square(y)
+        if stage_next is not None and copy_at == "backward":
+            stage_next()
         loss.backward()
+        if stage_next is not None and copy_at == "optimizer":
+            stage_next()
         blk.sgd_step(lr)
         x.grad = None
         return loss.detach()
 
     graphed = [None]        # GraphedSteps once a step has been captured
+    graphed_e2e = [None]    # the same steps, each also copying in the next batch from pinned host memory
 
     def timed_steps(n):
         barrier_sync(world)
@@ -231,7 +241,7 @@ def run_ours(args):
             err = e
         if agree_any(1 if err is not None else 0):
             return err if err is not None else RuntimeError("failure on another rank")
-        graphed[0] = None
+        graphed[0], graphed_e2e[0] = None, None
         if args.no_cuda_graph:
             return None
         # Capture the whole step (both input buffers) as CUDA graphs: one launch per step instead
@@ -247,26 +257,32 @@ def run_ours(args):
 
             gs = GraphedSteps(lambda x: step(x), dev_batches, health=health)
             gs.launches_per_step = (lib.mep_launch_count() - c0) // len(gs)
+            ge = None
+            if os.environ.get("MOONEP_BENCH_COPY_IN_GRAPH", "1") != "0":
+                ge = GraphedSteps(step, dev_batches, health=health, host_inputs=host_batches, pool=gs.pool)
             ok, note = 1, "whole step replayed from a captured CUDA graph"
         except Exception as e:      # noqa: BLE001
-            gs, ok, note = None, 0, f"capture failed, launched from Python: {type(e).__name__}: {str(e)[:160]}"
+            gs, ge, ok, note = None, None, 0, f"capture failed, launched from Python: {type(e).__name__}: {str(e)[:160]}"
             type(blk.moe).forget_deferred()
             torch.cuda.synchronize()
         if agree_any(1 - ok) and ok:
-            gs, note = None, "capture failed on another rank, launched from Python"
+            gs, ge, note = None, None, "capture failed on another rank, launched from Python"
         state["graph_note"] = note
         err = None
         try:
             if gs is not None:
                 for i in range(3):
                     gs.replay(i)
+                if ge is not None:
+                    for i in range(2):
+                        ge.replay(i)
                 torch.cuda.synchronize()
                 blk.buf.check(); gg.check_status()
         except Exception as e:      # noqa: BLE001
             err = e
         if agree_any(1 if err is not None else 0):
             return err if err is not None else RuntimeError("failure on another rank")
-        graphed[0] = gs
+        graphed[0], graphed_e2e[0] = gs, ge
         return None
 
     # Safety net: should a bounded device wait run out while preparing on any rank (reported as an
@@ -281,7 +297,7 @@ def run_ours(args):
         if plain:
             raise err
         path_note = f"fallback to the plain path after {type(err).__name__}: {str(err)[:120]}"
-        graphed[0] = None
+        graphed[0], graphed_e2e[0] = None, None
         type(blk.moe).forget_deferred()
         torch.cuda.synchronize()
         try:
@@ -326,23 +342,39 @@ def run_ours(args):
         step_done[i % 2].synchronize()
         return float((graphed[0].host_losses[i % 2] if graphed[0] is not None else loss_host[i % 2])[0])
 
+    def read_loss_of(gs, i):
+        step_done[i % 2].synchronize()
+        return float(gs.host_losses[i % 2][0])
+
     barrier_sync(world)
     t0 = time.perf_counter()
-    nxt = fetch(0)
-    for i in range(args.steps):
-        x, ev = nxt
-        if i + 1 < args.steps:
-            nxt = fetch(i + 1)
-        main.wait_event(ev)
-        if graphed[0] is not None:
-            graphed[0].replay(i)
-        else:
-            x.record_stream(main)
-            loss_host[i % 2].copy_(step(x).reshape(1), non_blocking=True)
-        step_done[i % 2] = main.record_event()
-        if i > 0:
-            loss_val = read_loss(i - 1)
-    loss_val = read_loss(args.steps - 1)
+    if graphed_e2e[0] is not None:
+        # every replay copies the NEXT step's batch from pinned host memory inside its graph (beside the
+        # optimizer, where no kernel with system-scope fences runs); only the first batch is copied here
+        ge = graphed_e2e[0]
+        dev_batches[0].detach().copy_(host_batches[0], non_blocking=True)
+        for i in range(args.steps):
+            ge.replay(i)
+            step_done[i % 2] = main.record_event()
+            if i > 0:
+                loss_val = read_loss_of(ge, i - 1)
+        loss_val = read_loss_of(ge, args.steps - 1)
+    else:
+        nxt = fetch(0)
+        for i in range(args.steps):
+            x, ev = nxt
+            if i + 1 < args.steps:
+                nxt = fetch(i + 1)
+            main.wait_event(ev)
+            if graphed[0] is not None:
+                graphed[0].replay(i)
+            else:
+                x.record_stream(main)
+                loss_host[i % 2].copy_(step(x).reshape(1), non_blocking=True)
+            step_done[i % 2] = main.record_event()
+            if i > 0:
+                loss_val = read_loss(i - 1)
+        loss_val = read_loss(args.steps - 1)
     barrier_sync(world)
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / args.steps, world)
     clocks = sampler.stop()
@@ -462,6 +494,8 @@ def run_ours(args):
                           + (" (each projection's SGD is launched inside the backward pass, on a side stream, once its "
                              "gradient is final)" if args.optimizer_in_backward else ""),
                   "launch": graph_note, "path": path_note,
+                  "e2e_input_copy": (f"inside each step's graph, starting at the {copy_at} phase, into the other input buffer"
+                                     if graphed_e2e[0] is not None else "on a side stream, issued before the step that precedes its use"),
                   "dispatch": ("per-tile ready flags: gate/up and dgrad(down) GEMMs start while the dispatch kernel runs"
                                if blk.moe.ready_flags else "the GEMMs start after the dispatch kernel's exit barrier"),
                   "combine": ("pushed by the down GEMM's epilogue into the source ranks' memory, then a local sum"

@@ -242,12 +242,14 @@ def run(args):
 
     lr = 1e-3
 
-    def step(x):
+    def step(x, before_optimizer=None):
         x.requires_grad_(True)
         w, topk, tpe = route(x)
         y = MoE.apply(x, w, topk, tpe)
         loss = mean_square(y)
         loss.backward()
+        if before_optimizer is not None:
+            before_optimizer()
         with torch.no_grad():
             for n in shapes:
                 fused["sgd"](W[n][rank, :epn], Gd[n][rank, :epn], lr)
@@ -340,14 +342,18 @@ def run(args):
     clocks = sampler.stop() if sampler is not None else {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
     copy_stream = torch.cuda.Stream()
 
-    def fetch(i):
+    def fetch(i, after=None):
         with torch.cuda.stream(copy_stream):
+            if after is not None:
+                copy_stream.wait_event(after)
             x = host[i % 2].to("cuda", non_blocking=True)
             ev = copy_stream.record_event()
         return x, ev
 
-    # same protocol as the main arm: the loss of step i goes to pinned host memory asynchronously
-    # and is read after step i+1 has been queued (the last one after the loop)
+    # same protocol as the main arm: the batch of step i+1 is copied from pinned host memory while the
+    # optimizer of step i runs (a host-to-device copy slows communication kernels it overlaps with; the
+    # optimizer is local work), only the first batch is copied up front; the loss of step i goes to pinned
+    # host memory asynchronously and is read after step i+1 has been queued (the last one after the loop)
     loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
     done = [None, None]
     lv = None
@@ -358,14 +364,17 @@ def run(args):
 
     sync()
     t0 = time.perf_counter()
-    nxt = fetch(0)
+    nxt = [fetch(0)]
     for i in range(args.steps):
-        x, ev = nxt
-        if i + 1 < args.steps:
-            nxt = fetch(i + 1)
+        x, ev = nxt[0]
+
+        def stage(i=i):
+            if i + 1 < args.steps:
+                nxt[0] = fetch(i + 1, after=torch.cuda.current_stream().record_event())
+
         torch.cuda.current_stream().wait_event(ev)
         x.record_stream(torch.cuda.current_stream())
-        loss_host[i % 2].copy_(step(x).reshape(1).float(), non_blocking=True)
+        loss_host[i % 2].copy_(step(x, stage).reshape(1).float(), non_blocking=True)
         done[i % 2] = torch.cuda.current_stream().record_event()
         if i > 0:
             lv = read_loss(i - 1)
@@ -448,6 +457,7 @@ def run(args):
                       "l2": "inputs larger than L2 (multi-GB working set per step)"},
            "notes": {"step": "router + dispatch + grouped GEMM fwd/bwd + combine + reduce_grad + SGD",
                      "launch": "launched from Python", "path": "default",
+                     "e2e_input_copy": "on a side stream, starting when the step before its use reaches the optimizer",
                      "dispatch": "the GEMMs start after the dispatch call returns",
                      "combine": "pulled from the peers' shards after the down GEMM",
                      "comm": "reference moonep.Buffer (unmodified)",

@@ -25,25 +25,52 @@ class GraphedSteps:
     Run a few eager warm-up steps before constructing this object.
     """
 
-    def __init__(self, step_fn: Callable[[torch.Tensor], torch.Tensor], inputs: Sequence[torch.Tensor],
-                 health: Callable[[], None] | None = None):
+    def __init__(self, step_fn: Callable[..., torch.Tensor], inputs: Sequence[torch.Tensor],
+                 health: Callable[[], None] | None = None, host_inputs: Sequence[torch.Tensor] | None = None,
+                 pool=None):
         """``health``: called before every replay; it should raise if an earlier replay recorded a
         device-side failure (e.g. ``lambda: (buf.healthy() or buf.check())``).  Such checks read a
-        flag in host memory, so they cost nothing and do not synchronise."""
+        flag in host memory, so they cost nothing and do not synchronise.
+
+        ``host_inputs`` (pinned host tensors, one per input buffer): the step on ``inputs[i]`` also copies
+        ``host_inputs[i+1]`` into ``inputs[i+1]`` on a side stream inside the same graph, i.e. every replay
+        brings in the batch of the next one (the caller refills the pinned buffer in between and copies the
+        very first batch itself).  ``step_fn`` is then called as ``step_fn(x, stage_next)`` and decides
+        where in the step the copy starts by calling ``stage_next()`` (at the end if it never does): a
+        host-to-device copy slows kernels that use system-scope fences while it runs, so it belongs beside
+        local work (the optimizer, weight-gradient GEMMs), not beside dispatch or combine.
+        ``pool``: memory pool of an earlier ``GraphedSteps`` to share (the two must not replay concurrently)."""
         self.health = health
         self.inputs = list(inputs)
         self.graphs, self.losses, self.host_losses = [], [], []
-        pool = None
-        for x in self.inputs:
+        side = torch.cuda.Stream() if host_inputs is not None else None
+        for i, x in enumerate(self.inputs):
             host = torch.zeros(1, dtype=torch.float32).pin_memory()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool=pool):
-                loss = step_fn(x)
+                if host_inputs is None:
+                    loss = step_fn(x)
+                else:
+                    staged = []
+
+                    def stage_next(i=i, staged=staged):
+                        if staged:
+                            return
+                        staged.append(True)
+                        nxt = (i + 1) % len(self.inputs)
+                        side.wait_stream(torch.cuda.current_stream())
+                        with torch.cuda.stream(side):
+                            self.inputs[nxt].detach().copy_(host_inputs[nxt], non_blocking=True)
+
+                    loss = step_fn(x, stage_next)
+                    stage_next()
+                    torch.cuda.current_stream().wait_stream(side)
                 host.copy_(loss.detach().reshape(1).float(), non_blocking=True)
             pool = g.pool()
             self.graphs.append(g)
             self.losses.append(loss)
             self.host_losses.append(host)
+        self.pool = pool
 
     def __len__(self) -> int:
         return len(self.graphs)

@@ -107,3 +107,61 @@ def test_captured_steps_match_eager_steps(optimizer_in_backward, cuda_device):
     assert l0[0] != l0[2], "the weights must actually be trained (same input, two steps later)"
     for a, b in zip(w0, w1):
         assert torch.equal(a, b)
+
+
+def test_captured_steps_stage_the_next_batch(cuda_device):
+    """``GraphedSteps(host_inputs=...)``: every replay copies the next step's batch from pinned host memory
+    inside its own graph, starting where the step says (here: before the optimizer).  Batches that the host
+    rewrites between replays must arrive, and losses and weights must equal those of eager steps on the
+    same sequence of batches."""
+    from moonep_b200.models.moe_block import MoEBlock, MoEConfig
+    from moonep_b200.ops import grouped_gemm as gg
+    from moonep_b200.utils import GraphedSteps
+    cfg = MoEConfig("t", H=256, Hp=256, K=2, epn=4, shared_experts=1, S=192)
+    g = torch.Generator().manual_seed(6)
+    batches = [(torch.randn(cfg.S, cfg.H, generator=g) * 0.5).to(torch.bfloat16) for _ in range(6)]
+    lr = 1e-2
+
+    def make_step(blk):
+        def step(x, stage_next=None):
+            x.requires_grad_(True)
+            loss = (blk.forward(x).float() ** 2).sum()
+            loss.backward()
+            if stage_next is not None:
+                stage_next()
+            blk.sgd_step(lr)
+            x.grad = None
+            return loss.detach()
+        return step
+
+    out = []
+    for graphed in (False, True):
+        blk = MoEBlock(cfg, num_sms=4, seed=3)
+        step = make_step(blk)
+        for i in range(2):
+            step(batches[i].cuda())                                         # warm-up, eager in both runs
+        losses = []
+        if graphed:
+            host = [batches[0].clone().pin_memory(), batches[1].clone().pin_memory()]
+            dev = [torch.empty_like(batches[0], device="cuda") for _ in range(2)]
+            gs = GraphedSteps(step, dev, host_inputs=host)                  # capture runs no kernel
+            dev[0].detach().copy_(host[0])                                  # the first batch is the caller's
+            for i in range(len(batches)):
+                if i + 1 < len(batches):
+                    host[(i + 1) % 2].copy_(batches[i + 1])                 # the loader refills the pinned buffer
+                gs.replay(i)
+                torch.cuda.synchronize()
+                losses.append(float(gs.host_losses[i % 2][0]))
+                if i + 1 < len(batches):
+                    assert torch.equal(dev[(i + 1) % 2].detach().cpu(), batches[i + 1]), f"batch {i + 1} did not arrive"
+        else:
+            for b in batches:
+                losses.append(float(step(b.cuda())))
+        torch.cuda.synchronize()
+        blk.buf.check(); gg.check_status()
+        out.append((losses, [blk.pools.local_weight(n).clone() for n in ("gate", "up", "down")]))
+        blk.destroy()
+    (l0, w0), (l1, w1) = out
+    assert all(abs(a - b) <= 1e-3 * abs(a) + 1e-6 for a, b in zip(l0, l1)), (l0, l1)
+    for a, b in zip(w0, w1):
+        assert torch.equal(a, b)
