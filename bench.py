@@ -35,9 +35,11 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--no-sweep", action="store_true")
-    ap.add_argument("--optimizer-in-backward", action="store_true",
-                    help="update each projection of the experts inside the backward pass, on a side stream, as soon "
-                         "as its gradient is final (measured slower than updating after the backward pass)")
+    ap.add_argument("--optimizer", default=os.environ.get("MOONEP_BENCH_OPTIMIZER", "epilogue"), choices=["epilogue", "backward", "after"],
+                    help="where the experts' SGD update runs: in the epilogue of the weight-gradient GEMMs (experts without "
+                         "replicas; replicated experts through a stored gradient that is reduced first), as stand-alone "
+                         "kernels inside the backward pass, or after the backward pass")
+    ap.add_argument("--optimizer-in-backward", action="store_true", help="same as --optimizer backward")
     ap.add_argument("--maxvio", type=float, default=MAXVIO_MAIN)
     ap.add_argument("--verify-plans", action="store_true",
                     help="instead of the benchmark: identical routing through this package's and the reference's "
@@ -176,15 +178,27 @@ def run_ours(args):
     dev_batches = [b.cuda() for b in host_batches]
     lr = 1e-3
     if args.optimizer_in_backward:
-        blk.fuse_optimizer(lr)      # each projection's SGD runs beside the remaining backward GEMMs
+        args.optimizer = "backward"
+
+    def place_optimizer(b):
+        if args.optimizer != "after":
+            b.fuse_optimizer(lr, in_epilogue=args.optimizer == "epilogue")
 
     # where in a captured step the host-to-device copy of the NEXT step's batch starts (end-to-end run)
-    copy_at = os.environ.get("MOONEP_BENCH_COPY_AT", "optimizer")
+    # ("quiet": the stretch of the backward pass without communication kernels, see ExpertParallelMoE.on_comm_quiet;
+    # "optimizer": before the stand-alone optimizer kernels, which is where that stretch is when they run after the
+    # backward pass)
+    copy_at = os.environ.get("MOONEP_BENCH_COPY_AT", "")
+
+    place_optimizer(blk)
+    if not copy_at:
+        copy_at = "optimizer" if args.optimizer == "after" else "quiet"
 
     def step(x, stage_next=None):
         x.requires_grad_(True)
         if stage_next is not None and copy_at == "start":
             stage_next()
+        blk.moe.on_comm_quiet = stage_next if copy_at == "quiet" else None
         y = blk.forward(x)
         loss = mean_square(y)
         if stage_next is not None and copy_at == "backward":
@@ -193,6 +207,7 @@ def run_ours(args):
         if stage_next is not None and copy_at == "optimizer":
             stage_next()
         blk.sgd_step(lr)
+        blk.moe.on_comm_quiet = None
         x.grad = None
         return loss.detach()
 
@@ -308,8 +323,7 @@ def run_ours(args):
         os.environ.update(MOONEP_PUSH_COMBINE="0", MOONEP_OVERLAP_BACKWARD="0", MOONEP_DEFER_LAST_REDUCTION="0",
                           MOONEP_PDL="0", MOONEP_READY_FLAGS="0")
         blk = MoEBlock(cfg, world, rank, num_sms=32, seed=0)
-        if args.optimizer_in_backward:
-            blk.fuse_optimizer(lr)
+        place_optimizer(blk)
     scale, realised, graph_note = state["scale"], state["realised"], state["graph_note"]
 
     ms, launches = timed_steps(args.steps)
@@ -491,8 +505,12 @@ def run_ours(args):
                    "num_sms": 32, "maxvio_target": args.maxvio, "maxvio": round(realised, 3),
                    "l2": "inputs larger than L2 (multi-GB working set per step)"},
         "notes": {"step": "router + dispatch + grouped GEMM fwd/bwd + combine + reduce_grad + SGD"
-                          + (" (each projection's SGD is launched inside the backward pass, on a side stream, once its "
-                             "gradient is final)" if args.optimizer_in_backward else ""),
+                          + {"after": "",
+                             "backward": " (each projection's SGD is launched inside the backward pass, on a side stream, "
+                                         "once its gradient is final)",
+                             "epilogue": " (SGD in the epilogue of the weight-gradient GEMMs for experts without replicas, no "
+                                         "fp32 gradient is stored for those; replicated experts: stored gradient, cross-rank "
+                                         "reduction, stand-alone SGD inside the backward pass)"}[args.optimizer],
                   "launch": graph_note, "path": path_note,
                   "e2e_input_copy": (f"inside each step's graph, starting at the {copy_at} phase, into the other input buffer"
                                      if graphed_e2e[0] is not None else "on a side stream, issued before the step that precedes its use"),

@@ -52,6 +52,14 @@ struct GemmArgs {
   int32_t group_first;
   int32_t sched_ctas;          // dynamic order: CTAs over ALL launches that draw from `sched` (several launches of
                                // one GEMM may share a counter); 0 = just this launch
+  // WGRAD (CTA-pair kernel), optional optimizer in the epilogue: for a group g with upd_mask[g] != 0 the
+  // gradient tile is not written to `out`; the bf16 weights upd_w[g] (same [G, M_w, N] layout) are updated in
+  // place instead, w -= upd_lr * dW, with the arithmetic of the stand-alone SGD kernel. Groups with
+  // upd_mask[g] == 0 (e.g. experts whose gradient still has to be reduced across ranks) are written as usual.
+  void* upd_w;
+  const int32_t* upd_mask;
+  float upd_lr;
+  int32_t reserved1;
 };
 
 }  // namespace mep

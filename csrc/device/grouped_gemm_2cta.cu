@@ -197,10 +197,26 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       if (t < 0) break;
       get_tile(t, ti);
       const int orow0 = ti.g * args.M_w + ti.m0 + (int)cr * 128 + q * 32;
-      if (ti.kblocks == 0) {           // empty group that must end with a zero gradient
-        float* orow = (float*)args.out + (size_t)(orow0 + lane) * args.N + ti.n0 + half * 128;
-        for (int j = 0; j < 32; ++j) reinterpret_cast<float4*>(orow)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      // optimizer in the epilogue: this group's weights are updated in place and no gradient is written
+      const bool upd = args.upd_mask != nullptr && args.upd_mask[ti.g] != 0;
+      if (ti.kblocks == 0) {           // empty group that must end with a zero gradient (nothing to update)
+        if (!upd) {
+          float* orow = (float*)args.out + (size_t)(orow0 + lane) * args.N + ti.n0 + half * 128;
+          for (int j = 0; j < 32; ++j) reinterpret_cast<float4*>(orow)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         --tcnt; continue;
+      }
+      // A chunk is 32 rows x 32 columns. The accumulator arrives with lane = row; the weights are read and
+      // written with four lanes per row instead (16 bytes each, eight rows per instruction: whole sectors),
+      // so the chunk takes the same trip through the warp's shared-memory slab as a stored gradient does.
+      const __nv_bfloat16* wbase = upd ? (const __nv_bfloat16*)args.upd_w + (size_t)orow0 * args.N + ti.n0 + (half * 4) * 32 : nullptr;
+      auto wptr = [&](int i, int k) {
+        return const_cast<__nv_bfloat16*>(wbase) + (size_t)((lane >> 2) + 8 * k) * args.N + i * 32 + (lane & 3) * 8;
+      };
+      int4 wv[2][4];
+      if (upd) {                       // first chunk's weights: in flight while the tile's MMAs finish
+#pragma unroll
+        for (int k = 0; k < 4; ++k) wv[0][k] = *reinterpret_cast<const int4*>(wptr(0, k));
       }
       const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
       int ok = 1;
@@ -218,11 +234,44 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       for (int i = 0; i < 4; ++i, ++chunk_no) {
         const int c = half * 4 + i;
         tc::tmem_ld_wait();
-        if (i + 1 < 4) tc::tmem_ld32(taddr + (c + 1) * 32, r[(i + 1) & 1]);
-        else {
+        if (i + 1 < 4) {
+          tc::tmem_ld32(taddr + (c + 1) * 32, r[(i + 1) & 1]);
+          if (upd) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) wv[(i + 1) & 1][k] = *reinterpret_cast<const int4*>(wptr(i + 1, k));
+          }
+        } else {
           tc::fence_before_sync();
           __syncwarp();
           if (lane == 0) remote_arrive(tempty_leader[acc]);
+        }
+        if (upd) {
+          const uint32_t ubuf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;
+          if (lane == 0) bulk_wait_read<0>();      // a gradient stored from this slab earlier has left it
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            tc::st_shared_v4(ubuf + lane * 128 + ((j ^ (lane & 7)) << 4), r[i & 1][4 * j], r[i & 1][4 * j + 1], r[i & 1][4 * j + 2], r[i & 1][4 * j + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int R = (lane >> 2) + 8 * k, p2 = (lane & 3) * 2;
+            const int4 g0 = tc::ld_shared_v4(ubuf + R * 128 + ((p2 ^ (R & 7)) << 4));
+            const int4 g1 = tc::ld_shared_v4(ubuf + R * 128 + (((p2 + 1) ^ (R & 7)) << 4));
+            const float gg[8] = {__int_as_float(g0.x), __int_as_float(g0.y), __int_as_float(g0.z), __int_as_float(g0.w),
+                                 __int_as_float(g1.x), __int_as_float(g1.y), __int_as_float(g1.z), __int_as_float(g1.w)};
+            int4 x = wv[i & 1][k];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float2 f = __bfloat1622float2(h[e]);
+              f.x = fmaf(-args.upd_lr, gg[2 * e], f.x);           // as in sgd_kernel
+              f.y = fmaf(-args.upd_lr, gg[2 * e + 1], f.y);
+              h[e] = __floats2bfloat162_rn(f.x, f.y);
+            }
+            *reinterpret_cast<int4*>(wptr(i, k)) = x;
+          }
+          continue;
         }
         const uint32_t buf = stg + (uint32_t)(chunk_no & 1) * kSlabBytes;
         if (lane == 0) bulk_wait_read<1>();

@@ -66,7 +66,29 @@ __global__ void __launch_bounds__(256) sgd_kernel(__nv_bfloat16* __restrict__ p,
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float2 f = __bfloat1622float2(h[k]);
-      f.x -= lr * gg[2 * k]; f.y -= lr * gg[2 * k + 1];
+      f.x = fmaf(-lr, gg[2 * k], f.x); f.y = fmaf(-lr, gg[2 * k + 1], f.y);      // the form wgrad's fused update uses
+      h[k] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    *reinterpret_cast<int4*>(p + i * 8) = x;
+  }
+}
+
+// The same update for the groups of a [G, n] tensor whose mask word is zero (`want` = 0) or non-zero (1):
+// used for the experts that the weight-gradient GEMM did not already update in its epilogue.
+__global__ void __launch_bounds__(256) sgd_groups_kernel(__nv_bfloat16* __restrict__ p, const float* __restrict__ g, float lr,
+                                                         int64_t n8, const int32_t* __restrict__ mask, int want) {
+  const int grp = blockIdx.y;
+  if ((mask[grp] != 0) != (want != 0)) return;
+  p += (int64_t)grp * n8 * 8; g += (int64_t)grp * n8 * 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    int4 x = *reinterpret_cast<const int4*>(p + i * 8);
+    const float4 g0 = *reinterpret_cast<const float4*>(g + i * 8), g1 = *reinterpret_cast<const float4*>(g + i * 8 + 4);
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 f = __bfloat1622float2(h[k]);
+      f.x = fmaf(-lr, gg[2 * k], f.x); f.y = fmaf(-lr, gg[2 * k + 1], f.y);      // the form wgrad's fused update uses
       h[k] = __floats2bfloat162_rn(f.x, f.y);
     }
     *reinterpret_cast<int4*>(p + i * 8) = x;
@@ -85,4 +107,11 @@ extern "C" int mep_swiglu_bwd(const void* dA, const void* gu, const float* w, vo
 extern "C" int mep_sgd_step(void* p, const float* g, float lr, int64_t n, int num_blocks, cudaStream_t stream) {
   MEP_REQUIRE(n % 8 == 0, "sgd_step: element count must be a multiple of 8");
   return mep::launch_plain(mep::sgd_kernel, dim3(num_blocks), dim3(256), 0, stream, (__nv_bfloat16*)p, g, lr, n / 8);
+}
+
+extern "C" int mep_sgd_step_groups(void* p, const float* g, float lr, int64_t n_per_group, int G, const int32_t* mask, int want,
+                                   int num_blocks, cudaStream_t stream) {
+  MEP_REQUIRE(n_per_group % 8 == 0 && G >= 1 && G <= 65535, "sgd_step_groups: %d groups of %lld elements", G, (long long)n_per_group);
+  return mep::launch_plain(mep::sgd_groups_kernel, dim3(num_blocks, G), dim3(256), 0, stream, (__nv_bfloat16*)p, g, lr,
+                           n_per_group / 8, mask, want);
 }

@@ -34,7 +34,8 @@ def sources():
 
 
 def headers():
-    return list(CSRC.glob("*.h")) + list((CSRC / "host").glob("*.h")) + list((CSRC / "device").glob("*.cuh"))
+    return (list(CSRC.glob("*.h")) + list((CSRC / "host").glob("*.h")) + list((CSRC / "device").glob("*.cuh"))
+            + list((CSRC / "device").glob("*.h")))
 
 
 def nvcc_path() -> str | None:

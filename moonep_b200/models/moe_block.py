@@ -112,15 +112,25 @@ class MoEBlock:
             ps += self.shared
         return ps
 
-    def fuse_optimizer(self, lr: float | None):
+    def fuse_optimizer(self, lr: float | None, in_epilogue: bool = False):
         """Apply the experts' SGD update inside the backward pass: each projection is updated on a
         side stream as soon as its gradient is final (``ExpertParallelMoE.on_grad_ready``), beside
-        the GEMMs that are still running.  ``None`` switches back to updating in ``sgd_step``."""
+        the GEMMs that are still running.  ``None`` switches back to updating in ``sgd_step``.
+
+        ``in_epilogue``: the experts are updated by their weight-gradient GEMMs themselves
+        (``wgrad(update=...)``: no fp32 gradient is written or read back for an expert whose gradient is
+        complete on this rank); the side-stream kernel then only covers the experts that have replicas on
+        other ranks, whose gradients are reduced first.  Same arithmetic, same result."""
         self._fused_lr = lr
+        moe = self.moe
+        moe.epilogue_lr = lr if (in_epilogue and lr is not None) else None
         if lr is None:
-            self.moe.on_grad_ready = None
+            moe.on_grad_ready = None
+        elif moe.epilogue_lr is None:
+            moe.on_grad_ready = lambda n: gg.sgd_step(self.pools.local_weight(n), self.pools.local_grad(n), lr)
         else:
-            self.moe.on_grad_ready = lambda n: gg.sgd_step(self.pools.local_weight(n), self.pools.local_grad(n), lr)
+            moe.on_grad_ready = lambda n: gg.sgd_step_groups(self.pools.local_weight(n), self.pools.local_grad(n), lr,
+                                                             moe._upd_mask, want=False)
 
     def sgd_step(self, lr: float):
         if self.moe.on_grad_ready is None:

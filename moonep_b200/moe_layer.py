@@ -72,6 +72,10 @@ class ExpertParallelMoE:
         self._total_sms = torch.cuda.get_device_properties(dev).multi_processor_count
         self._comm_sms = min(g.num_sms & ~1, self._total_sms - 2)
         self.on_grad_ready = None       # callable(name) -> None, see backward()
+        # callable() -> None, called in backward() on the compute stream where a stretch without communication
+        # kernels begins (after dgrad(down): SwiGLU backward and two weight-gradient GEMMs follow) -- the
+        # place to start work that disturbs them, such as a host-to-device copy of the next batch
+        self.on_comm_quiet = None
         self.grads_pending = None       # (projection, event) of a reduction still running after backward()
         # opt-in: backward() may return while the reduction of ``up`` still runs on the comm stream;
         # the caller then calls wait_grads() before it reads those gradients or uses the Buffer again
@@ -85,6 +89,23 @@ class ExpertParallelMoE:
         self._x = torch.zeros(g.NvS, g.H, **bf)
         self._w = torch.zeros(g.NvS, dtype=torch.float32, device=dev)
         self.accumulate_grads = False
+        # optimizer in the weight-gradient GEMM's epilogue (see ``backward``): learning rate, or None
+        self.epilogue_lr = None
+        i32 = dict(dtype=torch.int32, device=dev)
+        self._upd_mask = torch.zeros(2 * g.epn, **i32)
+        self._upd_hit = torch.zeros(g.epn + 1, **i32)
+        self._upd_ones = torch.ones(g.R * g.epn, **i32)
+
+    def _update_mask(self, plan):
+        """int32 ``[2*epn]``: 1 for the local experts whose gradient is complete on this rank (no replica of
+        them is in any rank's slots under ``plan``), 0 for replicated local experts and for the slots."""
+        epn = self.geo.epn
+        idx = plan.experts_to_copy.reshape(-1).long() - self.buf.rank * epn
+        idx = torch.where((idx >= 0) & (idx < epn), idx, torch.full_like(idx, epn))
+        self._upd_hit.zero_()
+        self._upd_hit.scatter_(0, idx, self._upd_ones)
+        self._upd_mask[:epn] = 1 - self._upd_hit[:epn]
+        return self._upd_mask
 
     # weights / grads as [2*epn, in, out]
     def _W(self, n):
@@ -204,7 +225,12 @@ class ExpertParallelMoE:
         exposed.  A GEMM that shares the GPU with a communication kernel is split over two launches
         with a common ticket counter (``_beside_comm``).
         ``on_grad_ready(name)``, if set, is called on a side stream as soon as the local gradient of
-        projection ``name`` is final and its weights are no longer read (optimizer in backward)."""
+        projection ``name`` is final and its weights are no longer read (optimizer in backward).
+        ``epilogue_lr``, if set: the weight-gradient GEMMs apply ``W -= lr * dW`` in their epilogue for
+        every local expert without a replica elsewhere and write no gradient for it (``_upd_mask``);
+        each of them runs after the last GEMM that reads its weights (wgrad(gate) moves behind
+        dgrad(gate/up), see below).  Replicated experts keep the stored-gradient path -- their gradients
+        are reduced across ranks first -- and ``on_grad_ready`` is expected to update exactly those."""
         buf, g, epn, Hp = self.buf, self.geo, self.geo.epn, self.Hp
         acc, ov, multi = self.accumulate_grads, self.overlap_backward, self.geo.R > 1
         self._join_deferred()
@@ -239,32 +265,59 @@ class ExpertParallelMoE:
         if ev_pf is not None:
             main.wait_event(ev_pf)      # dgrad(gate/up) further down reads the other two projections' slots
         dw_view = buf.router_weight_buffer_view
+        if self.on_comm_quiet is not None:
+            self.on_comm_quiet()
         gg.swiglu_bwd(self._dA, ctx.gu, ctx.w_nvs, self._dgu, dw_view, ctx.cu)
-        gg.wgrad(ctx.act, dy, ctx.cu, self._dW("down"), accumulate=acc, zero_empty_below=epn)
+        upd = lambda n: None      # noqa: E731
+        if self.epilogue_lr is not None:
+            assert not acc, "the optimizer cannot sit in the GEMM epilogue while gradients are accumulated"
+            mask, lr_e = self._update_mask(ctx.plan), self.epilogue_lr
+            upd = lambda n: (self._W(n), lr_e, mask)      # noqa: E731
+        gg.wgrad(ctx.act, dy, ctx.cu, self._dW("down"), accumulate=acc, zero_empty_below=epn, update=upd("down"))
         if not multi:
             self._optimizer("down", main)
-        gg.wgrad(ctx.x, self._dgu[:, :Hp], ctx.cu, self._dW("gate"), accumulate=acc, zero_empty_below=epn)
+        dW_gate, dG = self._dW("gate"), self._dgu[:, :Hp]
+        # With the optimizer in the epilogues, wgrad(gate) must come after dgrad(gate/up), which reads the gate
+        # weights: the order becomes  reduce(down) | dgrad(gate/up),  combine | wgrad(gate),  reduce(gate) |
+        # wgrad(up),  reduce(up)  -- every communication kernel still has a GEMM to run beside, except the last.
+        gate_late = self.epilogue_lr is not None
+        if not gate_late:
+            gg.wgrad(ctx.x, dG, ctx.cu, dW_gate, accumulate=acc, zero_empty_below=epn)
         ev_red = None
         if multi:
             # the weight-gradient GEMMs overwrite the slots they use, so consumed slots need no zeroing
             # unless gradients are accumulated over several backward passes
-            ev_red = buf.reduce_grad_subset(ctx.plan, [pair("down"), pair("gate")], async_finish=ov, clear_slots=acc)
+            first = [pair("down")] if gate_late else [pair("down"), pair("gate")]
+            ev_red = buf.reduce_grad_subset(ctx.plan, first, async_finish=ov, clear_slots=acc)
             self._optimizer("down", ev_red if ov else main)
         if ov and multi:
             ev = self._beside_comm(lambda n, tk: gg.dgrad_gate_up(self._dgu, Wg, Wu, ctx.cu, shard, num_ctas=n, ticket=tk))
             main.wait_event(ev)
         else:
             gg.dgrad_gate_up(self._dgu, Wg, Wu, ctx.cu, shard)
-        self._optimizer("gate", main, *([ev_red] if ev_red is not None else []))
+        if not gate_late:
+            self._optimizer("gate", main, *([ev_red] if ev_red is not None else []))
         grad_hidden, grad_w, ev_comb = buf.combine(plan=ctx.plan, hidden_nvsh=shard, route_weights_nvs=dw_view,
                                                    async_finish=ov, zero_copy=True, router_weights_zero_copy=True)
+        if gate_late:
+            if ov:
+                ev = self._beside_comm(lambda n, tk: gg.wgrad(ctx.x, dG, ctx.cu, dW_gate, accumulate=acc, zero_empty_below=epn,
+                                                              num_ctas=n, ticket=tk, update=upd("gate")))
+                main.wait_event(ev)   # also covers the combine, which precedes that launch on the comm stream
+            else:
+                gg.wgrad(ctx.x, dG, ctx.cu, dW_gate, accumulate=acc, zero_empty_below=epn, update=upd("gate"))
+            ev_red_g = None
+            if multi:
+                ev_red_g = buf.reduce_grad_subset(ctx.plan, [pair("gate")], async_finish=ov, clear_slots=acc)
         dW_up, dU = self._dW("up"), self._dgu[:, Hp:]
-        if ov:
+        if ov and (multi or not gate_late):      # a communication kernel was just queued on the comm stream
             ev = self._beside_comm(lambda n, tk: gg.wgrad(ctx.x, dU, ctx.cu, dW_up, accumulate=acc, zero_empty_below=epn,
-                                                          num_ctas=n, ticket=tk))
+                                                          num_ctas=n, ticket=tk, update=upd("up")))
             main.wait_event(ev)       # also covers the combine, which precedes that launch on the comm stream
         else:
-            gg.wgrad(ctx.x, dU, ctx.cu, dW_up, accumulate=acc, zero_empty_below=epn)
+            gg.wgrad(ctx.x, dU, ctx.cu, dW_up, accumulate=acc, zero_empty_below=epn, update=upd("up"))
+        if gate_late:
+            self._optimizer("gate", main, *([ev_red_g] if ev_red_g is not None else []))
         self.grads_pending = None
         if multi:
             # the last reduction has nothing of the backward pass left to hide behind: with

@@ -35,7 +35,8 @@ class GemmArgs(C.Structure):
                 ("push_wsrc", C.c_void_p), ("push_stride", C.c_uint64),
                 ("tile_done", C.c_void_p), ("tile_epoch", C.c_void_p), ("status_host", C.c_void_p),
                 ("group_flags", C.c_void_p), ("group_epoch", C.c_void_p),
-                ("push_rows", C.c_int32), ("push_ranks", C.c_int32), ("group_first", C.c_int32), ("sched_ctas", C.c_int32)]
+                ("push_rows", C.c_int32), ("push_ranks", C.c_int32), ("group_first", C.c_int32), ("sched_ctas", C.c_int32),
+                ("upd_w", C.c_void_p), ("upd_mask", C.c_void_p), ("upd_lr", C.c_float), ("reserved1", C.c_int32)]
 
 
 class PushTarget:
@@ -234,11 +235,18 @@ def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None, dynamic=Fals
             push=push, push_w=push_w)
 
 
-def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num_ctas=None, dynamic=False, ticket=None):
+def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num_ctas=None, dynamic=False, ticket=None,
+          update=None):
     """``out[g] (+)= x_g^T dy_g`` in fp32; ``out [G, in, out_dim]``.  ``dy`` may be a column slice
     of a wider matrix (row pitch = ``dy.stride(0)``).  Groups without rows are left untouched,
     except that with ``accumulate=False`` empty groups ``g < zero_empty_below`` are zeroed (local
-    experts that received no token must end with a zero gradient)."""
+    experts that received no token must end with a zero gradient).
+
+    ``update=(weights, lr, mask)``: optimizer in the epilogue.  For every group with ``mask[g] != 0``
+    (int32 ``[G]`` on the device) the gradient is not written; ``weights[g]`` (bf16, same shape as ``out``)
+    becomes ``weights[g] - lr * dW`` instead, bit for bit what ``sgd_step`` computes from a stored gradient.
+    Groups with ``mask[g] == 0`` are written to ``out`` as usual.  Needs weight shapes that are multiples
+    of 256 (the CTA-pair kernel)."""
     G, M, N = out.shape
     assert out.dtype == torch.float32 and out.is_contiguous()
     assert x.shape[1] == M and dy.shape[1] == N and M % 128 == 0 and N % 256 == 0
@@ -261,11 +269,17 @@ def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num
             args.sched, args.sched_ctas = ticket.ptr, ticket.total_ctas
         else:
             args.sched = _sched(x.device, dynamic)
+        if update is not None:
+            w, lr, mask = update
+            assert w.dtype == torch.bfloat16 and tuple(w.shape) == tuple(out.shape) and w.is_contiguous()
+            assert mask.dtype == torch.int32 and mask.numel() == G and mask.is_cuda
+            args.upd_w, args.upd_mask, args.upd_lr = w.data_ptr(), mask.data_ptr(), float(lr)
         rc = lib.mep_grouped_wgrad_2cta(C.c_void_p(x.data_ptr()), C.c_int64(x.shape[0]), C.c_int64(x.stride(0)),
                                         C.c_void_p(dy.data_ptr()), C.c_int64(dy.stride(0)), C.byref(args),
                                         num_ctas or _num_sms(x.device), _native.cur_stream())
         _native.check(rc, "grouped_wgrad_2cta")
         return
+    assert update is None, "wgrad(update=...) needs weight shapes that are multiples of 256"
     _launch(WGRAD, x, dy, None, cu, N=N, M_w=M, out=out, accumulate=accumulate, zero_empty_below=zero_empty_below,
             b_rows=dy.shape[0], b_cols=N, b_ld=dy.stride(0), groups=groups, num_ctas=num_ctas, dynamic=dynamic, ticket=ticket)
 
@@ -278,6 +292,18 @@ def swiglu_bwd(dA, gu, w, dgu, dw, cu, num_blocks=None):
     _native.check(lib.mep_swiglu_bwd(C.c_void_p(dA.data_ptr()), C.c_void_p(gu.data_ptr()), C.c_void_p(_native.ptr(w)),
                                      C.c_void_p(dgu.data_ptr()), C.c_void_p(_native.ptr(dw)), C.c_void_p(cu.data_ptr()),
                                      cu.numel(), Hp, nb, _native.cur_stream()), "swiglu_bwd")
+
+
+def sgd_step_groups(p, g, lr, mask, want: bool, num_blocks=None):
+    """``sgd_step`` for the groups ``i`` of ``p [G, ...]`` with ``(mask[i] != 0) == want`` only (``mask``: int32
+    ``[>= G]`` on the device): the complement of what ``wgrad(update=...)`` has already updated."""
+    lib = _native.load()
+    assert p.dtype == torch.bfloat16 and g.dtype == torch.float32 and p.shape == g.shape
+    assert p.is_contiguous() and g.is_contiguous() and mask.dtype == torch.int32 and mask.numel() >= p.shape[0]
+    nb = num_blocks or 2 * _num_sms(p.device)
+    _native.check(lib.mep_sgd_step_groups(C.c_void_p(p.data_ptr()), C.c_void_p(g.data_ptr()), C.c_float(lr),
+                                          C.c_int64(p[0].numel()), p.shape[0], C.c_void_p(mask.data_ptr()), 1 if want else 0,
+                                          nb, _native.cur_stream()), "sgd_step_groups")
 
 
 def sgd_step(p, g, lr, num_blocks=None):

@@ -133,6 +133,75 @@ def shared_slots_scenario(rank, R, dev):
     dist.barrier()
 
 
+def epilogue_optimizer_scenario(rank, R, dev):
+    """Two training steps with the SGD update inside the weight-gradient GEMMs' epilogue (experts without
+    replicas) plus the stored-gradient path for replicated experts, against the same two steps
+    with the stand-alone optimizer after the backward pass: the weights must come out bit for bit equal."""
+    S, H, Hp, K, epn, pad, lr = 256, 256, 256, 4, 4, 128, 0.5
+    E = R * epn
+    topk = routing.lognormal_topk(S, K, E, R, 1.2, 3, rank)[0].to(dev)
+    tpe = torch.bincount(topk.flatten().long(), minlength=E).to(torch.int32)
+    g = torch.Generator(device=dev).manual_seed(300 + rank)
+    x0 = (torch.randn(S, H, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    w0 = torch.rand(S, K, device=dev, generator=g) + 0.1
+    w0 = (w0 / w0.sum(dim=1, keepdim=True)).contiguous()
+    gy = (torch.randn(S, H, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+    init = {n: (torch.randn(epn, *shp, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+            for n, shp in (("gate", (H, Hp)), ("up", (H, Hp)), ("down", (Hp, H)))}
+    final, fused_any = [], 0
+    for in_epilogue in (False, True):
+        buf = Buffer(S, H, K, E, R, num_sms=8, token_padding=pad, push_combine=True)
+        pools = ExpertPools(epn, (H, Hp), (H, Hp), (Hp, H), with_grads=True)
+        for n in init:
+            pools.local_weight(n).copy_(init[n])
+            pools.compute_grad(n).zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        layer = ExpertParallelMoE(buf, pools, overlap_backward=True, ready_flags=True)
+        if in_epilogue:
+            layer.epilogue_lr = lr
+
+            def rest(n, layer=layer, pools=pools):
+                gg.sgd_step_groups(pools.local_weight(n), pools.local_grad(n), lr, layer._upd_mask, want=False)
+            layer.on_grad_ready = rest
+        for rep in range(2):
+            x = x0.clone().requires_grad_(True)
+            w = w0.clone().requires_grad_(True)
+            y = moe_apply(layer, x, w, topk, tpe)
+            y.backward(gy)
+            layer.wait_grads()
+            if not in_epilogue:
+                for n in init:
+                    gg.sgd_step(pools.local_weight(n), pools.local_grad(n), lr)
+            torch.cuda.synchronize()
+            dist.barrier()          # every owner has updated before anyone prefetches its experts again
+        try:
+            buf.check()
+            gg.check_status()
+        except Exception as exc:      # noqa: BLE001
+            ERRORS.append(f"epilogue optimizer ({in_epilogue}): {type(exc).__name__}: {exc}")
+        if in_epilogue:
+            fused_any = int(layer._upd_mask[:epn].sum())
+        final.append({n: pools.local_weight(n).clone() for n in init})
+        torch.cuda.synchronize()
+        dist.barrier()
+        pools.destroy()
+        buf.destroy()
+        dist.barrier()
+    for n in init:
+        chk(not torch.equal(final[0][n], init[n]), f"epilogue optimizer: {n} was not trained")
+        chk(torch.equal(final[0][n], final[1][n]),
+            f"epilogue optimizer: {n} differs from the stand-alone optimizer ({int((final[0][n] != final[1][n]).sum())} elements)")
+    tot = torch.tensor([fused_any, epn - fused_any], device=dev)
+    dist.all_reduce(tot)
+    chk(int(tot[0]) > 0, "epilogue optimizer: no expert took the fused path")
+    chk(int(tot[1]) > 0 or R == 1, "epilogue optimizer: no expert took the stored-gradient path")
+    ok = agree("epilogue optimizer")
+    if rank == 0:
+        print(f"[dist_layer] optimizer in the weight-gradient epilogue ({int(tot[0])} experts fused, {int(tot[1])} reduced first): "
+              f"{'ok' if ok else 'FAILED'}", flush=True)
+
+
 def main():
     dist.init_process_group("nccl")
     rank, R = dist.get_rank(), dist.get_world_size()
@@ -200,6 +269,8 @@ def main():
             break           # a device-side wait ran out: later variants would only repeat it
     if not ERRORS:
         shared_slots_scenario(rank, R, dev)
+    if not ERRORS:
+        epilogue_optimizer_scenario(rank, R, dev)
     if ERRORS:
         for e in ERRORS[:24]:
             print(f"[dist_layer] rank {rank}: {e}", flush=True)

@@ -136,6 +136,51 @@ def test_sgd(cuda_device):
     assert (diff != 0).float().mean() < 0.01
 
 
+@pytest.mark.parametrize("tile_order", ["static", "dynamic"])
+def test_wgrad_with_the_optimizer_in_its_epilogue(tile_order, cuda_device, monkeypatch):
+    """``wgrad(update=(W, lr, mask))``: groups with a non-zero mask word get ``W -= lr * dW`` and no gradient
+    (bit for bit what wgrad + sgd_step give), the others get their gradient and keep their weights; the
+    masked stand-alone update covers exactly the complement.  fp32 reference for the gradient itself."""
+    from moonep_b200.ops import grouped_gemm as gg
+    monkeypatch.setenv("MOONEP_GEMM_DYNAMIC", "1" if tile_order == "dynamic" else "0")
+    rpg = [256, 128, 0, 384, 128, 0]
+    G, H, Hp, lr = len(rpg), 512, 256, 0.05
+    cu, tot, rows, x, g = _setup(G, rpg, H, Hp, seed=4)
+    dy = (torch.randn(rows, Hp, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    W0 = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    mask = torch.tensor([1, 0, 1, 1, 0, 0], dtype=torch.int32, device="cuda")
+    # reference: plain wgrad, then the stand-alone optimizer on the masked groups
+    dW_ref = torch.full((G, H, Hp), 7.0, device="cuda")
+    gg.wgrad(x, dy, cu, dW_ref, accumulate=False, zero_empty_below=G)
+    W_ref = W0.clone()
+    gg.sgd_step_groups(W_ref, dW_ref, lr, mask, want=True)
+    # fused
+    W = W0.clone()
+    dW = torch.full((G, H, Hp), 7.0, device="cuda")
+    gg.wgrad(x, dy, cu, dW, accumulate=False, zero_empty_below=G, update=(W, lr, mask))
+    torch.cuda.synchronize()
+    gg.check_status()
+    for gi, a, b in _group_slices(rpg):
+        if int(mask[gi]):
+            assert torch.equal(W[gi], W_ref[gi]), f"group {gi}: fused update differs from wgrad + sgd"
+            assert (dW[gi] == 7.0).all(), f"group {gi}: an updated group must not write its gradient"
+            if a == b:
+                assert torch.equal(W[gi], W0[gi]), "an empty group must keep its weights"
+            else:
+                assert not torch.equal(W[gi], W0[gi])
+                ref = (W0[gi].float() - lr * (x[a:b].float().T @ dy[a:b].float()))
+                assert _relerr(W[gi], ref) < 5e-3
+        else:
+            assert torch.equal(W[gi], W0[gi]), f"group {gi}: weights of an unmasked group changed"
+            assert torch.equal(dW[gi], dW_ref[gi]), f"group {gi}: gradient of an unmasked group differs"
+    # the complement through the stand-alone kernel: afterwards every group is updated exactly once
+    gg.sgd_step_groups(W, dW, lr, mask, want=False)
+    W_all = W0.clone()
+    gg.sgd_step(W_all, dW_ref, lr)
+    torch.cuda.synchronize()
+    assert torch.equal(W, W_all)
+
+
 @pytest.mark.parametrize("pair_kernels", [False, True], ids=["1cta", "cta_pairs"])
 def test_two_launches_share_one_ticket_counter(pair_kernels, cuda_device, monkeypatch):
     """One GEMM issued as two launches on two streams with a common ticket counter: every tile is

@@ -165,3 +165,32 @@ def test_captured_steps_stage_the_next_batch(cuda_device):
     assert all(abs(a - b) <= 1e-3 * abs(a) + 1e-6 for a, b in zip(l0, l1)), (l0, l1)
     for a, b in zip(w0, w1):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("graphed", [False, True], ids=["eager", "captured"])
+def test_optimizer_in_the_wgrad_epilogue_matches_the_stand_alone_optimizer(graphed, cuda_device):
+    """``fuse_optimizer(lr, in_epilogue=True)``: the experts are updated by their weight-gradient GEMMs
+    (wgrad(gate) moves behind dgrad(gate/up) for that).  Losses and weights must equal those of
+    the same steps with the optimizer after the backward pass, bit for bit."""
+    from moonep_b200.models.moe_block import MoEBlock, MoEConfig
+    from moonep_b200.ops import grouped_gemm as gg
+    cfg = MoEConfig("t", H=256, Hp=256, K=2, epn=4, shared_experts=1, S=192)
+    g = torch.Generator(device="cuda").manual_seed(8)
+    xs = [(torch.randn(cfg.S, cfg.H, device="cuda", generator=g) * 0.5).to(torch.bfloat16) for _ in range(2)]
+    out = []
+    for in_epilogue in (False, True):
+        blk = MoEBlock(cfg, num_sms=4, seed=3)
+        if in_epilogue:
+            blk.fuse_optimizer(1e-2, in_epilogue=True)
+        _train(blk, [x.clone() for x in xs], 1e-2, 2, graphed=False)
+        losses = _train(blk, [x.clone() for x in xs], 1e-2, 5, graphed=graphed)
+        gg.check_status()
+        out.append((losses, [blk.pools.local_weight(n).clone() for n in ("gate", "up", "down")]))
+        if in_epilogue:
+            assert int(blk.moe._upd_mask[:cfg.epn].sum()) == cfg.epn, "one rank: every expert takes the fused path"
+        blk.destroy()
+    (l0, w0), (l1, w1) = out
+    assert l0 == l1, (l0, l1)
+    assert l0[0] != l0[2]
+    for a, b in zip(w0, w1):
+        assert torch.equal(a, b)
