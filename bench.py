@@ -394,13 +394,12 @@ def run_ours(args):
     clocks = sampler.stop()
     peak_gb = torch.cuda.max_memory_allocated() / 2**30
 
-    def time_ops(fns, n=5):
-        """Device time of each callable (CUDA events on this stream, mean of n after 2 warm-up calls,
-        barrier on both sides, max over ranks), in microseconds."""
-        out = []
-        for fn in fns:
-            for _ in range(2):
-                fn()
+    def best_of(fn, n=5, reps=3):
+        """Device time of ``fn`` in microseconds: CUDA events around n back-to-back calls, barrier on both sides,
+        max over ranks -- and the best of ``reps`` such batches, because these calls are launched from Python
+        and a pause of the host (another process, the garbage collector) stretches the batch it falls into."""
+        best = float("inf")
+        for _ in range(reps):
             barrier_sync(world)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -408,7 +407,16 @@ def run_ours(args):
                 fn()
             e1.record()
             barrier_sync(world)
-            out.append(round(max_over_ranks(e0.elapsed_time(e1) / n * 1e3, world), 1))
+            best = min(best, max_over_ranks(e0.elapsed_time(e1) / n * 1e3, world))
+        return best
+
+    def time_ops(fns, n=5):
+        """``best_of`` for each callable after 2 warm-up calls."""
+        out = []
+        for fn in fns:
+            for _ in range(2):
+                fn()
+            out.append(round(best_of(fn, n), 1))
         return out
 
     def comm_times(buf, xin, w, topk, tpe):
@@ -451,14 +459,7 @@ def run_ours(args):
             def time_comm(overlap):
                 for _ in range(3):
                     plan = comm(overlap)
-                barrier_sync(world)
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(5):
-                    comm(overlap)
-                e1.record()
-                barrier_sync(world)
-                return max_over_ranks(e0.elapsed_time(e1) / 5 * 1e3, world), plan
+                return best_of(lambda: comm(overlap)), plan
 
             # the same three calls in a row as the reference arm times, then with the prefetch issued
             # asynchronously: its kernel has barrier words of its own and runs beside the combine
