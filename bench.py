@@ -183,6 +183,8 @@ def run_ours(args):
     def place_optimizer(b):
         if args.optimizer != "after":
             b.fuse_optimizer(lr, in_epilogue=args.optimizer == "epilogue")
+            if args.optimizer == "epilogue" and b.moe.epilogue_lr is None:
+                args.optimizer = "backward"       # weight shapes the CTA-pair kernel does not cover
 
     # where in a captured step the host-to-device copy of the NEXT step's batch starts (end-to-end run)
     # ("quiet": the stretch of the backward pass without communication kernels, see ExpertParallelMoE.on_comm_quiet;

@@ -123,6 +123,8 @@ class MoEBlock:
         other ranks, whose gradients are reduced first.  Same arithmetic, same result."""
         self._fused_lr = lr
         moe = self.moe
+        # shapes the CTA-pair weight-gradient kernel does not cover fall back to the stand-alone kernels
+        in_epilogue = in_epilogue and all(gg.wgrad_update_supported(*self.pools.shape(n)) for n in ("gate", "up", "down"))
         moe.epilogue_lr = lr if (in_epilogue and lr is not None) else None
         if lr is None:
             moe.on_grad_ready = None

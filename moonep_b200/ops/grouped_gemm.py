@@ -235,6 +235,11 @@ def dgrad_gate_up(dgu, wg, wu, cu, out, groups=None, num_ctas=None, dynamic=Fals
             push=push, push_w=push_w)
 
 
+def wgrad_update_supported(M: int, N: int) -> bool:
+    """Whether ``wgrad(update=...)`` exists for ``[M, N]`` weight matrices (the CTA-pair kernel carries it)."""
+    return M % 256 == 0 and N % 256 == 0 and os.environ.get("MOONEP_WGRAD_2CTA", "1") != "0"
+
+
 def wgrad(x, dy, cu, out, accumulate=False, zero_empty_below=0, groups=None, num_ctas=None, dynamic=False, ticket=None,
           update=None):
     """``out[g] (+)= x_g^T dy_g`` in fp32; ``out [G, in, out_dim]``.  ``dy`` may be a column slice
