@@ -149,7 +149,7 @@ def epilogue_optimizer_scenario(rank, R, dev):
     init = {n: (torch.randn(epn, *shp, device=dev, generator=g) * 0.05).to(torch.bfloat16)
             for n, shp in (("gate", (H, Hp)), ("up", (H, Hp)), ("down", (Hp, H)))}
     final, fused_any = [], 0
-    for in_epilogue in (False, True):
+    for in_epilogue, overlap in ((False, True), (True, True), (True, False)):
         buf = Buffer(S, H, K, E, R, num_sms=8, token_padding=pad, push_combine=True)
         pools = ExpertPools(epn, (H, Hp), (H, Hp), (Hp, H), with_grads=True)
         for n in init:
@@ -157,7 +157,7 @@ def epilogue_optimizer_scenario(rank, R, dev):
             pools.compute_grad(n).zero_()
         torch.cuda.synchronize()
         dist.barrier()
-        layer = ExpertParallelMoE(buf, pools, overlap_backward=True, ready_flags=True)
+        layer = ExpertParallelMoE(buf, pools, overlap_backward=overlap, ready_flags=True)
         if in_epilogue:
             layer.epilogue_lr = lr
 
@@ -190,8 +190,10 @@ def epilogue_optimizer_scenario(rank, R, dev):
         dist.barrier()
     for n in init:
         chk(not torch.equal(final[0][n], init[n]), f"epilogue optimizer: {n} was not trained")
-        chk(torch.equal(final[0][n], final[1][n]),
-            f"epilogue optimizer: {n} differs from the stand-alone optimizer ({int((final[0][n] != final[1][n]).sum())} elements)")
+        for v, label in ((1, "overlapped backward"), (2, "serial backward")):
+            chk(torch.equal(final[0][n], final[v][n]),
+                f"epilogue optimizer, {label}: {n} differs from the stand-alone optimizer "
+                f"({int((final[0][n] != final[v][n]).sum())} elements)")
     tot = torch.tensor([fused_any, epn - fused_any], device=dev)
     dist.all_reduce(tot)
     chk(int(tot[0]) > 0, "epilogue optimizer: no expert took the fused path")

@@ -167,13 +167,15 @@ def test_captured_steps_stage_the_next_batch(cuda_device):
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("overlap", ["1", "0"], ids=["overlapped_backward", "serial_backward"])
 @pytest.mark.parametrize("graphed", [False, True], ids=["eager", "captured"])
-def test_optimizer_in_the_wgrad_epilogue_matches_the_stand_alone_optimizer(graphed, cuda_device):
+def test_optimizer_in_the_wgrad_epilogue_matches_the_stand_alone_optimizer(graphed, overlap, cuda_device, monkeypatch):
     """``fuse_optimizer(lr, in_epilogue=True)``: the experts are updated by their weight-gradient GEMMs
     (wgrad(gate) moves behind dgrad(gate/up) for that).  Losses and weights must equal those of
     the same steps with the optimizer after the backward pass, bit for bit."""
     from moonep_b200.models.moe_block import MoEBlock, MoEConfig
     from moonep_b200.ops import grouped_gemm as gg
+    monkeypatch.setenv("MOONEP_OVERLAP_BACKWARD", overlap)
     cfg = MoEConfig("t", H=256, Hp=256, K=2, epn=4, shared_experts=1, S=192)
     g = torch.Generator(device="cuda").manual_seed(8)
     xs = [(torch.randn(cfg.S, cfg.H, device="cuda", generator=g) * 0.5).to(torch.bfloat16) for _ in range(2)]
