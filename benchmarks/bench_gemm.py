@@ -52,6 +52,7 @@ def main():
     dA = torch.empty(rows, Hp, **bf)
     dWg = torch.empty(G, H, Hp, device="cuda")
     dWd = torch.empty(G, Hp, H, device="cuda")
+    upd_all = torch.ones(G, dtype=torch.int32, device="cuda")
     peak = None
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -63,6 +64,9 @@ def main():
         "dgrad_gate_up": (lambda: gg.dgrad_gate_up(gu, wg, wu, cu, y), 2 * 2 * rows * H * Hp),
         "wgrad_gate": (lambda: gg.wgrad(x, gu[:, :Hp], cu, dWg), 2 * rows * H * Hp),
         "wgrad_down": (lambda: gg.wgrad(act, y, cu, dWd), 2 * rows * H * Hp),
+        # optimizer in the epilogue: every group's bf16 weights are updated, no fp32 gradient is written
+        "wgrad_gate_sgd_epilogue": (lambda: gg.wgrad(x, gu[:, :Hp], cu, dWg, update=(wg, 1e-6, upd_all)), 2 * rows * H * Hp),
+        "sgd_step_gate": (lambda: gg.sgd_step(wg, dWg, 1e-6), 0),
     }
     only = [m for m in a.only.split(",") if m]
     for name, (fn, flops) in cases.items():
@@ -71,6 +75,10 @@ def main():
         ms = timed(fn, warmup=a.warmup, iters=a.iters)
         tf = flops / ms / 1e9
         row = {"mode": name, "ms": round(ms, 4), "tflops": round(tf, 1)}
+        if not flops:          # a memory-bound helper: report bytes instead (fp32 gradient + bf16 weights read, weights written)
+            row = {"mode": name, "ms": round(ms, 4), "GBps": round(G * H * Hp * 8 / ms / 1e6, 1)}
+            print(json.dumps(row))
+            continue
         if peak:
             row["frac_of_measured_cublas_peak"] = round(tf / peak, 3)
         print(json.dumps(row))

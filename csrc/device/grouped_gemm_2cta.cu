@@ -213,10 +213,12 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       auto wptr = [&](int i, int k) {
         return const_cast<__nv_bfloat16*>(wbase) + (size_t)((lane >> 2) + 8 * k) * args.N + i * 32 + (lane & 3) * 8;
       };
-      int4 wv[2][4];
-      if (upd) {                       // first chunk's weights: in flight while the tile's MMAs finish
+      int4 wv[4][4];
+      if (upd) {                       // the tile's weights (this warp's 32 x 128 part): in flight while its MMAs finish
 #pragma unroll
-        for (int k = 0; k < 4; ++k) wv[0][k] = *reinterpret_cast<const int4*>(wptr(0, k));
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) wv[i][k] = *reinterpret_cast<const int4*>(wptr(i, k));
       }
       const int acc = tcnt & 1; const uint32_t aph = (uint32_t)(tcnt >> 1) & 1u;
       int ok = 1;
@@ -236,10 +238,6 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         tc::tmem_ld_wait();
         if (i + 1 < 4) {
           tc::tmem_ld32(taddr + (c + 1) * 32, r[(i + 1) & 1]);
-          if (upd) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) wv[(i + 1) & 1][k] = *reinterpret_cast<const int4*>(wptr(i + 1, k));
-          }
         } else {
           tc::fence_before_sync();
           __syncwarp();
@@ -260,7 +258,7 @@ wgrad_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
             const int4 g1 = tc::ld_shared_v4(ubuf + R * 128 + (((p2 + 1) ^ (R & 7)) << 4));
             const float gg[8] = {__int_as_float(g0.x), __int_as_float(g0.y), __int_as_float(g0.z), __int_as_float(g0.w),
                                  __int_as_float(g1.x), __int_as_float(g1.y), __int_as_float(g1.z), __int_as_float(g1.w)};
-            int4 x = wv[i & 1][k];
+            int4 x = wv[i][k];
             __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
