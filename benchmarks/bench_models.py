@@ -35,6 +35,12 @@ def main():
     ap.add_argument("--private-slots", action="store_true",
                     help="every block gets its own Buffer and its own prefetch / reduce slots (default: the blocks "
                          "share one Buffer and one set of slots when there is more than one rank)")
+    ap.add_argument("--optimizer", default="epilogue", choices=["epilogue", "after"],
+                    help="experts' SGD in the epilogue of the weight-gradient GEMMs (default) or as kernels after the backward pass")
+    ap.add_argument("--no-attention", action="store_true",
+                    help="leave out the attention stand-in in front of every MoE layer (QKV projection, causal "
+                         "scaled-dot-product attention over the rank's tokens as one sequence, output projection; "
+                         "library kernels: it only gives the stack the compute a transformer block has between two MoE layers)")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
@@ -53,17 +59,39 @@ def main():
         shared_slots = SharedSlots(cfg.epn, (cfg.H, cfg.Hp), (cfg.H, cfg.Hp), (cfg.Hp, cfg.H), with_grads=True)
     blocks = [MoEBlock(cfg, world, rank, num_sms=32, seed=l, buffer=shared_buf, shared_slots=shared_slots) for l in range(layers)]
     x0 = torch.randn(cfg.S, cfg.H, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank)).to(torch.bfloat16)
+    lr = 1e-5
+    if a.optimizer == "epilogue":
+        for b in blocks:
+            b.fuse_optimizer(lr, in_epilogue=True)
+    attention = layers > 1 and not a.no_attention
+    heads = max(1, cfg.H // 128)
+    attn_w = []
+    if attention:
+        g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+        for _ in blocks:
+            attn_w.append(((torch.randn(cfg.H, 3 * cfg.H, device="cuda", generator=g) * cfg.H ** -0.5).to(torch.bfloat16).requires_grad_(True),
+                           (torch.randn(cfg.H, cfg.H, device="cuda", generator=g) * cfg.H ** -0.5).to(torch.bfloat16).requires_grad_(True)))
+
+    def norm(h):
+        return (h.float() * torch.rsqrt(h.float().pow(2).mean(dim=-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
 
     def step():
         x = x0.detach().requires_grad_(True)
         h = x
-        for b in blocks:            # pre-norm residual stream between the blocks
-            hn = (h.float() * torch.rsqrt(h.float().pow(2).mean(dim=-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
-            h = h + b.forward(hn)
+        for i, b in enumerate(blocks):            # pre-norm residual stream
+            if attention:
+                wqkv, wo = attn_w[i]
+                q, k, v = (norm(h) @ wqkv).view(cfg.S, 3, heads, cfg.H // heads).permute(1, 2, 0, 3).unsqueeze(1)
+                o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+                h = h + o.squeeze(0).permute(1, 0, 2).reshape(cfg.S, cfg.H) @ wo
+            h = h + b.forward(norm(h))
         loss = (h.float() ** 2).mean()
         loss.backward()
         for b in blocks:
-            b.sgd_step(1e-5)
+            b.sgd_step(lr)
+        for pair in attn_w:
+            for w in pair:
+                w.grad = None
         return loss.detach()
 
     for mv in sweep:
@@ -90,6 +118,7 @@ def main():
                               "iteration_ms": round(ms, 3), "tokens_per_s": round(cfg.S * world / ms * 1e3),
                               "peak_torch_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2),
                               "slots": "shared by all blocks" if shared_slots is not None else "one set per block",
+                              "optimizer": a.optimizer, "attention_stand_in": attention,
                               "expert_and_comm_mem_gib": round((sum(b.pools.bytes_per_rank for b in blocks)
                                                                 + (shared_slots.bytes_per_rank if shared_slots is not None else 0)
                                                                 + sum(bf._heap.chunk_bytes for bf in {id(b.buf): b.buf for b in blocks}.values()))
