@@ -48,6 +48,29 @@ class MoEContext:
 _DEFERRED: list = []       # layers whose last gradient reduction is still running (see wait_grads)
 
 
+def update_mask(experts_to_copy, rank: int, epn: int, mask=None, hit=None, ones=None):
+    """int32 ``[2*epn]`` over the groups of the compute view ``[local | slots]``: 1 for the local experts whose
+    gradient is complete on this rank (``experts_to_copy`` -- ``[R, epn]``, expert id held by every slot of every
+    rank, -1 for none -- names no replica of them), 0 for replicated local experts and for the slots.
+    Pure tensor ops on the table's device, no host synchronisation; ``mask`` / ``hit`` / ``ones`` are optional
+    preallocated work tensors (``[2*epn]``, ``[epn+1]``, ``[R*epn]`` int32)."""
+    dev = experts_to_copy.device
+    flat = experts_to_copy.reshape(-1)
+    if mask is None:
+        mask = torch.zeros(2 * epn, dtype=torch.int32, device=dev)
+    if hit is None:
+        hit = torch.zeros(epn + 1, dtype=torch.int32, device=dev)
+    if ones is None:
+        ones = torch.ones(flat.numel(), dtype=torch.int32, device=dev)
+    idx = flat.long() - rank * epn
+    idx = torch.where((idx >= 0) & (idx < epn), idx, torch.full_like(idx, epn))
+    hit.zero_()
+    hit.scatter_(0, idx, ones)
+    mask[:epn] = 1 - hit[:epn]
+    mask[epn:] = 0
+    return mask
+
+
 class ExpertParallelMoE:
     def __init__(self, buffer: Buffer, pools: ExpertPools, overlap_prefetch: bool = True,
                  overlap_backward: bool | None = None, ready_flags: bool | None = None):
@@ -97,15 +120,7 @@ class ExpertParallelMoE:
         self._upd_ones = torch.ones(g.R * g.epn, **i32)
 
     def _update_mask(self, plan):
-        """int32 ``[2*epn]``: 1 for the local experts whose gradient is complete on this rank (no replica of
-        them is in any rank's slots under ``plan``), 0 for replicated local experts and for the slots."""
-        epn = self.geo.epn
-        idx = plan.experts_to_copy.reshape(-1).long() - self.buf.rank * epn
-        idx = torch.where((idx >= 0) & (idx < epn), idx, torch.full_like(idx, epn))
-        self._upd_hit.zero_()
-        self._upd_hit.scatter_(0, idx, self._upd_ones)
-        self._upd_mask[:epn] = 1 - self._upd_hit[:epn]
-        return self._upd_mask
+        return update_mask(plan.experts_to_copy, self.buf.rank, self.geo.epn, self._upd_mask, self._upd_hit, self._upd_ones)
 
     # weights / grads as [2*epn, in, out]
     def _W(self, n):

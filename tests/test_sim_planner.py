@@ -219,3 +219,31 @@ def test_skew_solver_hits_the_requested_maxvio(target):
     topk, w, tpe = routing.softmax_topk(S, K, E, scale, 0, 3)
     assert torch.allclose(w.sum(dim=1), torch.ones(S), atol=1e-5) and int(tpe.sum()) == S * K
     assert all(len(set(row.tolist())) == K for row in topk[:32])
+
+
+def test_update_mask_names_exactly_the_unreplicated_local_experts():
+    """The mask that decides which experts the weight-gradient GEMM may update in its epilogue: on real plans
+    of the oracle, a local expert is masked in iff no rank holds a replica of it; slots are never masked in."""
+    import torch
+    from moonep_b200.moe_layer import update_mask
+    R, epn, S, K = 4, 6, 300, 4
+    E = R * epn
+    seen_replica = False
+    for seed in range(5):
+        topk = np.stack([routing.lognormal_topk(S, K, E, R, 2.0, seed, r)[0].numpy() for r in range(R)])
+        cp = plan_cluster(topk, E, 16)
+        etc = torch.from_numpy(np.asarray(cp.experts_to_copy)).to(torch.int32)
+        replicated = {int(e) for e in etc.flatten().tolist() if e >= 0}
+        seen_replica |= bool(replicated)
+        for r in range(R):
+            m = update_mask(etc, r, epn)
+            assert m.dtype == torch.int32 and m.shape == (2 * epn,)
+            want = [0 if (r * epn + g) in replicated else 1 for g in range(epn)] + [0] * epn
+            assert m.tolist() == want, f"seed {seed} rank {r}"
+    assert seen_replica, "the routing must produce replicas for this test to mean anything"
+    # preallocated work tensors are reused correctly across calls with different tables
+    mask, hit, ones = torch.zeros(2 * epn, dtype=torch.int32), torch.zeros(epn + 1, dtype=torch.int32), torch.ones(R * epn, dtype=torch.int32)
+    a = torch.full((R, epn), -1, dtype=torch.int32); a[1, 0] = 2
+    assert update_mask(a, 0, epn, mask, hit, ones).tolist() == [1, 1, 0, 1, 1, 1] + [0] * epn
+    b = torch.full((R, epn), -1, dtype=torch.int32)
+    assert update_mask(b, 0, epn, mask, hit, ones).tolist() == [1] * epn + [0] * epn
