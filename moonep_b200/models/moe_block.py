@@ -141,6 +141,7 @@ class MoEBlock:
                 gg.sgd_step(self.pools.local_weight(n), self.pools.local_grad(n), lr)
         else:
             assert lr == self._fused_lr, "the experts were already updated with another learning rate"
+            self.moe.wait_grads()       # the last reduction and the update behind it may still be running
         with torch.no_grad():
             for p in self.parameters():
                 if p.grad is not None:

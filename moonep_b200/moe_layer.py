@@ -339,13 +339,22 @@ class ExpertParallelMoE:
             # ``defer_last_reduction`` it is left running on the comm stream and ``wait_grads()`` (or
             # ``wait_grads("up")``) joins it, so an optimizer can update ``down`` and ``gate`` meanwhile
             ev_up = buf.reduce_grad_subset(ctx.plan, [pair("up")], clear_slots=acc,
-                                           async_finish=ov and self.defer_last_reduction and self.on_grad_ready is None)
-            if ev_up is not None:
+                                           async_finish=ov and self.defer_last_reduction)
+            if ev_up is not None and self.on_grad_ready is None:
                 self.grads_pending = ("up", ev_up)
                 _DEFERRED.append(self)
         if self.on_grad_ready is not None:
-            self.on_grad_ready("up")
-            main.wait_stream(self._opt)
+            if multi and ev_up is not None:
+                # the deferred reduction is followed by the optimizer hook of ``up`` on the optimizer stream;
+                # ``wait_grads`` then joins that stream (and with it the hooks of ``down`` and ``gate``)
+                self._opt.wait_event(ev_up)
+                with torch.cuda.stream(self._opt):
+                    self.on_grad_ready("up")
+                    self.grads_pending = ("up", self._opt.record_event())
+                _DEFERRED.append(self)
+            else:
+                self.on_grad_ready("up")
+                main.wait_stream(self._opt)
         return grad_hidden, grad_w
 
     def wait_grads(self, name: str | None = None) -> None:

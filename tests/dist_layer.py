@@ -158,6 +158,7 @@ def epilogue_optimizer_scenario(rank, R, dev):
         torch.cuda.synchronize()
         dist.barrier()
         layer = ExpertParallelMoE(buf, pools, overlap_backward=overlap, ready_flags=True)
+        layer.defer_last_reduction = True        # the reduction of ``up`` (and the update behind it) is joined by wait_grads()
         if in_epilogue:
             layer.epilogue_lr = lr
 
